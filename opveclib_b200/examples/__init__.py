@@ -1,0 +1,5 @@
+"""Example operators written in the operator language (counterparts of opveclib/examples/__init__.py)."""
+from .accumulate import accumulate, cumsum, cumprod
+from .expm1 import expm1, expm1_grad
+from .log1p import log1p, log1p_grad
+from .lstm import lstm, lstm_grad
