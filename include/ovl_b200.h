@@ -1,0 +1,140 @@
+/*
+ * ovl_b200.h - C ABI of the B200 operator launcher (libovl_b200.so).
+ *
+ * This library is what a host program binds to run OVL operators on a B200.  It replaces the reference's
+ * native glue for the evaluate path:
+ *   - the per-operator C++ entry point `<name>_generic_cuda(std::vector<std::shared_ptr<const InputParameter>>,
+ *     std::vector<std::shared_ptr<OutputParameter>>, CUstream, uint16_t threads_per_block, uint16_t* err)`
+ *     generated at opveclib/expression.py:685-699 (C++ STL types across a dlopen boundary, not a C ABI);
+ *   - the standalone CUDA harness `testCUDAOperator` (opveclib/testcudaop.cc:60-395);
+ *   - the launcher half of the TensorFlow custom op (opveclib/dynamiclibop.cc:127-171).
+ * Signatures use plain pointers and sizes only.  The callee never owns tensor memory (as in
+ * opveclib/dynamiclibop.h:48,77); modules and kernels live until destroyed or process exit.  Every function
+ * returns an OvlStatus; nothing calls exit() (the reference's harness does, opveclib/testcudaop.cc:22-43).
+ * Launches are asynchronous on the caller's stream and the library is re-entrant, like the reference's GPU
+ * launcher (opveclib/dynamiclibop.cc:161-171).
+ */
+#ifndef OVL_B200_H_
+#define OVL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Element type codes: wire values of the language's DType enum (opveclib/language.proto:16-37). */
+enum OvlDType {
+    OVL_FLOAT16 = 1, OVL_FLOAT32 = 2, OVL_FLOAT64 = 3, OVL_INT8 = 4, OVL_INT16 = 5, OVL_INT32 = 6, OVL_INT64 = 7,
+    OVL_UINT8 = 8, OVL_UINT16 = 9, OVL_UINT32 = 10, OVL_UINT64 = 11
+};
+
+/* Status codes.  OVL_ERR_ARITY / OVL_ERR_LENGTH correspond to the reference's `*err = 1` on a wrong number of
+ * tensors or a wrong element count (opveclib/expression.py:622, 639, 662-663). */
+enum OvlStatus {
+    OVL_OK = 0,
+    OVL_ERR_ARITY = 1,       /* wrong number of input or output tensors */
+    OVL_ERR_LENGTH = 2,      /* a tensor's element count differs from the kernel's signature */
+    OVL_ERR_DTYPE = 3,       /* a tensor's dtype differs from the kernel's signature */
+    OVL_ERR_NULL = 4,        /* a required pointer is null */
+    OVL_ERR_CUDA = 5,        /* a CUDA call failed; see ovl_last_cuda_error() */
+    OVL_ERR_NOT_FOUND = 6,   /* kernel symbol not present in the module */
+    OVL_ERR_SCRATCH = 7,     /* scratch buffer missing, too small or misaligned */
+    OVL_ERR_TIMEOUT = 8,     /* a bounded device-side wait expired (reported through the kernel's status word) */
+    OVL_ERR_ALIGNMENT = 9,   /* a tensor pointer does not meet the alignment the kernel was built for */
+    OVL_ERR_TOO_LARGE = 10,  /* size beyond what the entry point supports */
+    OVL_ERR_INVALID = 11     /* malformed specification */
+};
+
+/* A tensor argument: borrowed device (or host, where stated) memory, dtype code and element count.
+ * Same fields as the reference's `_TensorParam` / `TensorParam` (opveclib/operator.py:128-131,
+ * opveclib/testcop.cc:28-32). */
+typedef struct OvlTensor {
+    void* data;
+    int32_t dtype;
+    uint64_t len;
+} OvlTensor;
+
+typedef struct OvlModule OvlModule; /* a loaded cubin */
+typedef struct OvlKernel OvlKernel; /* one kernel of a module together with its signature and launch shape */
+
+/* Launch description of one generated kernel.  Kernel parameters are, in order: the input pointers, the
+ * output pointers, then the scratch pointer if scratch_bytes > 0. */
+typedef struct OvlKernelSpec {
+    const char* symbol;          /* name of the __global__ function inside the module */
+    uint32_t grid_x;             /* number of thread blocks */
+    uint32_t block_x;            /* threads per block */
+    uint32_t dynamic_smem_bytes; /* dynamic shared memory per block */
+    uint32_t n_inputs;
+    uint32_t n_outputs;
+    const int32_t* dtypes;       /* n_inputs + n_outputs dtype codes, inputs first */
+    const uint64_t* lens;        /* n_inputs + n_outputs element counts */
+    const uint32_t* align_bytes; /* n_inputs + n_outputs required pointer alignments (0 or 1 = none) */
+    uint64_t scratch_bytes;      /* device scratch the kernel needs (0 = none); provided by the caller */
+    uint64_t scratch_zero_bytes; /* leading part of the scratch that must be zero when the kernel starts;
+                                    ovl_launch clears it on the stream before the kernel */
+} OvlKernelSpec;
+
+/* Library / device ------------------------------------------------------------------------------------- */
+const char* ovl_version(void);
+const char* ovl_status_string(int status);
+/* CUDA error code of the calling thread's most recent OVL_ERR_CUDA (a cudaError_t value), 0 if none. */
+int ovl_last_cuda_error(void);
+/* Number of streaming multiprocessors of the current device. */
+int ovl_device_sm_count(int* out_count);
+
+/* Modules and kernels ---------------------------------------------------------------------------------- */
+/* Load an sm_100a cubin image from memory / from a file into the current device's context. */
+int ovl_module_load(const void* image, size_t size, OvlModule** out_module);
+int ovl_module_load_file(const char* path, OvlModule** out_module);
+int ovl_module_unload(OvlModule* module);
+/* Look up spec->symbol and bind it to a copy of the specification. */
+int ovl_kernel_create(OvlModule* module, const OvlKernelSpec* spec, OvlKernel** out_kernel);
+int ovl_kernel_destroy(OvlKernel* kernel);
+
+/* Launching -------------------------------------------------------------------------------------------- */
+/* Validate the tensors against the kernel's signature (arity, element counts, dtypes, alignment), clear the
+ * zeroed part of the scratch and enqueue one launch on `cuda_stream` (a cudaStream_t; NULL = default stream).
+ * Tensors are DEVICE pointers.  Replaces `<name>_generic_cuda` (opveclib/expression.py:685-699). */
+int ovl_launch(OvlKernel* kernel, const OvlTensor* inputs, size_t n_inputs, const OvlTensor* outputs,
+               size_t n_outputs, void* scratch, uint64_t scratch_bytes, void* cuda_stream);
+
+/* Timed launches: `iterations` launches, each bracketed by CUDA events on `cuda_stream`; milliseconds per
+ * launch are written to ms[0..iterations).  Synchronises the stream.  Replaces the timing loop of
+ * opveclib/testcudaop.cc:294-304. */
+int ovl_profile(OvlKernel* kernel, const OvlTensor* inputs, size_t n_inputs, const OvlTensor* outputs,
+                size_t n_outputs, void* scratch, uint64_t scratch_bytes, void* cuda_stream, uint32_t iterations,
+                float* ms);
+
+/* Host-buffer convenience with the contract of the reference harness (opveclib/testcudaop.cc:60-395):
+ * tensors are HOST pointers; the call stages inputs to device memory it allocates, fills outputs with 0xFE
+ * bytes, runs `iterations` timed launches, copies outputs back, frees the staging memory and synchronises.
+ * `ms` may be NULL. */
+int ovl_run_host(OvlKernel* kernel, const OvlTensor* host_inputs, size_t n_inputs, const OvlTensor* host_outputs,
+                 size_t n_outputs, uint32_t iterations, float* ms);
+
+/* Read the 32-bit status word a kernel keeps at the start of its scratch buffer (0 = no error; otherwise an
+ * OvlStatus such as OVL_ERR_TIMEOUT).  Synchronises the stream. */
+int ovl_read_kernel_status(const void* scratch, void* cuda_stream, int32_t* out_status);
+
+/* Built-in scans ----------------------------------------------------------------------------------------- */
+/* Inclusive scan (op: 0 = sum, 1 = product) of `lines` contiguous lines of `n` fp32 elements each, device
+ * memory in and out, with the same cooperative single-pass kernel the code generator uses for recognised
+ * accumulate loops (the reference's one-worker-per-line loop: opveclib/examples/test_accumulate.py:22-78).
+ * `carry` (device pointer to one double, or NULL) is combined into every element of a single line (lines
+ * must be 1 when it is given).  `scratch` must hold ovl_scan_f32_scratch_bytes(lines, n) bytes. */
+uint64_t ovl_scan_f32_scratch_bytes(uint64_t lines, uint64_t n);
+int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
+                 uint64_t scratch_bytes, void* cuda_stream);
+/* Reduce `n` fp32 elements to one double (sum or product, fixed combination order): the shard total that
+ * ranks exchange before a scan that crosses shard boundaries.  `scratch` must hold
+ * ovl_reduce_f32_scratch_bytes(n) bytes. */
+uint64_t ovl_reduce_f32_scratch_bytes(uint64_t n);
+int ovl_reduce_f32(int op, const float* in, uint64_t n, double* out_total, void* scratch, uint64_t scratch_bytes,
+                   void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OVL_B200_H_ */

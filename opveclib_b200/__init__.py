@@ -17,5 +17,6 @@ from .expr import minimum, maximum, power, arctan2, logical_and, logical_or
 from .expr import arange, if_, elif_, else_
 # operators
 from .opgraph import operator, gradient
+from .runtime import evaluate, profile
 # local runtime environment
 from .local import version, logger, cuda_enabled, cache_directory, clear_op_cache

@@ -1,0 +1,307 @@
+// Cooperative inclusive scan along contiguous lines: single pass, decoupled look-back (sm_100a).
+//
+// The operator language expresses a scan as one worker walking a whole line serially
+// (opveclib/examples/test_accumulate.py:22-78).  Here a line of n elements is cut into tiles of
+// BLOCK * VPT * VEC elements; thread blocks claim tiles in order from an atomic counter, scan their tile in
+// registers (serial scan inside each 128-bit vector, warp-shuffle scan across lanes, shared-memory scan across
+// warps), publish the tile aggregate, and obtain the prefix of everything to their left in the same line by
+// looking back over the descriptors of earlier tiles: aggregates are summed until a tile that already knows its
+// inclusive prefix is met.  Every element is read once and written once.
+//
+// Accumulation runs in the wider type Acc (double for fp32 data), so results do not depend on how the line was
+// cut and are the correctly rounded exact scan rather than a re-association of fp32 partial sums.
+//
+// Every wait on another block is bounded: when the bound expires the block records OVL_ERR_TIMEOUT in the status
+// word at the start of the scratch buffer and carries on with the identity as prefix; the host reports the
+// error after the launch.  Nothing traps.
+#pragma once
+#include "ovl_common.cuh"
+
+namespace ovl {
+
+constexpr int kScanBlock = 256;   // threads per block
+constexpr int kScanVpt = 4;       // 128-bit vectors per thread
+constexpr uint32_t kScanSpinLimit = 1u << 22;
+constexpr int32_t kErrTimeout = 8;  // OVL_ERR_TIMEOUT
+
+struct OpAdd {
+    template <typename A> static __device__ __forceinline__ A identity() { return A(0); }
+    template <typename A> static __device__ __forceinline__ A apply(A a, A b) { return a + b; }
+};
+struct OpMul {
+    template <typename A> static __device__ __forceinline__ A identity() { return A(1); }
+    template <typename A> static __device__ __forceinline__ A apply(A a, A b) { return a * b; }
+};
+
+// scratch layout: header, then one descriptor per tile
+struct ScanHeader {
+    int32_t status;         // 0, or an error code set by a block whose wait expired
+    uint32_t tile_counter;  // next tile to hand out
+    uint32_t pad[2];
+};
+template <typename Acc>
+struct alignas(16) TileDesc {
+    Acc aggregate;   // reduction of the tile alone            (valid when flag >= 1)
+    Acc prefix;      // reduction of the line up to tile's end (valid when flag == 2)
+    uint32_t flag;   // 0 empty, 1 aggregate published, 2 inclusive prefix published
+    uint32_t pad;
+};
+
+template <typename Acc>
+__host__ __device__ constexpr uint64_t scan_scratch_bytes(uint64_t total_tiles) {
+    return sizeof(ScanHeader) + total_tiles * sizeof(TileDesc<Acc>);
+}
+
+__device__ __forceinline__ uint32_t ld_flag(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_flag(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <typename A>
+__device__ __forceinline__ A shfl_up_any(A v, int delta) {
+    if constexpr (sizeof(A) == 8) {
+        long long x = *reinterpret_cast<long long*>(&v);
+        x = __shfl_up_sync(0xffffffffu, x, delta);
+        return *reinterpret_cast<A*>(&x);
+    } else {
+        return __shfl_up_sync(0xffffffffu, v, delta);
+    }
+}
+template <typename A>
+__device__ __forceinline__ A shfl_any(A v, int lane) {
+    if constexpr (sizeof(A) == 8) {
+        long long x = *reinterpret_cast<long long*>(&v);
+        x = __shfl_sync(0xffffffffu, x, lane);
+        return *reinterpret_cast<A*>(&x);
+    } else {
+        return __shfl_sync(0xffffffffu, v, lane);
+    }
+}
+
+// One launch scans `lines` lines of `n` elements.  ALIGNED: every line start is VEC-aligned (n % VEC == 0 or a
+// single line) and the base pointers are 16-byte aligned, so whole vectors can be moved with one instruction.
+template <typename T, typename Acc, class Op, int VEC, bool ALIGNED, bool HAS_CARRY>
+__device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry,
+                                           const uint64_t lines, const uint64_t n, void* scratch) {
+    constexpr int BLOCK = kScanBlock;
+    constexpr int VPT = kScanVpt;
+    constexpr int WARPS = BLOCK / 32;
+    constexpr uint32_t TILE = BLOCK * VPT * VEC;
+    constexpr uint32_t WARP_ELEMS = 32 * VPT * VEC;
+
+    ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
+    TileDesc<Acc>* desc = reinterpret_cast<TileDesc<Acc>*>(hdr + 1);
+    const uint64_t tiles_per_line = (n + TILE - 1) / TILE;
+    const uint64_t total_tiles = tiles_per_line * lines;
+
+    __shared__ Acc s_warp_total[WARPS];
+    __shared__ Acc s_exclusive;
+    __shared__ uint64_t s_tile;
+
+    const int lane = threadIdx.x & 31;
+    const int wid = threadIdx.x >> 5;
+
+    while (true) {
+        if (threadIdx.x == 0) s_tile = atomicAdd(&hdr->tile_counter, 1u);
+        __syncthreads();
+        const uint64_t tile = s_tile;
+        if (tile >= total_tiles) break;
+        const uint64_t line = tile / tiles_per_line;
+        const uint64_t tile_in_line = tile - line * tiles_per_line;
+        const uint64_t line_base = line * n;
+        const uint64_t tile_off = tile_in_line * TILE;              // offset of the tile inside its line
+        const uint64_t warp_off = tile_off + (uint64_t)wid * WARP_ELEMS;
+
+        // ---- load: warp-striped, lane L owns vector j at warp_off + j*32*VEC + L*VEC
+        Acc x[VPT][VEC];
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const uint64_t off = warp_off + (uint64_t)(j * 32 + lane) * VEC;
+            if (ALIGNED && off + VEC <= n) {
+                const Vec<T, VEC> v = load_vec<T, VEC>(in + line_base + off);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) x[j][e] = (Acc)v.v[e];
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) x[j][e] = (off + e < n) ? (Acc)in[line_base + off + e] : Op::template identity<Acc>();
+            }
+        }
+
+        // ---- scan inside the warp's chunk
+        Acc run = Op::template identity<Acc>();
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+#pragma unroll
+            for (int e = 1; e < VEC; ++e) x[j][e] = Op::apply(x[j][e - 1], x[j][e]);
+            Acc t = x[j][VEC - 1];
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const Acc y = shfl_up_any(t, d);
+                if (lane >= d) t = Op::apply(y, t);
+            }
+            Acc excl = shfl_up_any(t, 1);
+            if (lane == 0) excl = Op::template identity<Acc>();
+            const Acc base = Op::apply(run, excl);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) x[j][e] = Op::apply(base, x[j][e]);
+            run = Op::apply(run, shfl_any(t, 31));
+        }
+        if (lane == 0) s_warp_total[wid] = run;
+        __syncthreads();
+
+        // ---- prefix of the warps to the left inside the tile, and the tile aggregate
+        Acc warp_excl = Op::template identity<Acc>();
+        Acc aggregate = Op::template identity<Acc>();
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const Acc v = s_warp_total[w];
+            if (w < wid) warp_excl = Op::apply(warp_excl, v);
+            aggregate = Op::apply(aggregate, v);
+        }
+
+        // ---- prefix of the tiles to the left inside the line (decoupled look-back, warp 0)
+        if (wid == 0) {
+            Acc exclusive = Op::template identity<Acc>();
+            if (tile_in_line == 0) {
+                if (HAS_CARRY) exclusive = *carry;
+            } else {
+                if (lane == 0) {
+                    desc[tile].aggregate = aggregate;
+                    st_flag(&desc[tile].flag, 1u);
+                }
+                int64_t look = (int64_t)tile - 1;              // nearest tile of the current window
+                const int64_t first = (int64_t)(tile - tile_in_line);
+                bool done = false;
+                while (!done) {
+                    const int64_t mine = look - lane;
+                    uint32_t flag = 2u;                          // lanes left of the line start: nothing to add
+                    Acc val = Op::template identity<Acc>();
+                    bool beyond = mine < first;
+                    if (!beyond) {
+                        uint32_t spins = 0;
+                        flag = ld_flag(&desc[mine].flag);
+                        while (flag == 0u && spins < kScanSpinLimit) {
+                            __nanosleep(32);
+                            flag = ld_flag(&desc[mine].flag);
+                            ++spins;
+                        }
+                        if (flag == 0u) {
+                            atomicExch(&hdr->status, kErrTimeout);
+                            flag = 2u;                           // give up: behave as if the line started here
+                        } else {
+                            val = (flag == 2u) ? *(volatile Acc*)&desc[mine].prefix : *(volatile Acc*)&desc[mine].aggregate;
+                        }
+                    }
+                    // nearest lane that holds an inclusive prefix ends the look-back
+                    const uint32_t has_prefix = __ballot_sync(0xffffffffu, flag == 2u);
+                    const int stop = __ffs(has_prefix) - 1;      // always >= 0 once the window passes the line start
+                    const int last = (stop >= 0) ? stop : 31;
+                    // combine left to right: lane `last` (farthest) ... lane 0 (nearest), then what we have
+                    Acc window = Op::template identity<Acc>();
+                    for (int k = last; k >= 0; --k) window = Op::apply(window, shfl_any(val, k));
+                    exclusive = Op::apply(window, exclusive);
+                    if (stop >= 0) done = true;
+                    look -= 32;
+                }
+            }
+            if (lane == 0) {
+                desc[tile].prefix = Op::apply(exclusive, aggregate);
+                st_flag(&desc[tile].flag, 2u);
+                s_exclusive = exclusive;
+            }
+        }
+        __syncthreads();
+        const Acc offset = Op::apply(s_exclusive, warp_excl);
+
+        // ---- store
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const uint64_t off = warp_off + (uint64_t)(j * 32 + lane) * VEC;
+            if (ALIGNED && off + VEC <= n) {
+                Vec<T, VEC> v;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) v.v[e] = (T)Op::apply(offset, x[j][e]);
+                store_vec<T, VEC>(out + line_base + off, v);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e)
+                    if (off + e < n) out[line_base + off + e] = (T)Op::apply(offset, x[j][e]);
+            }
+        }
+        __syncthreads();   // s_tile / s_exclusive / s_warp_total are reused by the next tile
+    }
+}
+
+// Reduction of n elements to one Acc, combination order fixed by the launch shape: per-thread strided partials,
+// block tree, then the last block to finish combines the per-block partials in block order.
+// scratch: [uint32 done_counter, pad to 16 bytes][Acc partial per block]
+template <typename T, typename Acc, class Op, int VEC, bool ALIGNED>
+__device__ __forceinline__ void reduce_all(const T* __restrict__ in, const uint64_t n, Acc* __restrict__ out_total,
+                                           void* scratch) {
+    constexpr int BLOCK = kScanBlock;
+    __shared__ Acc s_part[BLOCK / 32];
+    __shared__ bool s_last;
+    uint32_t* counter = reinterpret_cast<uint32_t*>(scratch);
+    Acc* partials = reinterpret_cast<Acc*>(reinterpret_cast<char*>(scratch) + 16);
+
+    Acc acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = Op::template identity<Acc>();
+    const uint64_t nvec = ALIGNED ? n / VEC : 0;
+    const uint64_t stride = (uint64_t)gridDim.x * BLOCK;
+    uint64_t g = (uint64_t)blockIdx.x * BLOCK + threadIdx.x;
+    // four independent vectors in flight per thread
+    for (; g + 3 * stride < nvec; g += 4 * stride) {
+        Vec<T, VEC> v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = load_vec<T, VEC>(in + (g + u * stride) * VEC);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) acc[u] = Op::apply(acc[u], (Acc)v[u].v[e]);
+    }
+    for (; g < nvec; g += stride) {
+        const Vec<T, VEC> v = load_vec<T, VEC>(in + g * VEC);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) acc[0] = Op::apply(acc[0], (Acc)v.v[e]);
+    }
+    for (uint64_t i = nvec * VEC + (uint64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += stride)
+        acc[0] = Op::apply(acc[0], (Acc)in[i]);
+    Acc t = Op::apply(Op::apply(acc[0], acc[1]), Op::apply(acc[2], acc[3]));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        Acc y;
+        if constexpr (sizeof(Acc) == 8) {
+            long long xx = *reinterpret_cast<long long*>(&t);
+            xx = __shfl_down_sync(0xffffffffu, xx, d);
+            y = *reinterpret_cast<Acc*>(&xx);
+        } else {
+            y = __shfl_down_sync(0xffffffffu, t, d);
+        }
+        t = Op::apply(t, y);
+    }
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) s_part[wid] = t;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        Acc b = Op::template identity<Acc>();
+        for (int w = 0; w < BLOCK / 32; ++w) b = Op::apply(b, s_part[w]);
+        partials[blockIdx.x] = b;
+        __threadfence();
+        const uint32_t ticket = atomicAdd(counter, 1u);
+        s_last = (ticket == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        __threadfence();
+        Acc total = Op::template identity<Acc>();
+        for (uint32_t b = 0; b < gridDim.x; ++b) total = Op::apply(total, *(volatile Acc*)&partials[b]);
+        *out_total = total;
+    }
+}
+
+}  // namespace ovl

@@ -1,0 +1,448 @@
+"""CUDA code generation for sm_100a.
+
+Every (fused) kernel is lowered to a ``.cu`` translation unit that instantiates hand-written templates from
+``csrc/templates`` with the kernel's body.  The body is emitted as straight-line C, one statement per
+expression, in trace order and with each expression's own C type - the form the reference's generator emits
+(opveclib/expression.py:559-566 and the per-node ``gen_c``), so that fp32 arithmetic rounds at the same places
+as in the reference's C++ operator.  Code is compiled with ``--fmad=false`` and without fast-math; the
+differences to the C++ build that remain are those of CUDA's libm (expf, logf, tanhf ... within 1-2 ulp).
+
+Two entry points are generated per kernel:
+
+``<name>_gen``  one worker per loop iteration of a grid-stride loop; scalar accesses exactly as written.  The
+                correctness net for every access pattern (arbitrary scatter, loops, worker-local tensors).
+``<name>_vec``  each thread owns ``LANES`` consecutive workers along the innermost workgroup axis.  Reads and
+                writes whose offset is a wrap-free affine function of the position with unit stride along that
+                axis are hoisted out of the body into 128-bit ``ld.global.nc`` / ``st.global`` of the whole
+                group; offsets that do not depend on the innermost axis are loaded once per group; everything
+                else stays a scalar access in place.  Chosen at launch when every hoisted tensor's base pointer
+                is 16-byte aligned.
+
+Scans recognised by :mod:`opveclib_b200.patterns` use the cooperative scan template instead.
+"""
+import math
+
+from . import expr as E
+from .access import analyze
+from .kernel import iter_nodes
+from . import patterns
+
+_UNARY_F32 = {'acos': 'acosf', 'asin': 'asinf', 'atan': 'atanf', 'cos': 'cosf', 'cosh': 'coshf', 'sin': 'sinf',
+              'sinh': 'sinhf', 'tan': 'tanf', 'tanh': 'tanhf', 'exp': 'expf', 'log': 'logf', 'log10': 'log10f',
+              'sqrt': 'sqrtf', 'ceil': 'ceilf', 'floor': 'floorf', 'abs': 'fabsf'}
+_UNARY_F64 = {'acos': 'acos', 'asin': 'asin', 'atan': 'atan', 'cos': 'cos', 'cosh': 'cosh', 'sin': 'sin',
+              'sinh': 'sinh', 'tan': 'tan', 'tanh': 'tanh', 'exp': 'exp', 'log': 'log', 'log10': 'log10',
+              'sqrt': 'sqrt', 'ceil': 'ceil', 'floor': 'floor', 'abs': 'fabs'}
+_ABS_INT = {'int8': 'ovl::abs_8', 'int16': 'ovl::abs_16', 'int32': 'abs', 'int64': 'llabs'}
+_INFIX = {'add': '+', 'sub': '-', 'mul': '*', 'div': '/', 'mod': '%', 'eq': '==', 'ne': '!=', 'lt': '<',
+          'le': '<=', 'gt': '>', 'ge': '>=', 'and': '&&', 'or': '||'}
+_LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_MIN',
+           ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
+           ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
+
+TEMPLATE_VERSION = 'tv4'
+BLOCK_THREADS = 256
+# must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
+SCAN_BLOCK = 256
+SCAN_VPT = 4
+SCAN_HEADER_BYTES = 16
+
+
+def ctype(dtype):
+    return dtype.as_cstr()
+
+
+def literal(value):
+    if isinstance(value, float):
+        if math.isinf(value):
+            return 'INFINITY' if value > 0 else '(-INFINITY)'
+        if math.isnan(value):
+            return 'NAN'
+        return repr(value)
+    v = int(value)
+    if v > 2 ** 63 - 1:
+        return str(v) + 'ull'
+    if v == -2 ** 63:
+        return '(-9223372036854775807ll - 1)'
+    if abs(v) > 2 ** 31 - 1:
+        return str(v) + 'll'
+    return str(v)
+
+
+class BodyEmitter(object):
+    """Emits the statements of a kernel body.  ``read_subst`` / ``write_subst`` map id(node) of hoisted accesses
+    to the C text that replaces the memory access (a register expression / an assignment template)."""
+
+    def __init__(self, kernel, indent, read_subst=None, write_subst=None, position_text=None):
+        self.kernel = kernel
+        self.names = {}
+        self.lines = []
+        self.depth = indent
+        self.counter = 0
+        self.read_subst = read_subst or {}
+        self.write_subst = write_subst or {}
+        self.position_text = position_text
+
+    def name(self, node):
+        return self.names[id(node)]
+
+    def put(self, text):
+        self.lines.append('    ' * self.depth + text)
+
+    def fresh(self, node):
+        n = 'e' + str(self.counter)
+        self.counter += 1
+        self.names[id(node)] = n
+        return n
+
+    def block(self, block):
+        for node in block.nodes:
+            self.node(node)
+
+    def node(self, node):
+        k = node.kind
+        if k == 'input':
+            self.names[id(node)] = 'in' + str(node.attr['io_index'])
+        elif k == 'output':
+            self.names[id(node)] = 'out' + str(node.attr['io_index'])
+        elif k == 'const':
+            self.names[id(node)] = literal(node.attr['value'])
+        elif k == 'const_tensor':
+            self.names[id(node)] = '{' + ', '.join(literal(v) for v in node.to_array().tolist()) + '}'
+        elif k == 'position':
+            self.names[id(node)] = 'position'
+            if self.position_text is not None:
+                self.put(self.position_text)
+        elif k == 'variable' or k == 'cast':
+            n = self.fresh(node)
+            self.put(ctype(node.dtype) + ' ' + n + ' = ' + self.name(node.args[0]) + ';')
+        elif k == 'local':
+            n = self.fresh(node)
+            self.put(ctype(node.dtype) + ' ' + n + '[' + str(node.size) + '] = ' + self.name(node.args[0]) + ';')
+        elif k == 'assign_var':
+            self.put(self.name(node.args[0]) + ' = ' + self.name(node.args[1]) + ';')
+        elif k == 'assign_tensor':
+            if id(node) in self.write_subst:
+                self.put(self.write_subst[id(node)] % self.name(node.args[2]))
+            else:
+                self.put(self.name(node.args[0]) + '[' + self.name(node.args[1]) + '] = ' +
+                         self.name(node.args[2]) + ';')
+        elif k == 'read':
+            n = self.fresh(node)
+            if id(node) in self.read_subst:
+                self.put(ctype(node.dtype) + ' ' + n + ' = ' + self.read_subst[id(node)] + ';')
+            else:
+                self.put(ctype(node.dtype) + ' ' + n + ' = ' + self.name(node.args[0]) + '[' +
+                         self.name(node.args[1]) + '];')
+        elif k == 'limit':
+            self.names[id(node)] = _LIMITS[(node.attr['which'], node.dtype.name)]
+        elif k == 'unary':
+            fn, t = node.attr['fn'], node.dtype.name
+            x = self.name(node.args[0])
+            if fn == 'negate':
+                rhs = '-(' + x + ')'
+            elif fn == 'not':
+                rhs = '!(' + x + ')'
+            elif fn in ('isinf', 'isfinite', 'isnan'):
+                # the host's std::isinf & co. return bool; CUDA's may return any non-zero int
+                rhs = '(' + fn + '(' + x + ') ? 1 : 0)'
+            elif fn == 'abs' and t in _ABS_INT:
+                rhs = _ABS_INT[t] + '(' + x + ')'
+            else:
+                rhs = (_UNARY_F32 if t == 'float32' else _UNARY_F64)[fn] + '(' + x + ')'
+            n = self.fresh(node)
+            self.put(ctype(node.dtype) + ' ' + n + ' = ' + rhs + ';')
+        elif k == 'binary':
+            fn, t = node.attr['fn'], node.dtype.name
+            x, y = self.name(node.args[0]), self.name(node.args[1])
+            if fn == 'min':
+                rhs = '(((' + x + ')<(' + y + '))?(' + x + '):(' + y + '))'
+            elif fn == 'max':
+                rhs = '(((' + x + ')>(' + y + '))?(' + x + '):(' + y + '))'
+            elif fn == 'pow':
+                rhs = ('powf(' if t == 'float32' else 'pow(') + x + ',' + y + ')'
+            elif fn == 'atan2':
+                rhs = ('atan2f(' if t == 'float32' else 'atan2(') + x + ',' + y + ')'
+            elif fn == 'mod' and t == 'float32':
+                rhs = 'fmodf(' + x + ',' + y + ')'
+            elif fn == 'mod' and t == 'float64':
+                rhs = 'fmod(' + x + ',' + y + ')'
+            else:
+                rhs = '(' + x + ' ' + _INFIX[fn] + ' ' + y + ')'
+            n = self.fresh(node)
+            self.put(ctype(node.dtype) + ' ' + n + ' = ' + rhs + ';')
+        elif k == 'for':
+            i, a, b, s = [self.name(x) for x in node.args]
+            self.put('for(' + i + ' = ' + a + '; ((' + i + ' < ' + b + ')&&(' + s + '>0)) || ((' + i + ' > ' + b +
+                     ')&&(' + s + '<0)); ' + i + '+=' + s + '){')
+            self.depth += 1
+            self.block(node.body)
+            self.depth -= 1
+            self.put('}')
+        elif k == 'if':
+            for bi, (cond, blk) in enumerate(zip(node.conds, node.blocks)):
+                if bi == 0:
+                    self.put('if(' + self.name(cond) + '){')
+                elif cond is not None:
+                    self.put('}')
+                    self.put('else if(' + self.name(cond) + '){')
+                else:
+                    self.put('}')
+                    self.put('else{')
+                self.depth += 1
+                self.block(blk)
+                self.depth -= 1
+            self.put('}')
+        else:
+            raise NotImplementedError(k)
+
+
+def _strides(shape):
+    blocks = [1]
+    for d in range(len(shape) - 1, 0, -1):
+        blocks.append(blocks[-1] * shape[d])
+    blocks.reverse()
+    return blocks
+
+
+def _position_values(shape, widx):
+    """C expressions of the position entries of worker ``widx`` (opveclib/expression.py:1293-1306)."""
+    vals, rem = [], widx
+    for b in _strides(shape):
+        vals.append('(uint32_t)((' + rem + ')/' + str(b) + 'u)')
+        rem = '(' + rem + ') % ' + str(b) + 'u'
+    return vals
+
+
+def _params(kernel):
+    params = []
+    for n in kernel.inputs:
+        params.append('const ' + ctype(n.dtype) + '* __restrict__ in' + str(n.attr['io_index']))
+    for n in kernel.outputs:
+        params.append(ctype(n.dtype) + '* __restrict__ out' + str(n.attr['io_index']))
+    return params
+
+
+def _is_injective(form, ranges):
+    """Do distinct positions give distinct offsets?  (mixed-radix test on the coefficients)"""
+    terms = sorted((abs(c), ranges[s][1] - ranges[s][0]) for s, c in form.coefs.items())
+    span = 0
+    for c, extent in terms:
+        if extent == 0:
+            continue
+        if c <= span:
+            return False
+        span += c * extent
+    return True
+
+
+class VecPlan(object):
+    """Which accesses of a kernel are hoisted into vector / uniform loads and vector stores."""
+
+    def __init__(self):
+        self.lanes = 0
+        self.read_slots = []    # (tensor node, form, mode 'vec'|'uni', [read nodes])
+        self.write_slots = []   # (tensor node, form, [assign nodes], conditional)
+
+    @property
+    def usable(self):
+        return self.lanes > 1 and (any(s[2] == 'vec' for s in self.read_slots) or self.write_slots)
+
+
+def plan_vectorisation(kernel, info=None):
+    info = info or analyze(kernel)
+    plan = VecPlan()
+    shape = kernel.workgroup_shape
+    last = len(shape) - 1
+    psym = ('p', last)
+    if shape[last] == 1:
+        return plan
+    io_nodes = [n for n in kernel.inputs + kernel.outputs]
+    if not io_nodes:
+        return plan
+
+    def candidate(acc):
+        f = acc.form
+        if f is None or f.mod is not None or acc.loop_depth > 0:
+            return None
+        if any(s[0] == 'l' for s in f.coefs):
+            return None
+        if acc.tensor.kind not in ('input', 'output'):
+            return None
+        lo, hi = f.bounds(info.ranges)
+        if lo < 0 or hi >= acc.tensor.size:
+            return None
+        c = f.coef(psym)
+        if c == 1:
+            return 'vec'
+        if c == 0 and not acc.is_write:
+            return 'uni'
+        return None
+
+    cands = [(acc, candidate(acc)) for acc in info.accesses]
+    widest = max([acc.tensor.dtype.itemsize for acc, mode in cands if mode == 'vec'] or [0])
+    if widest == 0:
+        return plan
+    lanes = max(1, 16 // widest)
+    while lanes > 1 and shape[last] % lanes != 0:
+        lanes //= 2
+    if lanes <= 1:
+        return plan
+
+    def aligned(f):
+        if f.const % lanes != 0:
+            return False
+        for s, c in f.coefs.items():
+            if s != psym and c % lanes != 0 and info.ranges[s][1] > 0:
+                return False
+        return True
+
+    reads, writes = {}, {}
+    for acc, mode in cands:
+        if mode is None:
+            continue
+        if mode == 'vec' and not aligned(acc.form):
+            continue
+        key = (id(acc.tensor), acc.form.key())
+        if acc.is_write:
+            writes.setdefault(key, [acc.tensor, acc.form, [], False])
+            writes[key][2].append(acc.node)
+            if acc.cond_depth > 0:
+                writes[key][3] = True
+        else:
+            reads.setdefault(key, [acc.tensor, acc.form, mode, []])
+            reads[key][3].append(acc.node)
+
+    # a conditional store may only be widened to the whole group when no other worker and no other statement
+    # can target the elements a skipped lane would have written
+    slots_per_tensor = {}
+    for acc in info.accesses:
+        if acc.is_write and acc.tensor.kind == 'output':
+            k = acc.form.key() if acc.form is not None else ('?', id(acc.node))
+            slots_per_tensor.setdefault(id(acc.tensor), set()).add(k)
+    for key, slot in list(writes.items()):
+        if slot[3]:
+            if len(slots_per_tensor[id(slot[0])]) != 1 or not _is_injective(slot[1], info.ranges):
+                del writes[key]
+
+    plan.lanes = lanes
+    plan.read_slots = [tuple(v) for v in reads.values()]
+    plan.write_slots = [tuple(v) for v in writes.values()]
+    return plan
+
+
+def _address_expr(form, shape):
+    """C expression (uint64) of an affine offset at the group's first worker, from ``p<d>`` position names."""
+    terms = []
+    if form.const:
+        terms.append(str(form.const) + 'ull')
+    for (kind, d), c in sorted(form.coefs.items()):
+        terms.append('(uint64_t)p' + str(d) + ('' if c == 1 else ' * ' + str(c) + 'ull'))
+    return ' + '.join(terms) if terms else '0ull'
+
+
+def emit_cuda(kernel, name):
+    """Full ``.cu`` text for one kernel plus its launch metadata.
+
+    Returns (source, meta) with meta = {'gen': {...}, 'vec': {...} or None}; each entry has the symbol name, the
+    block size and the number of loop iterations the grid should cover."""
+    info = analyze(kernel)
+    shape = kernel.workgroup_shape
+    W = kernel.num_workers
+    widx_t = 'uint32_t' if W < 2 ** 31 else 'uint64_t'
+    params = ', '.join(_params(kernel))
+    src = ['// generated by opveclib_b200 (' + TEMPLATE_VERSION + ') for kernel ' + kernel.name,
+           '#include "ovl_common.cuh"', '']
+
+    # ---- generic kernel
+    pos_text = 'const uint32_t position[' + str(len(shape)) + '] = {' + \
+        ', '.join(_position_values(shape, 'worker_index')) + '};'
+    em = BodyEmitter(kernel, 2, position_text=pos_text)
+    em.block(kernel.body)
+    src += ['extern "C" __global__ void __launch_bounds__(' + str(BLOCK_THREADS) + ') ' + name + '_gen(' + params +
+            ') {',
+            '    const ' + widx_t + ' ovl_stride = (' + widx_t + ')gridDim.x * ' + str(BLOCK_THREADS) + 'u;',
+            '    for (' + widx_t + ' worker_index = (' + widx_t + ')blockIdx.x * ' + str(BLOCK_THREADS) +
+            'u + threadIdx.x; worker_index < ' + str(W) + 'ull; worker_index += ovl_stride) {'] + em.lines + \
+           ['    }', '}', '']
+    meta = {'gen': {'symbol': name + '_gen', 'block': BLOCK_THREADS, 'items': W}, 'vec': None, 'scan': None}
+
+    # ---- vectorised kernel
+    plan = plan_vectorisation(kernel, info)
+    if plan.usable:
+        L = plan.lanes
+        groups = W // L
+        last = len(shape) - 1
+        read_subst, write_subst = {}, {}
+        pre, post = [], []
+        aligned_tensors = set()
+        for si, (tensor, form, mode, nodes) in enumerate(plan.read_slots):
+            t = ctype(tensor.dtype)
+            tname = 'in' + str(tensor.attr['io_index'])
+            if mode == 'vec':
+                pre.append('const ovl::Vec<' + t + ', ' + str(L) + '> rv' + str(si) + ' = ovl::load_vec<' + t + ', ' +
+                           str(L) + '>(' + tname + ' + (' + _address_expr(form, shape) + '));')
+                for n in nodes:
+                    read_subst[id(n)] = 'rv' + str(si) + '.v[ovl_lane]'
+                aligned_tensors.add(('in', tensor.attr['io_index']))
+            else:
+                pre.append('const ' + t + ' ru' + str(si) + ' = *(' + tname + ' + (' +
+                           _address_expr(form, shape) + '));')
+                for n in nodes:
+                    read_subst[id(n)] = 'ru' + str(si)
+        for si, (tensor, form, nodes, conditional) in enumerate(plan.write_slots):
+            t = ctype(tensor.dtype)
+            tname = 'out' + str(tensor.attr['io_index'])
+            pre.append('ovl::Vec<' + t + ', ' + str(L) + '> wv' + str(si) + ';')
+            if conditional:
+                pre.append('#pragma unroll')
+                pre.append('for (int i = 0; i < ' + str(L) + '; ++i) wv' + str(si) + '.v[i] = 0;')
+            for n in nodes:
+                write_subst[id(n)] = 'wv' + str(si) + '.v[ovl_lane] = %s;'
+            post.append('ovl::store_vec<' + t + ', ' + str(L) + '>(' + tname + ' + (' + _address_expr(form, shape) +
+                        '), wv' + str(si) + ');')
+            aligned_tensors.add(('out', tensor.attr['io_index']))
+        pvals = _position_values(shape, 'ovl_w0')
+        pos_decl = ['const uint32_t p' + str(d) + ' = ' + v + ';' for d, v in enumerate(pvals)]
+        lane_pos = 'const uint32_t position[' + str(len(shape)) + '] = {' + ', '.join(
+            ['p' + str(d) for d in range(last)] + ['p' + str(last) + ' + (uint32_t)ovl_lane']) + '};'
+        em = BodyEmitter(kernel, 3, read_subst, write_subst, position_text=lane_pos)
+        em.block(kernel.body)
+        ind = '        '
+        src += ['extern "C" __global__ void __launch_bounds__(' + str(BLOCK_THREADS) + ') ' + name + '_vec(' +
+                params + ') {',
+                '    const ' + widx_t + ' ovl_stride = (' + widx_t + ')gridDim.x * ' + str(BLOCK_THREADS) + 'u;',
+                '    for (' + widx_t + ' ovl_g = (' + widx_t + ')blockIdx.x * ' + str(BLOCK_THREADS) +
+                'u + threadIdx.x; ovl_g < ' + str(groups) + 'ull; ovl_g += ovl_stride) {',
+                ind + 'const ' + widx_t + ' ovl_w0 = ovl_g * ' + str(L) + 'u;'] + \
+            [ind + l for l in pos_decl] + [ind + l for l in pre] + \
+            [ind + '#pragma unroll', ind + 'for (int ovl_lane = 0; ovl_lane < ' + str(L) + '; ++ovl_lane) {',
+             ind + '    const ' + widx_t + ' worker_index = ovl_w0 + ovl_lane; (void)worker_index;'] + \
+            em.lines + [ind + '}'] + [ind + l for l in post] + ['    }', '}', '']
+        meta['vec'] = {'symbol': name + '_vec', 'block': BLOCK_THREADS, 'items': groups, 'lanes': L,
+                       'aligned': sorted(aligned_tensors)}
+    # ---- cooperative scan
+    spec = patterns.match_scan(kernel, info)
+    if spec is not None and spec.n >= patterns.SCAN_MIN_AXIS:
+        src.insert(2, '#include "ovl_scan.cuh"')
+        t = ctype(spec.dtype)
+        acc = 'double' if spec.dtype.is_float else t
+        acc_size = 8 if spec.dtype.is_float else spec.dtype.itemsize
+        vec = max(1, min(4, 16 // spec.dtype.itemsize))
+        tile = SCAN_BLOCK * SCAN_VPT * vec
+        tiles = ((spec.n + tile - 1) // tile) * spec.lines
+        desc = 32 if acc_size == 8 else 16
+        scratch = SCAN_HEADER_BYTES + tiles * desc
+        op = 'ovl::OpAdd' if spec.op == 'add' else 'ovl::OpMul'
+        can_align = spec.lines == 1 or spec.n % vec == 0
+        variants = [('scanu', 'false')] + ([('scan', 'true')] if can_align else [])
+        for suffix, aligned in variants:
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(SCAN_BLOCK) + ') ' + name + '_' + suffix +
+                    '(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0, void* scratch) {',
+                    '    ovl::scan_lines<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned +
+                    ', false>(in0, out0, nullptr, ' + str(spec.lines) + 'ull, ' + str(spec.n) + 'ull, scratch);',
+                    '}', '']
+        meta['scan'] = {'symbol': name + '_scan' if can_align else None, 'symbol_unaligned': name + '_scanu',
+                        'block': SCAN_BLOCK, 'tiles': tiles, 'scratch_bytes': scratch, 'zero_bytes': scratch,
+                        'align_bytes': vec * spec.dtype.itemsize, 'lines': spec.lines, 'n': spec.n, 'op': spec.op}
+    return '\n'.join(src), meta

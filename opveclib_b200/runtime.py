@@ -1,0 +1,259 @@
+"""Evaluation of operator graphs on a B200: ``evaluate`` / ``profile`` with ``target_language='b200'``.
+
+Counterpart of the reference's standalone runtime (opveclib/operator.py:2099-2335): build the operator graph of
+the requested outputs, fuse it when ``opt_level >= 3``, compile each kernel (cached), and run the kernels in
+dependency order.  Differences by design: tensors live in device memory owned by torch, kernels are launched
+through the C-ABI launcher on torch's current stream, intermediates are released after their last use (the
+reference keeps them all, operator.py:2329), and there is no CPU target - if the launcher library or a GPU is
+missing the call fails.
+"""
+import os
+
+import numpy as np
+
+from . import compiler, launcher
+from .fuse import merge_op_dag
+from .local import logger
+from .opgraph import build_op_dag
+
+_programs = {}
+_DRYRUN = 'OVL_B200_DRYRUN'
+
+
+def _torch():
+    import torch
+    return torch
+
+
+class KernelPlan(object):
+    """A compiled kernel with its launchable variants (generic / vectorised / scan), created on first use."""
+
+    def __init__(self, kernel):
+        self.kernel = kernel
+        self.cubin, self.meta = compiler.compile_kernel(kernel)
+        self.name = self.meta['name']
+        self.in_types = kernel.input_types
+        self.out_types = kernel.output_types
+        self._modules = {}
+        self._variants = {}
+        self._scratch = {}
+        self._sms = {}
+        self.last_variant = None
+        self.launches = 0
+
+    def _module(self, device):
+        if device not in self._modules:
+            self._modules[device] = launcher.Module(self.cubin)
+        return self._modules[device]
+
+    def _sm_count(self, device):
+        if device not in self._sms:
+            self._sms[device] = _torch().cuda.get_device_properties(device).multi_processor_count
+        return self._sms[device]
+
+    def _variant(self, which, device):
+        key = (which, device)
+        if key in self._variants:
+            return self._variants[key]
+        meta = self.meta
+        dtypes = [t.dtype.code for t in self.in_types + self.out_types]
+        lens = [t.size for t in self.in_types + self.out_types]
+        n_in = len(self.in_types)
+        sms = self._sm_count(device)
+        aligns = [0] * len(dtypes)
+        scratch = zero = 0
+        if which in ('gen', 'vec'):
+            m = meta[which]
+            block = m['block']
+            grid = max(1, min((m['items'] + block - 1) // block, sms * (2048 // block)))
+            symbol = m['symbol']
+            if which == 'vec':
+                for kind, idx in m['aligned']:
+                    aligns[idx if kind == 'in' else n_in + idx] = 16
+        else:
+            m = meta['scan']
+            block = m['block']
+            grid = max(1, min(m['tiles'], sms * 8))
+            symbol = m['symbol'] if which == 'scan' else m['symbol_unaligned']
+            scratch, zero = m['scratch_bytes'], m['zero_bytes']
+            if which == 'scan':
+                aligns = [m['align_bytes']] * len(dtypes)
+        k = launcher.Kernel(self._module(device), symbol, grid, block, dtypes, lens, n_in, aligns, scratch, zero)
+        self._variants[key] = k
+        return k
+
+    def choose(self, in_ptrs, out_ptrs):
+        meta = self.meta
+        if meta.get('scan'):
+            al = meta['scan']['align_bytes']
+            if meta['scan']['symbol'] and all(p % al == 0 for p in in_ptrs + out_ptrs):
+                return 'scan'
+            return 'scanu'
+        if meta.get('vec'):
+            ok = True
+            for kind, idx in meta['vec']['aligned']:
+                p = in_ptrs[idx] if kind == 'in' else out_ptrs[idx]
+                if p % 16 != 0:
+                    ok = False
+            if ok:
+                return 'vec'
+        return 'gen'
+
+    def launch(self, ins, outs, stream_ptr, device, iterations=None):
+        """ins/outs: torch CUDA tensors.  Enqueues one launch (or ``iterations`` timed launches, returning the
+        milliseconds of each)."""
+        torch = _torch()
+        in_ptrs = [t.data_ptr() for t in ins]
+        out_ptrs = [t.data_ptr() for t in outs]
+        which = self.choose(in_ptrs, out_ptrs)
+        k = self._variant(which, device)
+        self.last_variant = which
+        in_arr = launcher.tensor_array([(p, t.dtype.code, t.size) for p, t in zip(in_ptrs, self.in_types)])
+        out_arr = launcher.tensor_array([(p, t.dtype.code, t.size) for p, t in zip(out_ptrs, self.out_types)])
+        scratch_ptr, scratch_bytes = None, 0
+        if k.scratch_bytes:
+            key = (device, stream_ptr)
+            buf = self._scratch.get(key)
+            if buf is None or buf.numel() < k.scratch_bytes:
+                buf = torch.empty(k.scratch_bytes, dtype=torch.uint8, device='cuda:%d' % device)
+                self._scratch[key] = buf
+            scratch_ptr, scratch_bytes = buf.data_ptr(), buf.numel()
+        if iterations is None:
+            st = k.launch(in_arr, len(ins), out_arr, len(outs), scratch_ptr, scratch_bytes, stream_ptr)
+            launcher.check(st, 'launching ' + self.kernel.name)
+            self.launches += 1
+            return None
+        st, ms = k.profile(in_arr, len(ins), out_arr, len(outs), scratch_ptr, scratch_bytes, stream_ptr, iterations)
+        launcher.check(st, 'profiling ' + self.kernel.name)
+        self.launches += iterations
+        return ms
+
+    def check_status(self, stream_ptr, device):
+        """Raise if a bounded device-side wait of this kernel expired (scan kernels only)."""
+        buf = self._scratch.get((device, stream_ptr))
+        if buf is None:
+            return
+        import ctypes
+        status = ctypes.c_int32(0)
+        launcher.check(launcher.library().ovl_read_kernel_status(buf.data_ptr(), stream_ptr, ctypes.byref(status)),
+                       'reading kernel status')
+        if status.value != 0:
+            raise launcher.OvlError(status.value, 'kernel ' + self.kernel.name)
+
+
+class Program(object):
+    """A compiled operator graph: kernel plans in launch order plus the wiring between them."""
+
+    def __init__(self, dag):
+        self.dag = dag
+        self.plans = [KernelPlan(k) for k in dag.kernels]
+        # last consumer of every intermediate, so its memory can be released early
+        self.last_use = {}
+        for op_index, refs in enumerate(dag.references):
+            for r in refs:
+                if not r.is_leaf:
+                    self.last_use[(r.op_index, r.op_output_index)] = op_index
+        self.keep = set(dag.outputs)
+
+    def run(self, leaf_tensors, device, stream_ptr, iterations=None, out_buffers=None):
+        """leaf_tensors: torch CUDA tensors for the graph inputs.  Returns (outputs, {name: ms list})."""
+        torch = _torch()
+        buffers = {}
+        times = {}
+        for op_index, plan in enumerate(self.plans):
+            ins = []
+            for r in self.dag.references[op_index]:
+                ins.append(leaf_tensors[r.dag_input_index] if r.is_leaf else buffers[(r.op_index, r.op_output_index)])
+            outs = []
+            for k, t in enumerate(plan.out_types):
+                preset = None
+                if out_buffers is not None and (op_index, k) in self.keep:
+                    preset = out_buffers[self.dag.outputs.index((op_index, k))]
+                if preset is None:
+                    preset = torch.empty(t.shape, dtype=t.dtype.as_torch(), device='cuda:%d' % device)
+                outs.append(preset)
+                buffers[(op_index, k)] = preset
+            ms = plan.launch(ins, outs, stream_ptr, device, iterations)
+            if ms is not None:
+                times[plan.name] = np.array(ms, dtype=np.float64)
+            for key in [key for key, last in self.last_use.items() if last == op_index and key not in self.keep]:
+                buffers.pop(key, None)
+        return [buffers[o] for o in self.dag.outputs], times
+
+    def check_status(self, device, stream_ptr):
+        for plan in self.plans:
+            if plan.meta.get('scan'):
+                plan.check_status(stream_ptr, device)
+
+
+def compile_outputs(output_list, opt_level=3):
+    """Build, fuse and compile the operator graph behind ``output_list``; cached by graph structure."""
+    if not isinstance(output_list, (list, tuple)):
+        output_list = [output_list]
+    dag = build_op_dag(*output_list)
+    key = (dag.text(), opt_level >= 3)
+    prog = _programs.get(key)
+    if prog is None:
+        fused = merge_op_dag(dag) if opt_level >= 3 else dag
+        prog = Program(fused)
+        _programs[key] = prog
+    return prog, dag
+
+
+def _is_torch(x):
+    return type(x).__module__.startswith('torch')
+
+
+def profile(output_list, target_language='b200', profiling_iterations=1, opt_level=3):
+    """Evaluate operator outputs.  Returns (list of results, {kernel name: ms per iteration}).
+
+    Leaf inputs may be numpy arrays (staged to the device and results copied back, as the reference harness
+    does at opveclib/testcudaop.cc:84-183, 306-379) or torch tensors; with any torch CUDA input the results stay
+    on the device as torch tensors."""
+    if target_language not in ('b200', 'cuda'):
+        raise ValueError('Unsupported target_language: ' + str(target_language) +
+                         " (this backend runs on the GPU only: use 'b200')")
+    if not isinstance(profiling_iterations, int) or profiling_iterations < 1:
+        raise ValueError('profiling_iterations must be a positive int')
+    prog, dag = compile_outputs(output_list, opt_level)
+    if os.environ.get(_DRYRUN):
+        # cache-warming mode for machines without a GPU: everything is compiled, nothing is launched
+        return [np.zeros(dag.kernels[o].output_types[k].shape, dtype=dag.kernels[o].output_types[k].dtype.as_numpy())
+                for o, k in dag.outputs], {}
+    torch = _torch()
+    if not torch.cuda.is_available():
+        raise RuntimeError('opveclib_b200 needs a CUDA device: there is no CPU execution path')
+    device = torch.cuda.current_device()
+    any_cuda_input = False
+    leaves = []
+    for x, t in zip(dag.inputs, dag.input_types):
+        if _is_torch(x):
+            if x.is_cuda:
+                any_cuda_input = True
+                device = x.device.index
+            leaves.append(x)
+        else:
+            leaves.append(torch.from_numpy(np.ascontiguousarray(x)))
+    dev = 'cuda:%d' % device
+    with torch.cuda.device(device):
+        stream_ptr = torch.cuda.current_stream().cuda_stream
+        staged = [x.contiguous() if x.is_cuda else x.to(dev, non_blocking=True) for x in leaves]
+        if profiling_iterations == 1 and not logger.isEnabledFor(10):
+            outs, times = prog.run(staged, device, stream_ptr, None)
+            for plan in prog.plans:
+                times[plan.name] = np.array([np.nan])
+        else:
+            outs, times = prog.run(staged, device, stream_ptr, profiling_iterations)
+        if any_cuda_input:
+            prog.check_status(device, stream_ptr)
+            return outs, times
+        host = [o.cpu().numpy() for o in outs]
+        prog.check_status(device, stream_ptr)
+    return host, times
+
+
+def evaluate(output_list, target_language='b200', opt_level=3):
+    """Evaluate operator outputs on the GPU; a single output comes back bare, several as a list
+    (opveclib/operator.py:2099-2117)."""
+    outs, _ = profile(output_list, target_language=target_language, profiling_iterations=1, opt_level=opt_level)
+    return outs[0] if len(outs) == 1 else outs

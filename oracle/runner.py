@@ -113,7 +113,11 @@ def profile(output_list, num_threads=0, iterations=1, flags='fast'):
     """Evaluate operator outputs on the CPU, unmerged.  Returns (arrays, {op position: ms per iteration})."""
     if not isinstance(output_list, (list, tuple)):
         output_list = [output_list]
-    dag = build_op_dag(*output_list)
+    return run_dag(build_op_dag(*output_list), num_threads, iterations, flags)
+
+
+def run_dag(dag, num_threads=0, iterations=1, flags='fast'):
+    """Run an operator graph (merged or not) operator by operator."""
     buffers, times = [], {}
     for op_index, kernel in enumerate(dag.kernels):
         cur_inputs = []
