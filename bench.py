@@ -1,0 +1,489 @@
+"""Benchmark of the hot path: fused OVL operator graphs on B200, next to the reference's CPU operator.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c2_cumsum|c2_cumprod|c1|c3|c5] [--impl reference]
+
+Default workload (the one the headline metric is quoted on): the 16-operator fused element-wise chain over an
+fp32 tensor [8, 2^27] drawn from uniform[-2, 2], rows sharded contiguously over N GPUs with no communication
+(total work fixed: strong scaling).  One step is one evaluation of the whole operator graph on the rank's rows.
+The other workloads exist for profiling single kernels; `c5` is the scan across shard boundaries.
+
+Prints one JSON line (rank 0).  ``value`` is elements/s with inputs resident in HBM, timed with CUDA events on
+the launching stream, maximum over ranks; ``e2e`` is the same work through ``ovl.evaluate`` from pinned host
+arrays and back (host<->device copies inside the timed region); ``roofline`` relates the dominant kernel's
+algorithmic bytes per launch to the measured HBM copy bandwidth; ``cpu_baseline`` times the reference's own
+generated C++ operators (oracle/_ref, else the oracle port) on this machine's host cores over a bounded sample.
+``--impl reference`` runs only that CPU arm and prints it in the same format.
+"""
+import argparse
+import json
+import os
+import re
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, 'tests')):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import numpy as np  # noqa: E402
+
+C4_ROWS, C4_COLS = 8, 1 << 27
+C4_SAMPLE_COLS = 1 << 24          # CPU sample: one row of 2^24 elements (1/64 of the workload)
+C5_TOTAL = 1 << 31
+C5_SAMPLE = 1 << 26
+SEED = 1234
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+# ---------------------------------------------------------------------------------------------------------
+def measured_peak():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    try:
+        with open(path) as f:
+            return float(json.load(f)['hbm_gbs']), 'measured'
+    except Exception:
+        return FALLBACK_HBM_GBS, 'fallback'
+
+
+def profiled_traffic(workload, elements_per_launch):
+    """DRAM bytes per launch scaled from the committed ncu summary (bytes per element), or None."""
+    path = os.path.join(ROOT, 'profiles', workload + '_kernel.md')
+    try:
+        with open(path) as f:
+            m = re.search(r'dram_bytes_per_element:\s*([0-9.]+)', f.read())
+        return float(m.group(1)) * elements_per_launch if m else None
+    except Exception:
+        return None
+
+
+class ClockSampler(object):
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+              'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', '-i', str(self.gpu), '--query-gpu=' + self.FIELDS,
+                                          '--format=csv,noheader,nounits', '-lms', '100'], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, universal_newlines=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ['hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap']
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(',')]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith('active'):
+                    reasons.add(n)
+        busy = [c for c in sm if c > 0.5 * (mx or 1)] or sm
+        return {'sm_mhz': float(np.median(busy)) if busy else None, 'sm_max_mhz': mx, 'reasons': sorted(reasons),
+                'samples': len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------------------
+def dist_env():
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    return rank, world, local
+
+
+def build_graph(workload, rows_local=None, n_local=None):
+    """(operator outputs, input shapes, elements per step on this rank, algorithmic bytes per element)."""
+    import cases
+    ns = cases.impl()
+    f32 = np.float32
+    z = lambda *shape: np.zeros(shape, dtype=f32)     # noqa: E731  (only the type matters for tracing)
+    if workload == 'c4':
+        return [cases.chain16(ns, z(rows_local, C4_COLS))], rows_local * C4_COLS, 8
+    if workload == 'c2_cumsum':
+        return [ns.cumsum(z(4096, 8192), axis=1)], 4096 * 8192, 8
+    if workload == 'c2_cumprod':
+        return [ns.cumprod(z(4096, 8192), axis=1)], 4096 * 8192, 8
+    if workload == 'c1':
+        return [cases.c1_chain(ns, z(1 << 20))], 1 << 20, 8
+    if workload == 'c1_shift':
+        return [cases.user_ops(ns).shift_cyclic(z(1 << 20))], 1 << 20, 8
+    if workload == 'c3':
+        op = ns.lstm(z(512, 4096), z(512, 1024), forget_bias=0.0)
+        return [op[0], op[1]], 512 * 1024, 28
+    if workload == 'c3_grad':
+        op = ns.lstm_grad(z(512, 4096), z(512, 1024), z(512, 1024), z(512, 1024), forget_bias=0.0)
+        return [op[0], op[1]], 512 * 1024, 48
+    raise ValueError('unknown workload ' + workload)
+
+
+def precompile():
+    """Compile the kernels of every benchmark workload (no GPU needed)."""
+    from opveclib_b200 import runtime
+    for n in (1, 2, 4, 8):
+        runtime.compile_outputs(build_graph('c4', rows_local=C4_ROWS // n)[0])
+    for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad'):
+        runtime.compile_outputs(build_graph(w)[0])
+
+
+def input_distribution(workload, index):
+    if workload == 'c4':
+        return ('uniform', -2.0, 2.0)
+    if workload == 'c2_cumprod':
+        return ('uniform', 0.99, 1.01)
+    if workload in ('c1', 'c1_shift'):
+        return ('uniform', -1.0, 1.0)
+    if workload == 'c3_grad' and index >= 2:
+        return ('normal', 0.0, 0.1)
+    return ('normal', 0.0, 1.0)
+
+
+def make_device_inputs(torch, workload, types, device, seed):
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    out = []
+    for i, t in enumerate(types):
+        kind, a, b = input_distribution(workload, i)
+        x = torch.empty(t.shape, dtype=torch.float32, device=device)
+        if kind == 'uniform':
+            x.uniform_(a, b, generator=gen)
+        else:
+            x.normal_(a, b, generator=gen)
+        out.append(x)
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+def cpu_reference_run(workload, iterations):
+    """Time the reference's CPU implementation on a bounded sample.  Returns a dict for ``cpu_baseline``."""
+    from oracle import ref_runner, runner
+    import cases
+    rs = np.random.RandomState(SEED)
+    if workload == 'c4':
+        name, shape, sample = 'c4_chain16_1x%d' % C4_SAMPLE_COLS, (1, C4_SAMPLE_COLS), \
+            'one row slice [1, 2^24] of the [8, 2^27] tensor (1/64 of a step)'
+        inputs = [rs.uniform(-2, 2, shape).astype(np.float32)]
+        elements = C4_SAMPLE_COLS
+    elif workload == 'c5':
+        name, shape, sample = 'c5_cumsum_%d' % C5_SAMPLE, (C5_SAMPLE,), 'first 2^26 of 2^31 elements (1/32 of a step)'
+        inputs = [rs.normal(0, 1, shape).astype(np.float32)]
+        elements = C5_SAMPLE
+    else:
+        table = {'c2_cumsum': 'c2_cumsum_4096x8192', 'c2_cumprod': 'c2_cumprod_4096x8192', 'c1': 'c1_chain_1048576',
+                 'c1_shift': 'c1_shift_1048576', 'c3': 'c3_lstm_512x1024', 'c3_grad': 'c3_lstm_grad_512x1024'}
+        name, sample = table[workload], 'the full workload'
+        outs, elements, _ = build_graph(workload)
+        from opveclib_b200.opgraph import build_op_dag
+        types = build_op_dag(*outs).input_types
+        inputs = []
+        for i, t in enumerate(types):
+            kind, a, b = input_distribution(workload, i)
+            inputs.append((rs.uniform(a, b, t.shape) if kind == 'uniform' else rs.normal(a, b, t.shape)).astype(np.float32))
+    if ref_runner.available(name):
+        threads = ref_runner.hardware_threads()
+        _, ms = ref_runner.run(name, inputs, num_threads=0, variant='opt', iterations=iterations)
+        _, ms_ref = ref_runner.run(name, inputs, num_threads=0, variant='ref', iterations=1)
+        kind = 'reference'
+        extra = {'ms_reference_flags': float(ms_ref.min()), 'ops_after_reference_merge':
+                 len(ref_runner.manifest()[name]['ops'])}
+    else:
+        # the oracle port: same generated arithmetic from this repository's restatement of the generator
+        ns = cases.impl()
+        if workload == 'c4':
+            outs = [cases.chain16(ns, inputs[0])]
+        elif workload == 'c5':
+            outs = [ns.cumsum(inputs[0])]
+        else:
+            raise RuntimeError('oracle/_ref is missing and no port is wired for ' + workload)
+        threads = runner.hardware_threads()
+        _, times = runner.profile(outs, num_threads=0, iterations=iterations)
+        ms = sum(times.values())
+        kind, extra = 'port', {}
+    single_threaded = workload == 'c5'   # a rank-1 accumulate is one worker (test_accumulate.py:40-41)
+    best = float(np.min(ms))
+    res = {'value': elements / (best * 1e-3), 'unit': 'elements/s', 'cores': 1 if single_threaded else threads,
+           'kind': kind, 'sample': sample, 'ms_per_sample': best, 'build': '-O2 -ffp-contract=off'}
+    res.update(extra)
+    return res, elements
+
+
+def run_reference_arm(args, workload):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return 0
+    t0 = time.time()
+    base, elements = cpu_reference_run(workload, max(1, args.warmup))   # warm-up passes
+    res, elements = cpu_reference_run(workload, max(1, args.steps))
+    line = {
+        'impl': 'reference', 'metric': 'fused-op elements/s', 'value': res['value'], 'unit': 'elements/s',
+        'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': res['ms_per_sample'],
+        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+        'config': workload_config(workload, args.gpus), 'cpu_baseline': res,
+        'e2e': {'value': res['value'], 'unit': 'elements/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0, 'wall_s': time.time() - t0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def workload_config(workload, n):
+    names = {
+        'c4': 'fused 16-op element-wise chain, fp32 [8, 2^27] uniform[-2,2], rows sharded over the GPUs',
+        'c2_cumsum': 'cumsum along axis 1, fp32 [4096, 8192] normal(0,1)',
+        'c2_cumprod': 'cumprod along axis 1, fp32 [4096, 8192] uniform[0.99,1.01]',
+        'c1': 'fused chain expm1(log1p(|x|))*0.5+x, fp32 [2^20] uniform[-1,1]',
+        'c1_shift': 'shift_cyclic by +1, fp32 [2^20]',
+        'c3': 'LSTM cell forward, gates fp32 [512, 4096], c [512, 1024]',
+        'c3_grad': 'LSTM cell gradient, gates fp32 [512, 4096], c/dc/dh [512, 1024]',
+        'c5': 'cumsum along the sharded axis, fp32 [2^31] normal(0,1), contiguous shards, fp64 carry exchange',
+    }
+    return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
+            'l2': 'inputs larger than L2 (126 MB)' if workload in ('c4', 'c5', 'c2_cumsum', 'c2_cumprod')
+            else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
+
+
+# ---------------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=20)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='b200')
+    ap.add_argument('--workload', default='c4')
+    ap.add_argument('--no-cpu', action='store_true', help='skip the CPU baseline leg')
+    ap.add_argument('--no-e2e', action='store_true', help='skip the end-to-end leg')
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl != 'reference':
+        args.warmup = 3
+    workload = args.workload
+    if args.impl == 'reference':
+        return run_reference_arm(args, workload)
+
+    import torch
+    import torch.distributed as dist
+    rank, world, local = dist_env()
+    if world != args.gpus:
+        # plain `python bench.py --gpus N` with N > 1: launch one process per GPU
+        if world == 1 and args.gpus > 1:
+            cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', '--nproc-per-node', str(args.gpus),
+                   '--master-addr', '127.0.0.1', '--master-port', str(29500 + os.getpid() % 1000), os.path.abspath(__file__)
+                   ] + sys.argv[1:]
+            return subprocess.call(cmd)
+        raise SystemExit('WORLD_SIZE does not match --gpus')
+    torch.cuda.set_device(local)
+    device = torch.device('cuda', local)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+
+    import opveclib_b200 as ovl
+    from opveclib_b200 import runtime, parallel
+    from opveclib_b200.opgraph import build_op_dag
+
+    stream_ptr = torch.cuda.current_stream().cuda_stream
+    flush = None
+    e2e = None
+    if workload == 'c5':
+        n_local = C5_TOTAL // world
+        scan = parallel.ShardedScan(n_local, 'add')
+        gen = torch.Generator(device=device)
+        gen.manual_seed(SEED + rank)
+        x = torch.empty(n_local, dtype=torch.float32, device=device).normal_(0, 1, generator=gen)
+        y = torch.empty_like(x)
+        elements_local, bytes_per_elem = n_local, 8
+
+        def step():
+            scan(x, out=y)
+        kernels_per_step = 1 if world == 1 else 2
+        finish = scan.check_status
+    else:
+        if workload != 'c4' and world > 1:
+            raise SystemExit('only c4 and c5 shard over several GPUs')
+        rows_local = C4_ROWS // world if workload == 'c4' else None
+        outs, elements_local, bytes_per_elem = build_graph(workload, rows_local=rows_local)
+        prog, dag = runtime.compile_outputs(outs)
+        ins = make_device_inputs(torch, workload, dag.input_types, device, SEED + rank)
+        out_bufs = [torch.empty(prog.plans[o].out_types[k].shape, dtype=torch.float32, device=device)
+                    for o, k in prog.dag.outputs]
+        small = sum(t.size * 4 for t in dag.input_types) < (256 << 20)
+        if small:
+            flush = torch.empty(192 << 20, dtype=torch.uint8, device=device)
+
+        def step():
+            prog.run(ins, local, stream_ptr, None, out_bufs)
+        kernels_per_step = len(prog.plans)
+
+        def finish():
+            prog.check_status(local, stream_ptr)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    finish()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    if flush is None:
+        start.record()
+        for _ in range(args.steps):
+            step()
+        stop.record()
+        barrier()
+        elapsed_ms = start.elapsed_time(stop)
+    else:
+        # L2-resident inputs: overwrite an L2-sized buffer between steps and time each step on its own
+        elapsed_ms = 0.0
+        for _ in range(args.steps):
+            flush.fill_(1)
+            start.record()
+            step()
+            stop.record()
+            stop.synchronize()
+            elapsed_ms += start.elapsed_time(stop)
+        barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    finish()
+    t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    elapsed_ms = float(t.item())
+    total_elements = elements_local * world
+    value = total_elements * args.steps / (elapsed_ms * 1e-3)
+
+    # ---- end to end through the public API: pinned host arrays in, pinned host arrays out
+    if not args.no_e2e and workload != 'c5':
+        host_in = [torch.empty(tuple(tt.shape), dtype=torch.float32, pin_memory=True) for tt in dag.input_types]
+        for h, d in zip(host_in, ins):
+            h.copy_(d)
+        host_out = [torch.empty(tuple(b.shape), dtype=torch.float32, pin_memory=True) for b in out_bufs]
+        np_in = [h.numpy() for h in host_in]
+        np_out = [h.numpy() for h in host_out]
+        graph = rebuild_with_inputs(workload, np_in, rows_local if workload == 'c4' else None)
+        e2e_steps = max(3, min(args.steps, 10))
+        ovl.evaluate(graph, target_language='b200', out=np_out)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            ovl.evaluate(graph, target_language='b200', out=np_out)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item())
+        e2e = {'value': total_elements * e2e_steps / dt, 'unit': 'elements/s',
+               'h2d_bytes_per_step': int(sum(a.nbytes for a in np_in)) * world,
+               'd2h_bytes_per_step': int(sum(a.nbytes for a in np_out)) * world, 'steps': e2e_steps,
+               'ms_per_step': dt / e2e_steps * 1e3, 'api': "ovl.evaluate(outputs, target_language='b200', out=pinned)"}
+    elif workload == 'c5' and not args.no_e2e:
+        host_in = torch.empty(n_local, dtype=torch.float32, pin_memory=True)
+        host_in.copy_(x)
+        host_out = torch.empty(n_local, dtype=torch.float32, pin_memory=True)
+        e2e_steps = 3
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            x.copy_(host_in, non_blocking=True)
+            scan(x, out=y)
+            host_out.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        tt = torch.tensor([dt], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        dt = float(tt.item())
+        e2e = {'value': total_elements * e2e_steps / dt, 'unit': 'elements/s', 'h2d_bytes_per_step': n_local * 4 * world,
+               'd2h_bytes_per_step': n_local * 4 * world, 'steps': e2e_steps, 'ms_per_step': dt / e2e_steps * 1e3,
+               'api': 'parallel.ShardedScan from/to pinned host tensors'}
+
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        launch_ms = elapsed_ms / args.steps
+        # the dominant kernel is the (single) fused kernel of a step; for c5 on several GPUs the reduction pass
+        # belongs to the same step, so the per-step bytes are reported against the per-step time
+        algo_bytes = bytes_per_elem * elements_local
+        achieved = algo_bytes / (launch_ms * 1e-3) / 1e9
+        line = {
+            'metric': 'fused-op elements/s', 'value': value, 'unit': 'elements/s', 'n_gpus': world,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': launch_ms, 'higher_is_better': True,
+            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
+            'config': workload_config(workload, world),
+            'effective_hbm_gbs': achieved * world, 'pct_of_8tbs_per_gpu': 100.0 * achieved / NOMINAL_HBM_GBS,
+            'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
+                         'peak_kind': peak_kind + ' HBM copy bandwidth', 'algorithmic_bytes_per_element': bytes_per_elem,
+                         'traffic': profiled_traffic(workload, elements_local)},
+            'clocks': clocks, 'e2e': e2e, 'gpu_launches': kernels_per_step * args.steps,
+        }
+        if world == 1 and not args.no_cpu:
+            try:
+                line['cpu_baseline'], _ = cpu_reference_run(workload, 3)
+            except Exception as exc:   # the baseline is a report, never a reason to lose the GPU number
+                line['cpu_baseline'] = {'error': '%s: %s' % (type(exc).__name__, exc)}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def rebuild_with_inputs(workload, np_inputs, rows_local):
+    """The workload's operator graph over concrete host arrays (the e2e leg evaluates real data)."""
+    import cases
+    ns = cases.impl()
+    if workload == 'c4':
+        return [cases.chain16(ns, np_inputs[0])]
+    if workload == 'c2_cumsum':
+        return [ns.cumsum(np_inputs[0], axis=1)]
+    if workload == 'c2_cumprod':
+        return [ns.cumprod(np_inputs[0], axis=1)]
+    if workload == 'c1':
+        return [cases.c1_chain(ns, np_inputs[0])]
+    if workload == 'c1_shift':
+        return [cases.user_ops(ns).shift_cyclic(np_inputs[0])]
+    if workload == 'c3':
+        op = ns.lstm(np_inputs[0], np_inputs[1], forget_bias=0.0)
+        return [op[0], op[1]]
+    if workload == 'c3_grad':
+        op = ns.lstm_grad(np_inputs[0], np_inputs[1], np_inputs[2], np_inputs[3], forget_bias=0.0)
+        return [op[0], op[1]]
+    raise ValueError(workload)
+
+
+if __name__ == '__main__':
+    sys.exit(main())

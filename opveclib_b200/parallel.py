@@ -1,0 +1,135 @@
+"""Single-box data parallelism: shard the leading axis over the ranks of a ``torch.distributed`` group.
+
+Workers of an operator are independent by construction (documentation/programming.rst:21 of the reference), so
+an element-wise or fused operator graph whose tensors all share the leading axis runs unchanged on each rank's
+slab - no communication.  The one exchange this backend knows is the carry of a scan that runs *along* the
+sharded axis (the reference has no multi-GPU support at all; its rank-1 ``accumulate`` is a single worker,
+opveclib/examples/test_accumulate.py:40-41):
+
+1. every rank reduces its shard to one fp64 total (read-only pass, built-in reduction kernel);
+2. the totals are all-gathered (8 bytes per rank, NCCL on GPUs, gloo in CPU tests) into local memory;
+3. every rank combines the totals of the ranks before it into its carry and runs the single-pass scan seeded
+   with that carry.
+
+Per element this moves 4 bytes in step 1 and 8 in step 3; with contiguous shards nothing cheaper exists, because
+a rank's carry depends on all data of the ranks before it.
+"""
+import ctypes
+
+import numpy as np
+
+from . import launcher
+
+
+def shard_bounds(length, rank, world_size):
+    """[begin, end) of ``rank``'s contiguous shard of an axis of ``length`` elements: the first
+    ``length % world_size`` ranks get one extra element."""
+    if not 0 <= rank < world_size:
+        raise ValueError('rank out of range')
+    base, extra = divmod(length, world_size)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def shard_leading_axis(array, rank, world_size):
+    """The rank's slab of ``array`` along axis 0 (a view)."""
+    begin, end = shard_bounds(array.shape[0], rank, world_size)
+    return array[begin:end]
+
+
+def exclusive_carry(totals, rank, op):
+    """Combine the shard totals of the ranks before ``rank`` left to right, in fp64."""
+    carry = np.float64(0.0 if op == 'add' else 1.0)
+    for r in range(rank):
+        carry = carry + np.float64(totals[r]) if op == 'add' else carry * np.float64(totals[r])
+    return carry
+
+
+def _op_code(op):
+    if op not in ('add', 'mul'):
+        raise ValueError("op must be 'add' or 'mul'")
+    return 0 if op == 'add' else 1
+
+
+class ShardedScan(object):
+    """Inclusive cumsum / cumprod of a rank-1 fp32 tensor split contiguously over the ranks of ``group``.
+
+    Buffers (scratch, totals) are allocated once per instance; ``__call__`` enqueues the three steps on torch's
+    current stream and returns the rank's part of the result."""
+
+    def __init__(self, shard_len, op='add', group=None, device=None):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.op = op
+        self.code = _op_code(op)
+        self.group = group
+        self.shard_len = int(shard_len)
+        self.distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        self.device = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+        lib = launcher.library()
+        self.lib = lib
+        self.scan_bytes = int(lib.ovl_scan_f32_scratch_bytes(1, self.shard_len))
+        self.reduce_bytes = int(lib.ovl_reduce_f32_scratch_bytes(self.shard_len))
+        self.scan_scratch = torch.empty(self.scan_bytes, dtype=torch.uint8, device=self.device)
+        self.reduce_scratch = torch.empty(self.reduce_bytes, dtype=torch.uint8, device=self.device)
+        self.total = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.totals = torch.zeros(self.world, dtype=torch.float64, device=self.device)
+        self.carry = torch.zeros(1, dtype=torch.float64, device=self.device)
+        # mask[r] = 1 for ranks before this one: the carry is a masked reduction of the gathered totals
+        self.before = torch.arange(self.world, device=self.device) < self.rank
+        self.launches = 0
+
+    def __call__(self, x, out=None):
+        torch = self.torch
+        if x.dtype != torch.float32 or x.dim() != 1 or x.numel() != self.shard_len or not x.is_contiguous():
+            raise ValueError('expected a contiguous rank-1 float32 tensor of %d elements' % self.shard_len)
+        if out is None:
+            out = torch.empty_like(x)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        carry_ptr = None
+        if self.world > 1:
+            launcher.check(self.lib.ovl_reduce_f32(self.code, x.data_ptr(), self.shard_len, self.total.data_ptr(),
+                                                   self.reduce_scratch.data_ptr(), self.reduce_bytes, stream),
+                           'shard reduction')
+            self.dist.all_gather_into_tensor(self.totals, self.total, group=self.group)
+            if self.op == 'add':
+                torch.sum(torch.where(self.before, self.totals, torch.zeros_like(self.totals)), dim=0, keepdim=True,
+                          out=self.carry)
+            else:
+                torch.prod(torch.where(self.before, self.totals, torch.ones_like(self.totals)), dim=0, keepdim=True,
+                           out=self.carry)
+            carry_ptr = self.carry.data_ptr()
+            self.launches += 1
+        launcher.check(self.lib.ovl_scan_f32(self.code, x.data_ptr(), out.data_ptr(), 1, self.shard_len, carry_ptr,
+                                             self.scan_scratch.data_ptr(), self.scan_bytes, stream), 'shard scan')
+        self.launches += 1
+        return out
+
+    def check_status(self):
+        """Raise if a bounded wait inside the scan kernel expired."""
+        status = ctypes.c_int32(0)
+        stream = self.torch.cuda.current_stream(self.device).cuda_stream
+        launcher.check(self.lib.ovl_read_kernel_status(self.scan_scratch.data_ptr(), stream, ctypes.byref(status)),
+                       'reading scan status')
+        if status.value != 0:
+            raise launcher.OvlError(status.value, 'sharded scan')
+
+
+def sharded_scan_host(shards, op='add'):
+    """Host-side statement of the three steps over a list of numpy shards (rank order); returns the list of
+    per-rank results.  Used by the CPU tests of the carry logic; the arithmetic mirrors the device path:
+    fp64 totals, fp64 carry, fp64 running value rounded to fp32 on store."""
+    totals = []
+    for s in shards:
+        s64 = s.astype(np.float64)
+        totals.append(np.sum(s64) if op == 'add' else np.prod(s64))
+    results = []
+    for r, s in enumerate(shards):
+        carry = exclusive_carry(totals, r, op)
+        s64 = s.astype(np.float64)
+        run = np.cumsum(s64) + carry if op == 'add' else np.cumprod(s64) * carry
+        results.append(run.astype(np.float32))
+    return results

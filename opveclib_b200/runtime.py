@@ -204,8 +204,11 @@ def _is_torch(x):
     return type(x).__module__.startswith('torch')
 
 
-def profile(output_list, target_language='b200', profiling_iterations=1, opt_level=3):
+def profile(output_list, target_language='b200', profiling_iterations=1, opt_level=3, out=None):
     """Evaluate operator outputs.  Returns (list of results, {kernel name: ms per iteration}).
+
+    ``out`` (extension): a list with one preallocated numpy array per requested output (pinned host memory
+    makes the copy back asynchronous and fast); results are written there instead of into fresh arrays.
 
     Leaf inputs may be numpy arrays (staged to the device and results copied back, as the reference harness
     does at opveclib/testcudaop.cc:84-183, 306-379) or torch tensors; with any torch CUDA input the results stay
@@ -247,13 +250,26 @@ def profile(output_list, target_language='b200', profiling_iterations=1, opt_lev
         if any_cuda_input:
             prog.check_status(device, stream_ptr)
             return outs, times
-        host = [o.cpu().numpy() for o in outs]
+        if out is not None:
+            if len(out) != len(outs):
+                raise ValueError('out must hold one array per requested output')
+            host = []
+            for dst, o in zip(out, outs):
+                if dst.shape != tuple(o.shape) or not dst.flags['C_CONTIGUOUS'] or \
+                        dst.dtype.name != str(o.dtype).replace('torch.', ''):
+                    raise ValueError('out array has the wrong shape, dtype or layout')
+                torch.from_numpy(dst).copy_(o, non_blocking=True)
+                host.append(dst)
+            torch.cuda.current_stream().synchronize()
+        else:
+            host = [o.cpu().numpy() for o in outs]
         prog.check_status(device, stream_ptr)
     return host, times
 
 
-def evaluate(output_list, target_language='b200', opt_level=3):
+def evaluate(output_list, target_language='b200', opt_level=3, out=None):
     """Evaluate operator outputs on the GPU; a single output comes back bare, several as a list
     (opveclib/operator.py:2099-2117)."""
-    outs, _ = profile(output_list, target_language=target_language, profiling_iterations=1, opt_level=opt_level)
+    outs, _ = profile(output_list, target_language=target_language, profiling_iterations=1, opt_level=opt_level,
+                      out=out)
     return outs[0] if len(outs) == 1 else outs
