@@ -134,6 +134,29 @@ uint64_t ovl_reduce_f32_scratch_bytes(uint64_t n);
 int ovl_reduce_f32(int op, const float* in, uint64_t n, double* out_total, void* scratch, uint64_t scratch_bytes,
                    void* cuda_stream);
 
+/* Allocation-free scan ----------------------------------------------------------------------------------- */
+/* Same scan as ovl_scan_f32, for hosts that may not allocate device memory: for example a plugin running inside
+ * an engine whose memory pool owns the whole GPU and forbids cudaMalloc from plugin code, or a latency-critical
+ * loop that cannot afford the device-wide synchronisation an allocation implies.  The caller passes only inputs
+ * and outputs; the tile descriptors live in a fixed array compiled into the library
+ * (OVL_SCAN_STATIC_SCRATCH_BYTES of device memory, held by every GPU that loads the library until the process
+ * exits).  This entry point has no counterpart in the reference.
+ *
+ *  - Limit: ovl_scan_f32_scratch_bytes(lines, n) must not exceed OVL_SCAN_STATIC_SCRATCH_BYTES (32767 tiles of
+ *    4096 elements, about 134 million fp32 elements in total); larger requests return OVL_ERR_TOO_LARGE.
+ *  - The first call on each device looks up the array's device address (with that device current); make that
+ *    first call before starting any stream capture.  No call allocates or frees memory.
+ *  - All calls share the one array, and it keeps whatever the previous call left in it: each call clears the part
+ *    it needs on `cuda_stream` before its kernel.  Two calls that can overlap on the GPU (different streams, no
+ *    dependency between them) race on the array; order them yourself.
+ *  - Errors of the bounded device-side waits are reported as for ovl_scan_f32; read them with
+ *    ovl_scan_f32_static_status() after the work on the stream has finished. */
+#define OVL_SCAN_STATIC_SCRATCH_BYTES (1u << 20)
+int ovl_scan_f32_static(int op, const float* in, float* out, uint64_t lines, uint64_t n, const double* carry,
+                        void* cuda_stream);
+/* Status word of the most recent ovl_scan_f32_static launch on the current device (synchronises the stream). */
+int ovl_scan_f32_static_status(void* cuda_stream, int32_t* out_status);
+
 #ifdef __cplusplus
 }
 #endif

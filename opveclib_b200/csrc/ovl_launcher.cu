@@ -8,6 +8,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -354,6 +355,62 @@ extern "C" int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines,
     OVL_CUDA(cudaMemsetAsync(scratch, 0, need, stream));
     if (op == 0) return launch_scan<ovl::OpAdd>(in, out, lines, n, carry, scratch, grid, aligned, stream);
     return launch_scan<ovl::OpMul>(in, out, lines, n, carry, scratch, grid, aligned, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant of ovl_scan_f32: the tile descriptors live in a file-scope device array instead of
+// caller-provided scratch, for hosts that are not allowed (or cannot afford) to allocate device memory.
+
+static __device__ __align__(256) unsigned char g_scan_static_scratch[OVL_SCAN_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the array on the current device.  In host code the array's name is only a handle for the
+// runtime, not an address a kernel could use; the address comes from cudaGetSymbolAddress, once per device.
+int static_scratch_address(void** out_ptr) {
+    int dev = 0;
+    OVL_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return OVL_ERR_INVALID;
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        OVL_CUDA(cudaGetSymbolAddress(&p, g_scan_static_scratch));
+        if (!p) return OVL_ERR_NULL;
+        g_static_ptr[dev] = p;
+    }
+    *out_ptr = g_static_ptr[dev];
+    return OVL_OK;
+}
+
+}  // namespace
+
+extern "C" int ovl_scan_f32_static(int op, const float* in, float* out, uint64_t lines, uint64_t n, const double* carry,
+                                   void* cuda_stream) {
+    if (!in || !out) return OVL_ERR_NULL;
+    if (op != 0 && op != 1) return OVL_ERR_INVALID;
+    if (lines == 0 || n == 0) return OVL_ERR_INVALID;
+    if (carry && lines != 1) return OVL_ERR_INVALID;
+    // size check first, in a form that cannot overflow
+    const uint64_t tiles_per_line = (n + kTile - 1) / kTile;
+    const uint64_t max_tiles = (OVL_SCAN_STATIC_SCRATCH_BYTES - sizeof(ovl::ScanHeader)) / sizeof(ovl::TileDesc<double>);
+    if (tiles_per_line > max_tiles || lines > max_tiles / tiles_per_line) return OVL_ERR_TOO_LARGE;
+    void* scratch = nullptr;
+    int st = static_scratch_address(&scratch);
+    if (st != OVL_OK) return st;
+    // ovl_scan_f32 clears the part of the scratch this launch uses and enqueues the kernel; it allocates nothing
+    return ovl_scan_f32(op, in, out, lines, n, carry, scratch, OVL_SCAN_STATIC_SCRATCH_BYTES, cuda_stream);
+}
+
+extern "C" int ovl_scan_f32_static_status(void* cuda_stream, int32_t* out_status) {
+    if (!out_status) return OVL_ERR_NULL;
+    void* scratch = nullptr;
+    int st = static_scratch_address(&scratch);
+    if (st != OVL_OK) return st;
+    return ovl_read_kernel_status(scratch, cuda_stream, out_status);
 }
 
 extern "C" uint64_t ovl_reduce_f32_scratch_bytes(uint64_t n) {
