@@ -264,6 +264,8 @@ def workload_config(workload, n):
         'c3_grad': 'LSTM cell gradient, gates fp32 [512, 4096], c/dc/dh [512, 1024]',
         'c5': 'cumsum along the sharded axis, fp32 [2^31] normal(0,1), contiguous shards, fp64 carry exchange',
     }
+    if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
+        names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
             'l2': 'inputs larger than L2 (126 MB)' if workload in ('c4', 'c5', 'c2_cumsum', 'c2_cumprod')
             else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
@@ -271,18 +273,22 @@ def workload_config(workload, n):
 
 # ---------------------------------------------------------------------------------------------------------
 def main():
+    global C4_ROWS, C4_COLS
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=20)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='b200')
     ap.add_argument('--workload', default='c4')
+    ap.add_argument('--c4-rows', type=int, default=C4_ROWS, help='rows of the c4 tensor (profiling small cases)')
+    ap.add_argument('--c4-cols', type=int, default=C4_COLS, help='columns of the c4 tensor (profiling small cases)')
     ap.add_argument('--no-cpu', action='store_true', help='skip the CPU baseline leg')
     ap.add_argument('--no-e2e', action='store_true', help='skip the end-to-end leg')
     args = ap.parse_args()
     if args.warmup < 3 and args.impl != 'reference':
         args.warmup = 3
     workload = args.workload
+    C4_ROWS, C4_COLS = args.c4_rows, args.c4_cols
     if args.impl == 'reference':
         return run_reference_arm(args, workload)
 

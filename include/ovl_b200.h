@@ -143,7 +143,7 @@ int ovl_reduce_f32(int op, const float* in, uint64_t n, double* out_total, void*
  * exits).  This entry point has no counterpart in the reference.
  *
  *  - Limit: ovl_scan_f32_scratch_bytes(lines, n) must not exceed OVL_SCAN_STATIC_SCRATCH_BYTES (32767 tiles of
- *    4096 elements, about 134 million fp32 elements in total); larger requests return OVL_ERR_TOO_LARGE.
+ *    8192 elements, about 268 million fp32 elements in total); larger requests return OVL_ERR_TOO_LARGE.
  *  - The first call on each device looks up the array's device address (with that device current); make that
  *    first call before starting any stream capture.  No call allocates or frees memory.
  *  - All calls share the one array, and it keeps whatever the previous call left in it: each call clears the part

@@ -288,11 +288,11 @@ extern "C" int ovl_read_kernel_status(const void* scratch, void* cuda_stream, in
 
 namespace {
 
-template <class Op, bool ALIGNED, bool HAS_CARRY>
-__global__ void __launch_bounds__(ovl::kScanBlock) scan_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
-                                                                  const double* __restrict__ carry, uint64_t lines, uint64_t n,
-                                                                  void* scratch) {
-    ovl::scan_lines<float, double, Op, 4, ALIGNED, HAS_CARRY>(in, out, carry, lines, n, scratch);
+template <class Op, bool ALIGNED, bool HAS_CARRY, bool LOOKBACK>
+__global__ void __launch_bounds__(ovl::kScanBlock, 2) scan_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                                     const double* __restrict__ carry, uint64_t lines,
+                                                                     uint64_t n, void* scratch) {
+    ovl::scan_lines<float, double, Op, 4, ALIGNED, HAS_CARRY, LOOKBACK>(in, out, carry, lines, n, scratch);
 }
 
 template <class Op, bool ALIGNED>
@@ -316,15 +316,24 @@ int sm_count_cached() {
     return sms;
 }
 
+template <class Op, bool ALIGNED, bool HAS_CARRY>
+void launch_scan_lb(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
+                    uint32_t grid, bool lookback, cudaStream_t stream) {
+    if (lookback)
+        scan_f32_kernel<Op, ALIGNED, HAS_CARRY, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
+    else
+        scan_f32_kernel<Op, ALIGNED, HAS_CARRY, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
+}
+
 template <class Op>
 int launch_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, uint32_t grid,
-                bool aligned, cudaStream_t stream) {
+                bool aligned, bool lookback, cudaStream_t stream) {
     if (aligned) {
-        if (carry) scan_f32_kernel<Op, true, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
-        else scan_f32_kernel<Op, true, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
+        if (carry) launch_scan_lb<Op, true, true>(in, out, lines, n, carry, scratch, grid, lookback, stream);
+        else launch_scan_lb<Op, true, false>(in, out, lines, n, carry, scratch, grid, lookback, stream);
     } else {
-        if (carry) scan_f32_kernel<Op, false, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
-        else scan_f32_kernel<Op, false, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
+        if (carry) launch_scan_lb<Op, false, true>(in, out, lines, n, carry, scratch, grid, lookback, stream);
+        else launch_scan_lb<Op, false, false>(in, out, lines, n, carry, scratch, grid, lookback, stream);
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);
@@ -350,11 +359,13 @@ extern "C" int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines,
     if (tiles >= (1ull << 32) - 65536) return OVL_ERR_TOO_LARGE;   // the tile counter is 32 bits wide
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const bool aligned = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0) && (lines == 1 || n % 4 == 0);
-    const uint64_t max_grid = (uint64_t)sm_count_cached() * 8;
+    const bool lookback = n > kTile;
+    const uint64_t max_grid = (uint64_t)sm_count_cached() * 2;     // two resident blocks of 512 threads per SM
     const uint32_t grid = (uint32_t)(tiles < max_grid ? tiles : max_grid);
-    OVL_CUDA(cudaMemsetAsync(scratch, 0, need, stream));
-    if (op == 0) return launch_scan<ovl::OpAdd>(in, out, lines, n, carry, scratch, grid, aligned, stream);
-    return launch_scan<ovl::OpMul>(in, out, lines, n, carry, scratch, grid, aligned, stream);
+    // lines of at most one tile publish nothing: only the header (status word) has to be clear
+    OVL_CUDA(cudaMemsetAsync(scratch, 0, lookback ? need : sizeof(ovl::ScanHeader), stream));
+    if (op == 0) return launch_scan<ovl::OpAdd>(in, out, lines, n, carry, scratch, grid, aligned, lookback, stream);
+    return launch_scan<ovl::OpMul>(in, out, lines, n, carry, scratch, grid, aligned, lookback, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------

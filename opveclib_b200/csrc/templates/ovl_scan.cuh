@@ -2,11 +2,14 @@
 //
 // The operator language expresses a scan as one worker walking a whole line serially
 // (opveclib/examples/test_accumulate.py:22-78).  Here a line of n elements is cut into tiles of
-// BLOCK * VPT * VEC elements; thread blocks claim tiles in order from an atomic counter, scan their tile in
-// registers (serial scan inside each 128-bit vector, warp-shuffle scan across lanes, shared-memory scan across
-// warps), publish the tile aggregate, and obtain the prefix of everything to their left in the same line by
-// looking back over the descriptors of earlier tiles: aggregates are summed until a tile that already knows its
-// inclusive prefix is met.  Every element is read once and written once.
+// BLOCK * VPT * VEC elements; thread blocks scan their tile in registers (serial scan inside each 128-bit
+// vector, warp-shuffle scan across lanes, shared-memory scan across warps).  Lines that fit one tile need nothing
+// else.  For longer lines blocks claim tiles in order from an atomic counter, publish the tile aggregate, and
+// obtain the prefix of everything to their left in the same line by looking back over the descriptors of
+// earlier tiles: aggregates are summed until a tile that already knows its inclusive prefix is met; several
+// warps inspect consecutive windows of 32 descriptors at once, because the rate at which prefixes can travel
+// along the line is (tiles inspected per round) / (one L2 round trip).  Every element is read once and
+// written once.
 //
 // Accumulation runs in the wider type Acc (double for fp32 data), so results do not depend on how the line was
 // cut and are the correctly rounded exact scan rather than a re-association of fp32 partial sums.
@@ -19,8 +22,9 @@
 
 namespace ovl {
 
-constexpr int kScanBlock = 256;   // threads per block
-constexpr int kScanVpt = 4;       // 128-bit vectors per thread
+constexpr int kScanBlock = 512;          // threads per block
+constexpr int kScanVpt = 4;              // 128-bit vectors per thread
+constexpr int kScanLookbackWarps = 4;    // look-back windows (of 32 tiles each) inspected in parallel
 constexpr uint32_t kScanSpinLimit = 1u << 22;
 constexpr int32_t kErrTimeout = 8;  // OVL_ERR_TIMEOUT
 
@@ -72,6 +76,16 @@ __device__ __forceinline__ A shfl_up_any(A v, int delta) {
     }
 }
 template <typename A>
+__device__ __forceinline__ A shfl_down_any(A v, int delta) {
+    if constexpr (sizeof(A) == 8) {
+        long long x = *reinterpret_cast<long long*>(&v);
+        x = __shfl_down_sync(0xffffffffu, x, delta);
+        return *reinterpret_cast<A*>(&x);
+    } else {
+        return __shfl_down_sync(0xffffffffu, v, delta);
+    }
+}
+template <typename A>
 __device__ __forceinline__ A shfl_any(A v, int lane) {
     if constexpr (sizeof(A) == 8) {
         long long x = *reinterpret_cast<long long*>(&v);
@@ -82,33 +96,47 @@ __device__ __forceinline__ A shfl_any(A v, int lane) {
     }
 }
 
-// One launch scans `lines` lines of `n` elements.  ALIGNED: every line start is VEC-aligned (n % VEC == 0 or a
-// single line) and the base pointers are 16-byte aligned, so whole vectors can be moved with one instruction.
-template <typename T, typename Acc, class Op, int VEC, bool ALIGNED, bool HAS_CARRY>
+// One launch scans `lines` lines of `n` elements.
+//  ALIGNED    every line start is VEC-aligned (n % VEC == 0 or a single line) and the base pointers are 16-byte
+//             aligned, so whole vectors move with one instruction.
+//  LOOKBACK   lines are longer than one tile.  false: one tile per line, tiles are handed out statically
+//             (blockIdx, blockIdx + gridDim, ...), nothing is published and no block ever waits for another.
+//             true: tiles are claimed in order from the atomic counter and prefixes travel through descriptors.
+template <typename T, typename Acc, class Op, int VEC, bool ALIGNED, bool HAS_CARRY, bool LOOKBACK>
 __device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry,
                                            const uint64_t lines, const uint64_t n, void* scratch) {
     constexpr int BLOCK = kScanBlock;
     constexpr int VPT = kScanVpt;
     constexpr int WARPS = BLOCK / 32;
+    constexpr int LBW = kScanLookbackWarps;
     constexpr uint32_t TILE = BLOCK * VPT * VEC;
     constexpr uint32_t WARP_ELEMS = 32 * VPT * VEC;
 
     ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
     TileDesc<Acc>* desc = reinterpret_cast<TileDesc<Acc>*>(hdr + 1);
-    const uint64_t tiles_per_line = (n + TILE - 1) / TILE;
+    const uint64_t tiles_per_line = LOOKBACK ? (n + TILE - 1) / TILE : 1;
     const uint64_t total_tiles = tiles_per_line * lines;
 
-    __shared__ Acc s_warp_total[WARPS];
-    __shared__ Acc s_exclusive;
+    __shared__ Acc s_warp_total[2][WARPS];     // double buffered by iteration parity: one barrier per tile
+    __shared__ Acc s_win_sum[LBW];
+    __shared__ int s_win_found[LBW];
     __shared__ uint64_t s_tile;
 
     const int lane = threadIdx.x & 31;
     const int wid = threadIdx.x >> 5;
+    uint64_t static_tile = blockIdx.x;
+    int parity = 0;
 
     while (true) {
-        if (threadIdx.x == 0) s_tile = atomicAdd(&hdr->tile_counter, 1u);
-        __syncthreads();
-        const uint64_t tile = s_tile;
+        uint64_t tile;
+        if (LOOKBACK) {
+            if (threadIdx.x == 0) s_tile = atomicAdd(&hdr->tile_counter, 1u);
+            __syncthreads();
+            tile = s_tile;
+        } else {
+            tile = static_tile;
+            static_tile += gridDim.x;
+        }
         if (tile >= total_tiles) break;
         const uint64_t line = tile / tiles_per_line;
         const uint64_t tile_in_line = tile - line * tiles_per_line;
@@ -150,7 +178,7 @@ __device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restri
             for (int e = 0; e < VEC; ++e) x[j][e] = Op::apply(base, x[j][e]);
             run = Op::apply(run, shfl_any(t, 31));
         }
-        if (lane == 0) s_warp_total[wid] = run;
+        if (lane == 0) s_warp_total[parity][wid] = run;
         __syncthreads();
 
         // ---- prefix of the warps to the left inside the tile, and the tile aggregate
@@ -158,64 +186,83 @@ __device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restri
         Acc aggregate = Op::template identity<Acc>();
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-            const Acc v = s_warp_total[w];
+            const Acc v = s_warp_total[parity][w];
             if (w < wid) warp_excl = Op::apply(warp_excl, v);
             aggregate = Op::apply(aggregate, v);
         }
+        parity ^= 1;
 
-        // ---- prefix of the tiles to the left inside the line (decoupled look-back, warp 0)
-        if (wid == 0) {
-            Acc exclusive = Op::template identity<Acc>();
-            if (tile_in_line == 0) {
-                if (HAS_CARRY) exclusive = *carry;
-            } else {
-                if (lane == 0) {
-                    desc[tile].aggregate = aggregate;
-                    st_flag(&desc[tile].flag, 1u);
-                }
-                int64_t look = (int64_t)tile - 1;              // nearest tile of the current window
-                const int64_t first = (int64_t)(tile - tile_in_line);
-                bool done = false;
-                while (!done) {
-                    const int64_t mine = look - lane;
-                    uint32_t flag = 2u;                          // lanes left of the line start: nothing to add
+        // ---- prefix of the tiles to the left inside the line
+        Acc exclusive = Op::template identity<Acc>();
+        if (tile_in_line == 0) {
+            if (HAS_CARRY) exclusive = *carry;
+            if (LOOKBACK && threadIdx.x == 0) {
+                desc[tile].prefix = Op::apply(exclusive, aggregate);
+                st_flag(&desc[tile].flag, 2u);
+            }
+        } else if (LOOKBACK) {
+            // decoupled look-back: LBW warps inspect LBW consecutive windows of 32 earlier tiles at once
+            if (threadIdx.x == 0) {
+                desc[tile].aggregate = aggregate;
+                st_flag(&desc[tile].flag, 1u);
+            }
+            const int64_t first = (int64_t)(tile - tile_in_line);   // first tile of this line
+            int64_t base = (int64_t)tile - 1;                       // nearest tile of window 0
+            bool done = false;
+            while (!done) {
+                if (wid < LBW) {
+                    const int64_t mine = base - 32 * wid - lane;
+                    uint32_t flag = 2u;                              // left of the line start: nothing to add
                     Acc val = Op::template identity<Acc>();
-                    bool beyond = mine < first;
-                    if (!beyond) {
+                    if (mine >= first) {
                         uint32_t spins = 0;
                         flag = ld_flag(&desc[mine].flag);
                         while (flag == 0u && spins < kScanSpinLimit) {
-                            __nanosleep(32);
+                            if (spins > 8) __nanosleep(32);
                             flag = ld_flag(&desc[mine].flag);
                             ++spins;
                         }
                         if (flag == 0u) {
                             atomicExch(&hdr->status, kErrTimeout);
-                            flag = 2u;                           // give up: behave as if the line started here
+                            flag = 2u;                               // give up: behave as if the line started here
                         } else {
                             val = (flag == 2u) ? *(volatile Acc*)&desc[mine].prefix : *(volatile Acc*)&desc[mine].aggregate;
                         }
                     }
-                    // nearest lane that holds an inclusive prefix ends the look-back
+                    // the nearest lane holding an inclusive prefix ends this window
                     const uint32_t has_prefix = __ballot_sync(0xffffffffu, flag == 2u);
-                    const int stop = __ffs(has_prefix) - 1;      // always >= 0 once the window passes the line start
+                    const int stop = __ffs(has_prefix) - 1;
                     const int last = (stop >= 0) ? stop : 31;
-                    // combine left to right: lane `last` (farthest) ... lane 0 (nearest), then what we have
-                    Acc window = Op::template identity<Acc>();
-                    for (int k = last; k >= 0; --k) window = Op::apply(window, shfl_any(val, k));
-                    exclusive = Op::apply(window, exclusive);
-                    if (stop >= 0) done = true;
-                    look -= 32;
+                    // combine left to right: lane `last` (farthest) ... lane 0 (nearest); an order-preserving tree:
+                    // after step d lane k holds v[k+2d-1] (+) ... (+) v[k]
+                    Acc window = (lane <= last) ? val : Op::template identity<Acc>();
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        const Acc far = shfl_down_any(window, d);
+                        if (lane + d < 32) window = Op::apply(far, window);
+                    }
+                    if (lane == 0) {
+                        s_win_sum[wid] = window;
+                        s_win_found[wid] = (stop >= 0) ? 1 : 0;
+                    }
                 }
+                __syncthreads();
+#pragma unroll
+                for (int w = 0; w < LBW; ++w) {
+                    if (!done) {
+                        exclusive = Op::apply(s_win_sum[w], exclusive);
+                        if (s_win_found[w]) done = true;
+                    }
+                }
+                base -= 32 * LBW;
+                if (!done) __syncthreads();     // the window slots are rewritten in the next round
             }
-            if (lane == 0) {
+            if (threadIdx.x == 0) {
                 desc[tile].prefix = Op::apply(exclusive, aggregate);
                 st_flag(&desc[tile].flag, 2u);
-                s_exclusive = exclusive;
             }
         }
-        __syncthreads();
-        const Acc offset = Op::apply(s_exclusive, warp_excl);
+        const Acc offset = Op::apply(exclusive, warp_excl);
 
         // ---- store
 #pragma unroll
@@ -232,7 +279,7 @@ __device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restri
                     if (off + e < n) out[line_base + off + e] = (T)Op::apply(offset, x[j][e]);
             }
         }
-        __syncthreads();   // s_tile / s_exclusive / s_warp_total are reused by the next tile
+        if (LOOKBACK) __syncthreads();   // s_tile and the window slots are reused by the next tile
     }
 }
 

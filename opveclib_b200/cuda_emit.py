@@ -40,10 +40,10 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv4'
+TEMPLATE_VERSION = 'tv5'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
-SCAN_BLOCK = 256
+SCAN_BLOCK = 512
 SCAN_VPT = 4
 SCAN_HEADER_BYTES = 16
 
@@ -436,13 +436,16 @@ def emit_cuda(kernel, name):
         op = 'ovl::OpAdd' if spec.op == 'add' else 'ovl::OpMul'
         can_align = spec.lines == 1 or spec.n % vec == 0
         variants = [('scanu', 'false')] + ([('scan', 'true')] if can_align else [])
+        lookback = spec.n > tile
         for suffix, aligned in variants:
-            src += ['extern "C" __global__ void __launch_bounds__(' + str(SCAN_BLOCK) + ') ' + name + '_' + suffix +
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(SCAN_BLOCK) + ', 2) ' + name + '_' + suffix +
                     '(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0, void* scratch) {',
                     '    ovl::scan_lines<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned +
-                    ', false>(in0, out0, nullptr, ' + str(spec.lines) + 'ull, ' + str(spec.n) + 'ull, scratch);',
+                    ', false, ' + ('true' if lookback else 'false') + '>(in0, out0, nullptr, ' + str(spec.lines) +
+                    'ull, ' + str(spec.n) + 'ull, scratch);',
                     '}', '']
         meta['scan'] = {'symbol': name + '_scan' if can_align else None, 'symbol_unaligned': name + '_scanu',
-                        'block': SCAN_BLOCK, 'tiles': tiles, 'scratch_bytes': scratch, 'zero_bytes': scratch,
+                        'block': SCAN_BLOCK, 'tiles': tiles, 'scratch_bytes': scratch,
+                        'zero_bytes': scratch if lookback else SCAN_HEADER_BYTES, 'blocks_per_sm': 2,
                         'align_bytes': vec * spec.dtype.itemsize, 'lines': spec.lines, 'n': spec.n, 'op': spec.op}
     return '\n'.join(src), meta

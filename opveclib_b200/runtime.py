@@ -73,7 +73,7 @@ class KernelPlan(object):
         else:
             m = meta['scan']
             block = m['block']
-            grid = max(1, min(m['tiles'], sms * 8))
+            grid = max(1, min(m['tiles'], sms * m.get('blocks_per_sm', 2)))
             symbol = m['symbol'] if which == 'scan' else m['symbol_unaligned']
             scratch, zero = m['scratch_bytes'], m['zero_bytes']
             if which == 'scan':

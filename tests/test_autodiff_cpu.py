@@ -1,0 +1,92 @@
+"""Backward operator graphs composed from ``@gradient`` definitions, checked on the CPU through the oracle.
+
+The reference checks its merged gradient graphs against TensorFlow's autodiff
+(opveclib/test/test_operator_merge.py:395-483, opveclib/stdops/test_math.py:91-157, 270-307); torch's autograd
+in float64 plays that role here."""
+import numpy as np
+import torch
+
+import cases
+from helpers import assert_exact
+from opveclib_b200.autodiff import compose_backward
+from opveclib_b200.fuse import merge_op_dag
+from opveclib_b200.opgraph import build_op_dag
+from oracle import runner
+
+
+def _run_backward(dag, grads_out):
+    bdag, has_grad = compose_backward(dag)
+    fused = merge_op_dag(bdag)
+    leaves = list(dag.inputs) + list(grads_out)
+    bdag.inputs = leaves
+    fused.inputs = leaves
+    plain, _ = runner.run_dag(bdag)
+    merged, _ = runner.run_dag(fused)
+    for a, b in zip(plain, merged):
+        assert_exact(b, a, 'fused backward')
+    return plain, has_grad, len(bdag.kernels), len(fused.kernels)
+
+
+def test_stdops_lstm_backward_matches_autograd_and_fuses_to_one_kernel():
+    ns = cases.impl()
+    so = ns.stdops
+    rs = np.random.RandomState(0)
+    g, c = rs.normal(size=(4, 24)), rs.normal(size=(4, 6))
+    i, j, f, o = so.split(g, split_dim=1, num_split=4)
+    new_c = so.mul(c, so.sigmoid(f)) + so.sigmoid(i) * so.tanh(j)
+    new_h = so.tanh(new_c) * so.sigmoid(o)
+    dag = build_op_dag(new_c, new_h)
+    dc, dh = rs.normal(size=(4, 6)), rs.normal(size=(4, 6))
+    grads, has_grad, n_plain, n_fused = _run_backward(dag, [dc, dh])
+    assert has_grad == [True, True] and n_plain > 10 and n_fused == 1
+
+    tg = torch.tensor(g, requires_grad=True)
+    tc = torch.tensor(c, requires_grad=True)
+    ti, tj, tf, to = tg.chunk(4, dim=1)
+    nc = tc * torch.sigmoid(tf) + torch.sigmoid(ti) * torch.tanh(tj)
+    nh = torch.tanh(nc) * torch.sigmoid(to)
+    ((nc * torch.tensor(dc)).sum() + (nh * torch.tensor(dh)).sum()).backward()
+    want = {id(g): tg.grad.numpy(), id(c): tc.grad.numpy()}
+    for leaf, got in zip(dag.inputs, grads):
+        np.testing.assert_allclose(got, want[id(leaf)], rtol=1e-12, atol=1e-14)
+
+
+def test_hand_fused_lstm_gradient_operator_is_used():
+    ns = cases.impl()
+    rs = np.random.RandomState(1)
+    g, c = rs.normal(size=(3, 16)), rs.normal(size=(3, 4))
+    op = ns.lstm(g, c, forget_bias=0.5)
+    dag = build_op_dag(op[0], op[1])
+    dc, dh = rs.normal(size=(3, 4)), rs.normal(size=(3, 4))
+    grads, has_grad, n_plain, n_fused = _run_backward(dag, [dc, dh])
+    assert has_grad == [True, True] and n_plain == 1     # only lstm_grad is needed: it recomputes what it uses
+
+    tg = torch.tensor(g, requires_grad=True)
+    tc = torch.tensor(c, requires_grad=True)
+    ti, tj, tf, to = tg.chunk(4, dim=1)
+    nc = tc * torch.sigmoid(tf + 0.5) + torch.sigmoid(ti) * torch.tanh(tj)
+    nh = torch.tanh(nc) * torch.sigmoid(to)
+    ((nc * torch.tensor(dc)).sum() + (nh * torch.tensor(dh)).sum()).backward()
+    want = {id(g): tg.grad.numpy(), id(c): tc.grad.numpy()}
+    for leaf, got in zip(dag.inputs, grads):
+        np.testing.assert_allclose(got, want[id(leaf)], rtol=1e-10, atol=1e-12)
+
+
+def test_shared_input_contributions_are_summed_and_missing_gradients_block():
+    ns = cases.impl()
+    so = ns.stdops
+    rs = np.random.RandomState(2)
+    x, y = rs.uniform(0.5, 2, 7), rs.uniform(0.5, 2, 7)
+    z = so.mul(x, y) + so.div(x, y) - ns.expm1(x)      # x feeds three operators
+    dag = build_op_dag(z)
+    dz = rs.normal(size=7)
+    grads, has_grad, _, _ = _run_backward(dag, [dz])
+    want = {id(x): dz * (y + 1 / y - np.exp(x)), id(y): dz * (x - x / (y * y))}
+    for leaf, got in zip(dag.inputs, grads):
+        np.testing.assert_allclose(got, want[id(leaf)], rtol=1e-12)
+    # `mod` has no gradient: nothing flows to its inputs
+    w = so.mod(x, y) * y
+    dag = build_op_dag(w)
+    bdag, has_grad = compose_backward(dag)
+    flags = dict((id(leaf), h) for leaf, h in zip(dag.inputs, has_grad))
+    assert flags[id(x)] is False

@@ -33,10 +33,10 @@ def test_status_strings_and_size_queries_work_without_a_device():
     assert lib.ovl_status_string(0) == b'ok'
     assert b'element count' in lib.ovl_status_string(2)
     assert b'wait expired' in lib.ovl_status_string(8)
-    # 16-byte header + one 32-byte descriptor per tile of 4096 elements
-    assert lib.ovl_scan_f32_scratch_bytes(1, 4096) == 16 + 32
-    assert lib.ovl_scan_f32_scratch_bytes(3, 4097) == 16 + 32 * 6
-    assert lib.ovl_scan_f32_scratch_bytes(4096, 8192) == 16 + 32 * 8192
+    # 16-byte header + one 32-byte descriptor per tile of 8192 elements
+    assert lib.ovl_scan_f32_scratch_bytes(1, 8192) == 16 + 32
+    assert lib.ovl_scan_f32_scratch_bytes(3, 8193) == 16 + 32 * 6
+    assert lib.ovl_scan_f32_scratch_bytes(4096, 8192) == 16 + 32 * 4096
 
 
 def test_argument_validation_happens_before_any_cuda_call():

@@ -1,0 +1,120 @@
+"""The scan across shard boundaries on GPUs: built-in reduction and carry-seeded scan kernels, and the NCCL
+exchange when two devices are present."""
+import ctypes
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from helpers import DRYRUN
+from opveclib_b200 import launcher, parallel
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(DRYRUN, reason='needs a device')]
+
+
+def _reference(x, op):
+    x64 = x.astype(np.float64)
+    return (np.cumsum(x64) if op == 'add' else np.cumprod(x64)).astype(np.float32)
+
+
+@pytest.mark.parametrize('op', ['add', 'mul'])
+@pytest.mark.parametrize('n', [1, 5, 8191, 8192, 8193, 100003, 1 << 21])
+def test_single_rank_scan_is_the_rounded_exact_scan(op, n):
+    import torch
+    rs = np.random.RandomState(n % 1000)
+    x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.99, 1.01, n)).astype(np.float32)
+    scan = parallel.ShardedScan(n, op)
+    y = scan(torch.from_numpy(x).cuda())
+    scan.check_status()
+    got = y.cpu().numpy()
+    want = _reference(x, op)
+    # fp64 accumulation: every element is the correctly rounded exact prefix (the fp64 reference itself carries
+    # rounding of the order of 1e-16 * n, far below one fp32 ulp here)
+    np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
+
+
+@pytest.mark.parametrize('op', ['add', 'mul'])
+@pytest.mark.parametrize('world', [2, 4, 8])
+def test_rank_emulation_on_one_gpu_reduce_carry_scan(op, world):
+    """All ranks' three steps run one after the other on one device through the C-ABI entry points; the
+    concatenated result equals the unsharded scan.  (Kernels of different ranks never wait for each other, so
+    running them back to back on one GPU is the same computation.)"""
+    import torch
+    lib = launcher.library()
+    code = 0 if op == 'add' else 1
+    n = 50000 * world + 3
+    rs = np.random.RandomState(world)
+    x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.999, 1.001, n)).astype(np.float32)
+    shards = [torch.from_numpy(np.ascontiguousarray(parallel.shard_leading_axis(x, r, world))).cuda()
+              for r in range(world)]
+    stream = torch.cuda.current_stream().cuda_stream
+    totals = torch.zeros(world, dtype=torch.float64, device='cuda')
+    for r, s in enumerate(shards):
+        nbytes = int(lib.ovl_reduce_f32_scratch_bytes(s.numel()))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device='cuda')
+        launcher.check(lib.ovl_reduce_f32(code, s.data_ptr(), s.numel(), totals[r:].data_ptr(), scratch.data_ptr(),
+                                          nbytes, stream), 'reduce')
+    host_totals = totals.cpu().numpy()
+    for r, s in enumerate(shards):
+        s64 = s.cpu().numpy().astype(np.float64)
+        np.testing.assert_allclose(host_totals[r], s64.sum() if op == 'add' else s64.prod(), rtol=1e-12)
+    parts = []
+    for r, s in enumerate(shards):
+        carry = torch.tensor([parallel.exclusive_carry(host_totals, r, op)], dtype=torch.float64, device='cuda')
+        out = torch.empty_like(s)
+        nbytes = int(lib.ovl_scan_f32_scratch_bytes(1, s.numel()))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device='cuda')
+        launcher.check(lib.ovl_scan_f32(code, s.data_ptr(), out.data_ptr(), 1, s.numel(), carry.data_ptr(),
+                                        scratch.data_ptr(), nbytes, stream), 'scan')
+        status = ctypes.c_int32(-1)
+        launcher.check(lib.ovl_read_kernel_status(scratch.data_ptr(), stream, ctypes.byref(status)), 'status')
+        assert status.value == 0
+        parts.append(out.cpu().numpy())
+    np.testing.assert_allclose(np.concatenate(parts), _reference(x, op), rtol=1.3e-7, atol=0)
+
+
+def _nccl_rank(rank, world, port, op, n, queue):
+    import torch
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
+    try:
+        rs = np.random.RandomState(9)
+        x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.999, 1.001, n)).astype(np.float32)
+        mine = np.ascontiguousarray(parallel.shard_leading_axis(x, rank, world))
+        scan = parallel.ShardedScan(mine.size, op)
+        y = scan(torch.from_numpy(mine).cuda())
+        scan.check_status()
+        queue.put((rank, y.cpu().numpy()))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('op', ['add', 'mul'])
+def test_two_gpus_exchange_carries_over_nccl(op):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(('127.0.0.1', 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    world, n = 2, 300001
+    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, op, n, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    parts = dict(queue.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    rs = np.random.RandomState(9)
+    x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.999, 1.001, n)).astype(np.float32)
+    np.testing.assert_allclose(np.concatenate([parts[r] for r in range(world)]), _reference(x, op), rtol=1.3e-7,
+                               atol=0)

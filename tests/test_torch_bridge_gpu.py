@@ -1,0 +1,90 @@
+"""The torch bridge on a GPU: torch tensors in and out, gradients through ``torch.autograd``."""
+import numpy as np
+import pytest
+
+import cases
+from helpers import DRYRUN
+
+pytestmark = pytest.mark.gpu
+
+
+def _cuda(a, grad=False):
+    import torch
+    if DRYRUN:
+        return a
+    return torch.tensor(a, device='cuda', requires_grad=grad)
+
+
+@pytest.mark.skipif(DRYRUN, reason='needs a device')
+def test_as_torch_forward_and_backward_match_autograd():
+    import torch
+    ns = cases.impl()
+    so = ns.stdops
+    rs = np.random.RandomState(3)
+    g = torch.tensor(rs.normal(size=(8, 64)).astype(np.float32), device='cuda', requires_grad=True)
+    c = torch.tensor(rs.normal(size=(8, 16)).astype(np.float32), device='cuda', requires_grad=True)
+    i, j, f, o = so.split(g, split_dim=1, num_split=4)
+    new_c = so.mul(c, so.sigmoid(f)) + so.sigmoid(i) * so.tanh(j)
+    new_h = so.tanh(new_c) * so.sigmoid(o)
+    nc, nh = ns.ovl.as_torch([new_c, new_h])
+    assert nc.is_cuda and nc.requires_grad
+    wc = torch.tensor(rs.normal(size=(8, 16)).astype(np.float32), device='cuda')
+    wh = torch.tensor(rs.normal(size=(8, 16)).astype(np.float32), device='cuda')
+    ((nc * wc).sum() + (nh * wh).sum()).backward()
+    got_g, got_c = g.grad.clone(), c.grad.clone()
+
+    g2 = g.detach().clone().requires_grad_(True)
+    c2 = c.detach().clone().requires_grad_(True)
+    ti, tj, tf, to = g2.chunk(4, dim=1)
+    rc = c2 * torch.sigmoid(tf) + torch.sigmoid(ti) * torch.tanh(tj)
+    rh = torch.tanh(rc) * torch.sigmoid(to)
+    ((rc * wc).sum() + (rh * wh).sum()).backward()
+    torch.testing.assert_close(nc.detach(), rc.detach(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(nh.detach(), rh.detach(), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(got_g, g2.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(got_c, c2.grad, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.skipif(DRYRUN, reason='needs a device')
+def test_hand_fused_lstm_through_as_torch_and_evaluate_on_device_tensors():
+    import torch
+    ns = cases.impl()
+    rs = np.random.RandomState(4)
+    g = torch.tensor(rs.normal(size=(16, 128)).astype(np.float32), device='cuda', requires_grad=True)
+    c = torch.tensor(rs.normal(size=(16, 32)).astype(np.float32), device='cuda', requires_grad=True)
+    op = ns.lstm(g, c, forget_bias=0.0)
+    nc, nh = ns.ovl.as_torch([op[0], op[1]])
+    (nc.sum() + 2 * nh.sum()).backward()
+    g2 = g.detach().clone().requires_grad_(True)
+    c2 = c.detach().clone().requires_grad_(True)
+    ti, tj, tf, to = g2.chunk(4, dim=1)
+    rc = c2 * torch.sigmoid(tf) + torch.sigmoid(ti) * torch.tanh(tj)
+    rh = torch.tanh(rc) * torch.sigmoid(to)
+    (rc.sum() + 2 * rh.sum()).backward()
+    torch.testing.assert_close(g.grad, g2.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(c.grad, c2.grad, rtol=1e-4, atol=1e-5)
+    # evaluate() with device tensors keeps results on the device
+    out = ns.ovl.evaluate([op[0], op[1]])
+    assert all(isinstance(t, torch.Tensor) and t.is_cuda for t in out)
+    torch.testing.assert_close(out[0], rc.detach(), rtol=1e-5, atol=1e-6)
+
+
+def test_backward_kernels_compile():
+    """Cache warming for the two tests above (also runs without a device): trace, compose, fuse, compile."""
+    from opveclib_b200 import runtime
+    from opveclib_b200.autodiff import compose_backward
+    from opveclib_b200.fuse import merge_op_dag
+    from opveclib_b200.opgraph import build_op_dag
+    ns = cases.impl()
+    so = ns.stdops
+    g, c = np.zeros((8, 64), np.float32), np.zeros((8, 16), np.float32)
+    i, j, f, o = so.split(g, split_dim=1, num_split=4)
+    new_c = so.mul(c, so.sigmoid(f)) + so.sigmoid(i) * so.tanh(j)
+    new_h = so.tanh(new_c) * so.sigmoid(o)
+    g2, c2 = np.zeros((16, 128), np.float32), np.zeros((16, 32), np.float32)
+    op = ns.lstm(g2, c2, forget_bias=0.0)
+    for outs in ([new_c, new_h], [op[0], op[1]]):
+        runtime.compile_outputs(outs)
+        bdag, _ = compose_backward(build_op_dag(*outs))
+        prog = runtime.Program(merge_op_dag(bdag))
+        assert len(prog.plans) == 1
