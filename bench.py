@@ -264,6 +264,8 @@ def workload_config(workload, n):
         'c3_grad': 'LSTM cell gradient, gates fp32 [512, 4096], c/dc/dh [512, 1024]',
         'c5': 'cumsum along the sharded axis, fp32 [2^31] normal(0,1), contiguous shards, fp64 carry exchange',
     }
+    if workload == 'c5' and C5_TOTAL != 1 << 31:
+        names['c5'] = 'cumsum along the sharded axis, fp32 [%d] normal(0,1) (reduced case)' % C5_TOTAL
     if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
         names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
@@ -273,7 +275,7 @@ def workload_config(workload, n):
 
 # ---------------------------------------------------------------------------------------------------------
 def main():
-    global C4_ROWS, C4_COLS
+    global C4_ROWS, C4_COLS, C5_TOTAL
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
     ap.add_argument('--steps', type=int, default=20)
@@ -282,13 +284,14 @@ def main():
     ap.add_argument('--workload', default='c4')
     ap.add_argument('--c4-rows', type=int, default=C4_ROWS, help='rows of the c4 tensor (profiling small cases)')
     ap.add_argument('--c4-cols', type=int, default=C4_COLS, help='columns of the c4 tensor (profiling small cases)')
+    ap.add_argument('--c5-n', type=int, default=C5_TOTAL, help='elements of the c5 tensor (profiling small cases)')
     ap.add_argument('--no-cpu', action='store_true', help='skip the CPU baseline leg')
     ap.add_argument('--no-e2e', action='store_true', help='skip the end-to-end leg')
     args = ap.parse_args()
     if args.warmup < 3 and args.impl != 'reference':
         args.warmup = 3
     workload = args.workload
-    C4_ROWS, C4_COLS = args.c4_rows, args.c4_cols
+    C4_ROWS, C4_COLS, C5_TOTAL = args.c4_rows, args.c4_cols, args.c5_n
     if args.impl == 'reference':
         return run_reference_arm(args, workload)
 

@@ -74,6 +74,9 @@ typedef struct OvlKernelSpec {
     uint64_t scratch_bytes;      /* device scratch the kernel needs (0 = none); provided by the caller */
     uint64_t scratch_zero_bytes; /* leading part of the scratch that must be zero when the kernel starts;
                                     ovl_launch clears it on the stream before the kernel */
+    uint32_t cooperative;        /* non-zero: thread blocks wait for one another (look-back scans), so the kernel is
+                                    started as a cooperative launch and grid_x is clamped to the number of blocks
+                                    the device can hold at once */
 } OvlKernelSpec;
 
 /* Library / device ------------------------------------------------------------------------------------- */
@@ -142,8 +145,9 @@ int ovl_reduce_f32(int op, const float* in, uint64_t n, double* out_total, void*
  * (OVL_SCAN_STATIC_SCRATCH_BYTES of device memory, held by every GPU that loads the library until the process
  * exits).  This entry point has no counterpart in the reference.
  *
- *  - Limit: ovl_scan_f32_scratch_bytes(lines, n) must not exceed OVL_SCAN_STATIC_SCRATCH_BYTES (32767 tiles of
- *    8192 elements, about 268 million fp32 elements in total); larger requests return OVL_ERR_TOO_LARGE.
+ *  - Limit: ovl_scan_f32_scratch_bytes(lines, n) must not exceed OVL_SCAN_STATIC_SCRATCH_BYTES (32767 tiles:
+ *    that many lines of up to 8192 elements, or about 134 million elements in longer lines, which are cut into
+ *    tiles of 4096); larger requests return OVL_ERR_TOO_LARGE.
  *  - The first call on each device looks up the array's device address (with that device current); make that
  *    first call before starting any stream capture.  No call allocates or frees memory.
  *  - All calls share the one array, and it keeps whatever the previous call left in it: each call clears the part

@@ -54,6 +54,7 @@ struct OvlKernel {
     std::vector<uint32_t> align;
     uint32_t n_in, n_out;
     uint64_t scratch_bytes, scratch_zero_bytes;
+    uint32_t cooperative;
 };
 
 extern "C" const char* ovl_version(void) { return "ovl_b200 0.1.0 (sm_100a)"; }
@@ -137,6 +138,7 @@ extern "C" int ovl_kernel_create(OvlModule* module, const OvlKernelSpec* spec, O
     else k->align.assign(n, 0);
     k->scratch_bytes = spec->scratch_bytes;
     k->scratch_zero_bytes = spec->scratch_zero_bytes;
+    k->cooperative = spec->cooperative;
     for (uint32_t i = 0; i < n; ++i)
         if (dtype_size(k->dtypes[i]) == 0) {
             delete k;
@@ -185,6 +187,21 @@ int enqueue(const OvlKernel* k, const OvlTensor* in, size_t n_in, const OvlTenso
     if (k->scratch_bytes) ptrs[n++] = scratch;
     for (size_t i = 0; i < n; ++i) args[i] = &ptrs[i];
     if (k->scratch_zero_bytes) OVL_CUDA(cudaMemsetAsync(scratch, 0, k->scratch_zero_bytes, stream));
+    if (k->cooperative) {
+        // blocks of this kernel wait for one another: all of them have to be resident
+        uint32_t grid = k->grid_x;
+        int per_sm = 0, dev = 0, sms = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k->fn, (int)k->block_x, k->dynamic_smem) ==
+                cudaSuccess && per_sm > 0 && cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
+            const uint64_t cap = (uint64_t)per_sm * (uint64_t)sms;
+            if (grid > cap) grid = (uint32_t)cap;
+        } else {
+            (void)cudaGetLastError();
+        }
+        OVL_CUDA(cudaLaunchCooperativeKernel((const void*)k->fn, dim3(grid), dim3(k->block_x), args, k->dynamic_smem, stream));
+        return OVL_OK;
+    }
     OVL_CUDA(cudaLaunchKernel((const void*)k->fn, dim3(k->grid_x), dim3(k->block_x), args, k->dynamic_smem, stream));
     return OVL_OK;
 }
@@ -289,10 +306,18 @@ extern "C" int ovl_read_kernel_status(const void* scratch, void* cuda_stream, in
 namespace {
 
 template <class Op, bool ALIGNED, bool HAS_CARRY, bool LOOKBACK>
-__global__ void __launch_bounds__(ovl::kScanBlock, 2) scan_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+__global__ void __launch_bounds__(LOOKBACK ? ovl::kScanBlockLookback : ovl::kScanBlock, LOOKBACK ? 4 : 2) scan_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
                                                                      const double* __restrict__ carry, uint64_t lines,
                                                                      uint64_t n, void* scratch) {
     ovl::scan_lines<float, double, Op, 4, ALIGNED, HAS_CARRY, LOOKBACK>(in, out, carry, lines, n, scratch);
+}
+
+template <class Op, bool ALIGNED, bool HAS_CARRY>
+__global__ void __launch_bounds__(ovl::kScanBlockLookback, 4) scan_f32_wave_kernel(const float* __restrict__ in,
+                                                                                  float* __restrict__ out,
+                                                                                  const double* __restrict__ carry, uint64_t n,
+                                                                                  void* scratch) {
+    ovl::scan_long_line<float, double, Op, 4, ALIGNED, HAS_CARRY>(in, out, carry, n, scratch);
 }
 
 template <class Op, bool ALIGNED>
@@ -301,7 +326,11 @@ __global__ void __launch_bounds__(ovl::kScanBlock) reduce_f32_kernel(const float
     ovl::reduce_all<float, double, Op, 4, ALIGNED>(in, n, out_total, scratch);
 }
 
+// a line of at most kTile elements is one tile; longer lines are cut into tiles of kTileLookback elements
 constexpr uint64_t kTile = (uint64_t)ovl::kScanBlock * ovl::kScanVpt * 4;
+constexpr uint64_t kTileLookback = (uint64_t)ovl::kScanBlockLookback * ovl::kScanVpt * 4;
+
+inline uint64_t tiles_per_line(uint64_t n) { return n <= kTile ? 1 : (n + kTileLookback - 1) / kTileLookback; }
 
 int sm_count_cached() {
     static int sms = 0;
@@ -317,25 +346,53 @@ int sm_count_cached() {
 }
 
 template <class Op, bool ALIGNED, bool HAS_CARRY>
-void launch_scan_lb(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
-                    uint32_t grid, bool lookback, cudaStream_t stream) {
-    if (lookback)
-        scan_f32_kernel<Op, ALIGNED, HAS_CARRY, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
-    else
+cudaError_t launch_scan_lb(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
+                           uint64_t tiles, bool lookback, cudaStream_t stream) {
+    const uint64_t sms = (uint64_t)sm_count_cached();
+    if (!lookback) {
+        const uint64_t max_grid = sms * 2;
+        const uint32_t grid = (uint32_t)(tiles < max_grid ? tiles : max_grid);
         scan_f32_kernel<Op, ALIGNED, HAS_CARRY, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
+        return cudaGetLastError();
+    }
+    if (lines == 1) {
+        // one long line: wave scan (cooperative launch, at most kWaveMaxBlocks resident blocks)
+        auto wave_kernel = scan_f32_wave_kernel<Op, ALIGNED, HAS_CARRY>;
+        int wave_per_sm = 0;
+        cudaError_t we = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&wave_per_sm, wave_kernel, ovl::kScanBlockLookback, 0);
+        if (we != cudaSuccess) return we;
+        if (wave_per_sm < 1) return cudaErrorLaunchOutOfResources;
+        uint64_t cap = sms * (uint64_t)wave_per_sm;
+        if (cap > (uint64_t)ovl::kWaveMaxBlocks) cap = ovl::kWaveMaxBlocks;
+        const uint32_t wave_grid = (uint32_t)(tiles < cap ? tiles : cap);
+        void* wave_args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&n, (void*)&scratch};
+        return cudaLaunchCooperativeKernel((const void*)wave_kernel, dim3(wave_grid), dim3(ovl::kScanBlockLookback), wave_args,
+                                           0, stream);
+    }
+    // look-back: blocks wait for each other's aggregates, so all of them must be resident at once - a
+    // cooperative launch with the grid clamped to what the device holds
+    auto kernel = scan_f32_kernel<Op, ALIGNED, HAS_CARRY, true>;
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, ovl::kScanBlockLookback, 0);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+    const uint64_t max_grid = sms * (uint64_t)per_sm;
+    const uint32_t grid = (uint32_t)(tiles < max_grid ? tiles : max_grid);
+    void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&lines, (void*)&n, (void*)&scratch};
+    return cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(ovl::kScanBlockLookback), args, 0, stream);
 }
 
 template <class Op>
-int launch_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, uint32_t grid,
+int launch_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, uint64_t tiles,
                 bool aligned, bool lookback, cudaStream_t stream) {
+    cudaError_t e;
     if (aligned) {
-        if (carry) launch_scan_lb<Op, true, true>(in, out, lines, n, carry, scratch, grid, lookback, stream);
-        else launch_scan_lb<Op, true, false>(in, out, lines, n, carry, scratch, grid, lookback, stream);
+        if (carry) e = launch_scan_lb<Op, true, true>(in, out, lines, n, carry, scratch, tiles, lookback, stream);
+        else e = launch_scan_lb<Op, true, false>(in, out, lines, n, carry, scratch, tiles, lookback, stream);
     } else {
-        if (carry) launch_scan_lb<Op, false, true>(in, out, lines, n, carry, scratch, grid, lookback, stream);
-        else launch_scan_lb<Op, false, false>(in, out, lines, n, carry, scratch, grid, lookback, stream);
+        if (carry) e = launch_scan_lb<Op, false, true>(in, out, lines, n, carry, scratch, tiles, lookback, stream);
+        else e = launch_scan_lb<Op, false, false>(in, out, lines, n, carry, scratch, tiles, lookback, stream);
     }
-    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return cuda_fail(e);
     return OVL_OK;
 }
@@ -343,8 +400,8 @@ int launch_scan(const float* in, float* out, uint64_t lines, uint64_t n, const d
 }  // namespace
 
 extern "C" uint64_t ovl_scan_f32_scratch_bytes(uint64_t lines, uint64_t n) {
-    const uint64_t tiles = ((n + kTile - 1) / kTile) * lines;
-    return ovl::scan_scratch_bytes<double>(tiles);
+    if (lines == 1 && n > kTile) return ovl::wave_scratch_bytes();   // one long line: two wave buffers
+    return ovl::scan_scratch_bytes<double>(tiles_per_line(n) * lines);
 }
 
 extern "C" int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines, uint64_t n, const double* carry,
@@ -355,17 +412,15 @@ extern "C" int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines,
     if (carry && lines != 1) return OVL_ERR_INVALID;
     const uint64_t need = ovl_scan_f32_scratch_bytes(lines, n);
     if (!scratch || scratch_bytes < need || ((uintptr_t)scratch % 16) != 0) return OVL_ERR_SCRATCH;
-    const uint64_t tiles = ((n + kTile - 1) / kTile) * lines;
+    const uint64_t tiles = tiles_per_line(n) * lines;
     if (tiles >= (1ull << 32) - 65536) return OVL_ERR_TOO_LARGE;   // the tile counter is 32 bits wide
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const bool aligned = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0) && (lines == 1 || n % 4 == 0);
     const bool lookback = n > kTile;
-    const uint64_t max_grid = (uint64_t)sm_count_cached() * 2;     // two resident blocks of 512 threads per SM
-    const uint32_t grid = (uint32_t)(tiles < max_grid ? tiles : max_grid);
     // lines of at most one tile publish nothing: only the header (status word) has to be clear
     OVL_CUDA(cudaMemsetAsync(scratch, 0, lookback ? need : sizeof(ovl::ScanHeader), stream));
-    if (op == 0) return launch_scan<ovl::OpAdd>(in, out, lines, n, carry, scratch, grid, aligned, lookback, stream);
-    return launch_scan<ovl::OpMul>(in, out, lines, n, carry, scratch, grid, aligned, lookback, stream);
+    if (op == 0) return launch_scan<ovl::OpAdd>(in, out, lines, n, carry, scratch, tiles, aligned, lookback, stream);
+    return launch_scan<ovl::OpMul>(in, out, lines, n, carry, scratch, tiles, aligned, lookback, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -406,9 +461,9 @@ extern "C" int ovl_scan_f32_static(int op, const float* in, float* out, uint64_t
     if (lines == 0 || n == 0) return OVL_ERR_INVALID;
     if (carry && lines != 1) return OVL_ERR_INVALID;
     // size check first, in a form that cannot overflow
-    const uint64_t tiles_per_line = (n + kTile - 1) / kTile;
+    const uint64_t per_line = tiles_per_line(n);
     const uint64_t max_tiles = (OVL_SCAN_STATIC_SCRATCH_BYTES - sizeof(ovl::ScanHeader)) / sizeof(ovl::TileDesc<double>);
-    if (tiles_per_line > max_tiles || lines > max_tiles / tiles_per_line) return OVL_ERR_TOO_LARGE;
+    if (per_line > max_tiles || lines > max_tiles / per_line) return OVL_ERR_TOO_LARGE;
     void* scratch = nullptr;
     int st = static_scratch_address(&scratch);
     if (st != OVL_OK) return st;

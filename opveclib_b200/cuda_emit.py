@@ -40,12 +40,14 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv5'
+TEMPLATE_VERSION = 'tv10'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
+SCAN_BLOCK_LOOKBACK = 256
 SCAN_VPT = 4
 SCAN_HEADER_BYTES = 16
+WAVE_MAX_BLOCKS = 1024      # kWaveMaxBlocks
 
 
 def ctype(dtype):
@@ -429,23 +431,31 @@ def emit_cuda(kernel, name):
         acc = 'double' if spec.dtype.is_float else t
         acc_size = 8 if spec.dtype.is_float else spec.dtype.itemsize
         vec = max(1, min(4, 16 // spec.dtype.itemsize))
-        tile = SCAN_BLOCK * SCAN_VPT * vec
-        tiles = ((spec.n + tile - 1) // tile) * spec.lines
+        lookback = spec.n > SCAN_BLOCK * SCAN_VPT * vec
+        block = SCAN_BLOCK_LOOKBACK if lookback else SCAN_BLOCK
+        tile = block * SCAN_VPT * vec
+        tiles = ((spec.n + tile - 1) // tile if lookback else 1) * spec.lines
         desc = 32 if acc_size == 8 else 16
-        scratch = SCAN_HEADER_BYTES + tiles * desc
+        wave = lookback and spec.lines == 1
+        scratch = SCAN_HEADER_BYTES + (2 * WAVE_MAX_BLOCKS * 16 if wave else tiles * desc)
         op = 'ovl::OpAdd' if spec.op == 'add' else 'ovl::OpMul'
         can_align = spec.lines == 1 or spec.n % vec == 0
         variants = [('scanu', 'false')] + ([('scan', 'true')] if can_align else [])
-        lookback = spec.n > tile
         for suffix, aligned in variants:
-            src += ['extern "C" __global__ void __launch_bounds__(' + str(SCAN_BLOCK) + ', 2) ' + name + '_' + suffix +
-                    '(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0, void* scratch) {',
-                    '    ovl::scan_lines<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned +
-                    ', false, ' + ('true' if lookback else 'false') + '>(in0, out0, nullptr, ' + str(spec.lines) +
-                    'ull, ' + str(spec.n) + 'ull, scratch);',
-                    '}', '']
+            head = 'extern "C" __global__ void __launch_bounds__(' + str(block) + ', ' + ('4' if lookback else '2') + \
+                ') ' + name + '_' + suffix + '(const ' + t + '* __restrict__ in0, ' + t + \
+                '* __restrict__ out0, void* scratch) {'
+            if wave:
+                call = '    ovl::scan_long_line<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned + \
+                    ', false>(in0, out0, nullptr, ' + str(spec.n) + 'ull, scratch);'
+            else:
+                call = '    ovl::scan_lines<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned + \
+                    ', false, ' + ('true' if lookback else 'false') + '>(in0, out0, nullptr, ' + str(spec.lines) + \
+                    'ull, ' + str(spec.n) + 'ull, scratch);'
+            src += [head, call, '}', '']
         meta['scan'] = {'symbol': name + '_scan' if can_align else None, 'symbol_unaligned': name + '_scanu',
-                        'block': SCAN_BLOCK, 'tiles': tiles, 'scratch_bytes': scratch,
-                        'zero_bytes': scratch if lookback else SCAN_HEADER_BYTES, 'blocks_per_sm': 2,
+                        'block': block, 'tiles': tiles, 'scratch_bytes': scratch,
+                        'zero_bytes': scratch if lookback else SCAN_HEADER_BYTES, 'blocks_per_sm': 4 if lookback else 2,
+                        'lookback': bool(lookback), 'max_grid': WAVE_MAX_BLOCKS if wave else None,
                         'align_bytes': vec * spec.dtype.itemsize, 'lines': spec.lines, 'n': spec.n, 'op': spec.op}
     return '\n'.join(src), meta

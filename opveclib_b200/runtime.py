@@ -62,6 +62,7 @@ class KernelPlan(object):
         sms = self._sm_count(device)
         aligns = [0] * len(dtypes)
         scratch = zero = 0
+        cooperative = 0
         if which in ('gen', 'vec'):
             m = meta[which]
             block = m['block']
@@ -73,12 +74,13 @@ class KernelPlan(object):
         else:
             m = meta['scan']
             block = m['block']
-            grid = max(1, min(m['tiles'], sms * m.get('blocks_per_sm', 2)))
+            grid = max(1, min(m['tiles'], sms * m.get('blocks_per_sm', 2), m.get('max_grid') or (1 << 30)))
             symbol = m['symbol'] if which == 'scan' else m['symbol_unaligned']
             scratch, zero = m['scratch_bytes'], m['zero_bytes']
+            cooperative = 1 if m.get('lookback') else 0
             if which == 'scan':
                 aligns = [m['align_bytes']] * len(dtypes)
-        k = launcher.Kernel(self._module(device), symbol, grid, block, dtypes, lens, n_in, aligns, scratch, zero)
+        k = launcher.Kernel(self._module(device), symbol, grid, block, dtypes, lens, n_in, aligns, scratch, zero, 0, cooperative)
         self._variants[key] = k
         return k
 

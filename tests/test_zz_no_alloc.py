@@ -41,7 +41,7 @@ def test_static_scratch_scan_matches_regular_scan_on_two_calls_in_a_row():
     lib = launcher.library()
     gen = torch.Generator(device='cuda')
     gen.manual_seed(77)
-    # first call: many lines of two tiles each, sum; leaves 600 descriptors behind in the shared array
+    # first call: many lines of three tiles each, sum; leaves 900 descriptors behind in the shared array
     a = torch.empty((300, 9000), dtype=torch.float32, device='cuda').normal_(0, 1, generator=gen)
     got, want = _scan_both(lib, torch, 0, a)
     assert np.array_equal(got, want)
