@@ -123,13 +123,25 @@ int ovl_read_kernel_status(const void* scratch, void* cuda_stream, int32_t* out_
 
 /* Built-in scans ----------------------------------------------------------------------------------------- */
 /* Inclusive scan (op: 0 = sum, 1 = product) of `lines` contiguous lines of `n` fp32 elements each, device
- * memory in and out, with the same cooperative single-pass kernel the code generator uses for recognised
- * accumulate loops (the reference's one-worker-per-line loop: opveclib/examples/test_accumulate.py:22-78).
+ * memory in and out, with the same cooperative kernels the code generator uses for recognised accumulate loops
+ * (the reference's one-worker-per-line loop: opveclib/examples/test_accumulate.py:22-78).  Accumulation is in
+ * fp64.  Lines of at most 8192 elements are scanned in one pass by one thread block each; longer lines in three
+ * streaming passes (tile aggregates, prefixes of the aggregates, seeded tile scans) or, with the environment
+ * variable OVL_SCAN_MODE=lookback, in a single pass with decoupled look-back.
  * `carry` (device pointer to one double, or NULL) is combined into every element of a single line (lines
  * must be 1 when it is given).  `scratch` must hold ovl_scan_f32_scratch_bytes(lines, n) bytes. */
 uint64_t ovl_scan_f32_scratch_bytes(uint64_t lines, uint64_t n);
 int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
                  uint64_t scratch_bytes, void* cuda_stream);
+/* The same scan of ONE line split at the point where ranks of a sharded scan exchange their totals:
+ * ovl_scan_f32_begin reads the shard once, keeps the per-tile aggregates in `scratch` and writes the shard's
+ * total to *out_total (device memory); after the carry has been formed from the totals of the ranks before,
+ * ovl_scan_f32_finish produces the result.  The pair moves 12 bytes per element, like ovl_scan_f32 on a long
+ * line, so a shard costs the same whether or not a carry exchange sits in the middle. */
+int ovl_scan_f32_begin(int op, const float* in, uint64_t n, double* out_total, void* scratch, uint64_t scratch_bytes,
+                       void* cuda_stream);
+int ovl_scan_f32_finish(int op, const float* in, float* out, uint64_t n, const double* carry, void* scratch,
+                        uint64_t scratch_bytes, void* cuda_stream);
 /* Reduce `n` fp32 elements to one double (sum or product, fixed combination order): the shard total that
  * ranks exchange before a scan that crosses shard boundaries.  `scratch` must hold
  * ovl_reduce_f32_scratch_bytes(n) bytes. */

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include <mutex>
 #include <string>
@@ -305,19 +306,26 @@ extern "C" int ovl_read_kernel_status(const void* scratch, void* cuda_stream, in
 
 namespace {
 
-template <class Op, bool ALIGNED, bool HAS_CARRY, bool LOOKBACK>
-__global__ void __launch_bounds__(LOOKBACK ? ovl::kScanBlockLookback : ovl::kScanBlock, LOOKBACK ? 4 : 2) scan_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
-                                                                     const double* __restrict__ carry, uint64_t lines,
-                                                                     uint64_t n, void* scratch) {
-    ovl::scan_lines<float, double, Op, 4, ALIGNED, HAS_CARRY, LOOKBACK>(in, out, carry, lines, n, scratch);
+template <class Op, bool ALIGNED, bool HAS_CARRY, int MODE>
+__global__ void __launch_bounds__(MODE == ovl::kScanLookback ? ovl::kScanBlockLookback : ovl::kScanBlock,
+                                  MODE == ovl::kScanLookback ? 4 : 2)
+    scan_f32_kernel(const float* __restrict__ in, float* __restrict__ out, const double* __restrict__ carry, uint64_t lines,
+                    uint64_t n, void* scratch) {
+    ovl::scan_lines<float, double, Op, 4, ALIGNED, HAS_CARRY, MODE>(in, out, carry, lines, n, scratch);
 }
 
-template <class Op, bool ALIGNED, bool HAS_CARRY>
-__global__ void __launch_bounds__(ovl::kScanBlockLookback, 4) scan_f32_wave_kernel(const float* __restrict__ in,
-                                                                                  float* __restrict__ out,
-                                                                                  const double* __restrict__ carry, uint64_t n,
-                                                                                  void* scratch) {
-    ovl::scan_long_line<float, double, Op, 4, ALIGNED, HAS_CARRY>(in, out, carry, n, scratch);
+template <class Op, bool ALIGNED>
+__global__ void __launch_bounds__(ovl::kScanBlock, 2) tile_aggregates_f32_kernel(const float* __restrict__ in, uint64_t lines,
+                                                                                uint64_t n, double* __restrict__ agg) {
+    ovl::tile_aggregates<float, double, Op, 4, ALIGNED>(in, lines, n, agg);
+}
+
+template <class Op, bool HAS_CARRY, bool WRITE_PREFIX>
+__global__ void __launch_bounds__(ovl::kScanBlock) scan_aggregates_f64_kernel(double* __restrict__ agg, uint64_t lines,
+                                                                             uint64_t tiles_per_line,
+                                                                             const double* __restrict__ carry,
+                                                                             double* __restrict__ total_out) {
+    ovl::scan_aggregates<double, Op, HAS_CARRY, WRITE_PREFIX>(agg, lines, tiles_per_line, carry, total_out);
 }
 
 template <class Op, bool ALIGNED>
@@ -326,11 +334,16 @@ __global__ void __launch_bounds__(ovl::kScanBlock) reduce_f32_kernel(const float
     ovl::reduce_all<float, double, Op, 4, ALIGNED>(in, n, out_total, scratch);
 }
 
-// a line of at most kTile elements is one tile; longer lines are cut into tiles of kTileLookback elements
+// a line of at most kTile elements is one tile; longer lines are cut into tiles of kTile elements (three-pass
+// scan) or kTileLookback elements (single-pass look-back scan)
 constexpr uint64_t kTile = (uint64_t)ovl::kScanBlock * ovl::kScanVpt * 4;
 constexpr uint64_t kTileLookback = (uint64_t)ovl::kScanBlockLookback * ovl::kScanVpt * 4;
 
-inline uint64_t tiles_per_line(uint64_t n) { return n <= kTile ? 1 : (n + kTileLookback - 1) / kTileLookback; }
+inline uint64_t tiles_per_line(uint64_t n, bool lookback) {
+    if (n <= kTile) return 1;
+    const uint64_t t = lookback ? kTileLookback : kTile;
+    return (n + t - 1) / t;
+}
 
 int sm_count_cached() {
     static int sms = 0;
@@ -345,82 +358,176 @@ int sm_count_cached() {
     return sms;
 }
 
+// OVL_SCAN_MODE=lookback selects the single-pass decoupled look-back kernel for lines of several tiles; the
+// default is the three-pass scan, which is faster on this device (no waiting between thread blocks)
+bool use_lookback() {
+    static int cached = -1;
+    if (cached < 0) {
+        const char* e = getenv("OVL_SCAN_MODE");
+        cached = (e && strcmp(e, "lookback") == 0) ? 1 : 0;
+    }
+    return cached == 1;
+}
+
+inline uint32_t clamp_grid(uint64_t tiles, uint64_t per_sm) {
+    const uint64_t cap = (uint64_t)sm_count_cached() * per_sm;
+    const uint64_t g = tiles < cap ? tiles : cap;
+    return (uint32_t)(g ? g : 1);
+}
+
+// pass 1 of the three-pass scan: per-tile aggregates into the scratch (after the header)
+template <class Op>
+cudaError_t launch_tile_aggregates(const float* in, uint64_t lines, uint64_t n, void* scratch, bool aligned,
+                                   cudaStream_t stream) {
+    double* agg = reinterpret_cast<double*>(reinterpret_cast<char*>(scratch) + sizeof(ovl::ScanHeader));
+    const uint32_t grid = clamp_grid(tiles_per_line(n, false) * lines, 2);
+    if (aligned) tile_aggregates_f32_kernel<Op, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, lines, n, agg);
+    else tile_aggregates_f32_kernel<Op, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, lines, n, agg);
+    return cudaGetLastError();
+}
+
+// pass 2: exclusive prefixes of the aggregates (optionally seeded with the carry), and/or the line totals
+template <class Op>
+cudaError_t launch_scan_aggregates(void* scratch, uint64_t lines, uint64_t n, const double* carry, double* total_out,
+                                   bool write_prefix, cudaStream_t stream) {
+    double* agg = reinterpret_cast<double*>(reinterpret_cast<char*>(scratch) + sizeof(ovl::ScanHeader));
+    const uint64_t tpl = tiles_per_line(n, false);
+    const uint32_t grid = clamp_grid(lines, 4);
+    if (write_prefix) {
+        if (carry) scan_aggregates_f64_kernel<Op, true, true><<<grid, ovl::kScanBlock, 0, stream>>>(agg, lines, tpl, carry, total_out);
+        else scan_aggregates_f64_kernel<Op, false, true><<<grid, ovl::kScanBlock, 0, stream>>>(agg, lines, tpl, carry, total_out);
+    } else {
+        scan_aggregates_f64_kernel<Op, false, false><<<grid, ovl::kScanBlock, 0, stream>>>(agg, lines, tpl, carry, total_out);
+    }
+    return cudaGetLastError();
+}
+
 template <class Op, bool ALIGNED, bool HAS_CARRY>
-cudaError_t launch_scan_lb(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
-                           uint64_t tiles, bool lookback, cudaStream_t stream) {
-    const uint64_t sms = (uint64_t)sm_count_cached();
-    if (!lookback) {
-        const uint64_t max_grid = sms * 2;
-        const uint32_t grid = (uint32_t)(tiles < max_grid ? tiles : max_grid);
-        scan_f32_kernel<Op, ALIGNED, HAS_CARRY, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, out, carry, lines, n, scratch);
+cudaError_t launch_scan_mode(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
+                             int mode, cudaStream_t stream) {
+    if (mode == ovl::kScanOneTile) {
+        scan_f32_kernel<Op, ALIGNED, HAS_CARRY, ovl::kScanOneTile><<<clamp_grid(lines, 2), ovl::kScanBlock, 0, stream>>>(
+            in, out, carry, lines, n, scratch);
         return cudaGetLastError();
     }
-    if (lines == 1) {
-        // one long line: wave scan (cooperative launch, at most kWaveMaxBlocks resident blocks)
-        auto wave_kernel = scan_f32_wave_kernel<Op, ALIGNED, HAS_CARRY>;
-        int wave_per_sm = 0;
-        cudaError_t we = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&wave_per_sm, wave_kernel, ovl::kScanBlockLookback, 0);
-        if (we != cudaSuccess) return we;
-        if (wave_per_sm < 1) return cudaErrorLaunchOutOfResources;
-        uint64_t cap = sms * (uint64_t)wave_per_sm;
-        if (cap > (uint64_t)ovl::kWaveMaxBlocks) cap = ovl::kWaveMaxBlocks;
-        const uint32_t wave_grid = (uint32_t)(tiles < cap ? tiles : cap);
-        void* wave_args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&n, (void*)&scratch};
-        return cudaLaunchCooperativeKernel((const void*)wave_kernel, dim3(wave_grid), dim3(ovl::kScanBlockLookback), wave_args,
-                                           0, stream);
+    if (mode == ovl::kScanPrefixed) {
+        scan_f32_kernel<Op, ALIGNED, false, ovl::kScanPrefixed>
+            <<<clamp_grid(tiles_per_line(n, false) * lines, 2), ovl::kScanBlock, 0, stream>>>(in, out, nullptr, lines, n, scratch);
+        return cudaGetLastError();
     }
     // look-back: blocks wait for each other's aggregates, so all of them must be resident at once - a
     // cooperative launch with the grid clamped to what the device holds
-    auto kernel = scan_f32_kernel<Op, ALIGNED, HAS_CARRY, true>;
+    auto kernel = scan_f32_kernel<Op, ALIGNED, HAS_CARRY, ovl::kScanLookback>;
     int per_sm = 0;
     cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, ovl::kScanBlockLookback, 0);
     if (e != cudaSuccess) return e;
     if (per_sm < 1) return cudaErrorLaunchOutOfResources;
-    const uint64_t max_grid = sms * (uint64_t)per_sm;
-    const uint32_t grid = (uint32_t)(tiles < max_grid ? tiles : max_grid);
+    const uint32_t grid = clamp_grid(tiles_per_line(n, true) * lines, (uint64_t)per_sm);
     void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&lines, (void*)&n, (void*)&scratch};
     return cudaLaunchCooperativeKernel((const void*)kernel, dim3(grid), dim3(ovl::kScanBlockLookback), args, 0, stream);
 }
 
 template <class Op>
-int launch_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, uint64_t tiles,
-                bool aligned, bool lookback, cudaStream_t stream) {
-    cudaError_t e;
+cudaError_t launch_scan_pass(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
+                             bool aligned, int mode, cudaStream_t stream) {
     if (aligned) {
-        if (carry) e = launch_scan_lb<Op, true, true>(in, out, lines, n, carry, scratch, tiles, lookback, stream);
-        else e = launch_scan_lb<Op, true, false>(in, out, lines, n, carry, scratch, tiles, lookback, stream);
-    } else {
-        if (carry) e = launch_scan_lb<Op, false, true>(in, out, lines, n, carry, scratch, tiles, lookback, stream);
-        else e = launch_scan_lb<Op, false, false>(in, out, lines, n, carry, scratch, tiles, lookback, stream);
+        if (carry) return launch_scan_mode<Op, true, true>(in, out, lines, n, carry, scratch, mode, stream);
+        return launch_scan_mode<Op, true, false>(in, out, lines, n, carry, scratch, mode, stream);
     }
-    if (e != cudaSuccess) return cuda_fail(e);
+    if (carry) return launch_scan_mode<Op, false, true>(in, out, lines, n, carry, scratch, mode, stream);
+    return launch_scan_mode<Op, false, false>(in, out, lines, n, carry, scratch, mode, stream);
+}
+
+int check_scan_args(int op, const void* in, uint64_t lines, uint64_t n, const double* carry, const void* scratch,
+                    uint64_t scratch_bytes) {
+    if (!in) return OVL_ERR_NULL;
+    if (op != 0 && op != 1) return OVL_ERR_INVALID;
+    if (lines == 0 || n == 0) return OVL_ERR_INVALID;
+    if (carry && lines != 1) return OVL_ERR_INVALID;
+    if (!scratch || scratch_bytes < ovl_scan_f32_scratch_bytes(lines, n) || ((uintptr_t)scratch % 16) != 0)
+        return OVL_ERR_SCRATCH;
+    if (tiles_per_line(n, true) * lines >= (1ull << 32) - 65536) return OVL_ERR_TOO_LARGE;
     return OVL_OK;
 }
 
 }  // namespace
 
 extern "C" uint64_t ovl_scan_f32_scratch_bytes(uint64_t lines, uint64_t n) {
-    if (lines == 1 && n > kTile) return ovl::wave_scratch_bytes();   // one long line: two wave buffers
-    return ovl::scan_scratch_bytes<double>(tiles_per_line(n) * lines);
+    // header + one 32-byte slot per tile; sized for the finer (look-back) tiling so either scan mode fits
+    return ovl::scan_scratch_bytes<double>(tiles_per_line(n, true) * lines);
 }
+
+namespace {
+
+// second half of a scan: prefixes of the tile aggregates (seeded with the carry), then the seeded tile scans
+template <class Op>
+int finish_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, bool aligned,
+                cudaStream_t stream) {
+    cudaError_t e = launch_scan_aggregates<Op>(scratch, lines, n, carry, nullptr, true, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = launch_scan_pass<Op>(in, out, lines, n, nullptr, scratch, aligned, ovl::kScanPrefixed, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return OVL_OK;
+}
+
+template <class Op>
+int run_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, bool aligned,
+             cudaStream_t stream) {
+    if (n <= kTile) {
+        cudaError_t e = launch_scan_pass<Op>(in, out, lines, n, carry, scratch, aligned, ovl::kScanOneTile, stream);
+        return e == cudaSuccess ? OVL_OK : cuda_fail(e);
+    }
+    if (use_lookback()) {
+        // the descriptors must start out empty
+        OVL_CUDA(cudaMemsetAsync(scratch, 0, ovl_scan_f32_scratch_bytes(lines, n), stream));
+        cudaError_t e = launch_scan_pass<Op>(in, out, lines, n, carry, scratch, aligned, ovl::kScanLookback, stream);
+        return e == cudaSuccess ? OVL_OK : cuda_fail(e);
+    }
+    cudaError_t e = launch_tile_aggregates<Op>(in, lines, n, scratch, aligned, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return finish_scan<Op>(in, out, lines, n, carry, scratch, aligned, stream);
+}
+
+}  // namespace
 
 extern "C" int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines, uint64_t n, const double* carry,
                             void* scratch, uint64_t scratch_bytes, void* cuda_stream) {
-    if (!in || !out) return OVL_ERR_NULL;
-    if (op != 0 && op != 1) return OVL_ERR_INVALID;
-    if (lines == 0 || n == 0) return OVL_ERR_INVALID;
-    if (carry && lines != 1) return OVL_ERR_INVALID;
-    const uint64_t need = ovl_scan_f32_scratch_bytes(lines, n);
-    if (!scratch || scratch_bytes < need || ((uintptr_t)scratch % 16) != 0) return OVL_ERR_SCRATCH;
-    const uint64_t tiles = tiles_per_line(n) * lines;
-    if (tiles >= (1ull << 32) - 65536) return OVL_ERR_TOO_LARGE;   // the tile counter is 32 bits wide
+    if (!out) return OVL_ERR_NULL;
+    int st = check_scan_args(op, in, lines, n, carry, scratch, scratch_bytes);
+    if (st != OVL_OK) return st;
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const bool aligned = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0) && (lines == 1 || n % 4 == 0);
-    const bool lookback = n > kTile;
-    // lines of at most one tile publish nothing: only the header (status word) has to be clear
-    OVL_CUDA(cudaMemsetAsync(scratch, 0, lookback ? need : sizeof(ovl::ScanHeader), stream));
-    if (op == 0) return launch_scan<ovl::OpAdd>(in, out, lines, n, carry, scratch, tiles, aligned, lookback, stream);
-    return launch_scan<ovl::OpMul>(in, out, lines, n, carry, scratch, tiles, aligned, lookback, stream);
+    OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader), stream));   // status word
+    if (op == 0) return run_scan<ovl::OpAdd>(in, out, lines, n, carry, scratch, aligned, stream);
+    return run_scan<ovl::OpMul>(in, out, lines, n, carry, scratch, aligned, stream);
+}
+
+extern "C" int ovl_scan_f32_begin(int op, const float* in, uint64_t n, double* out_total, void* scratch,
+                                  uint64_t scratch_bytes, void* cuda_stream) {
+    if (!out_total) return OVL_ERR_NULL;
+    int st = check_scan_args(op, in, 1, n, nullptr, scratch, scratch_bytes);
+    if (st != OVL_OK) return st;
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const bool aligned = ((uintptr_t)in % 16 == 0);
+    OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader), stream));
+    cudaError_t e = (op == 0) ? launch_tile_aggregates<ovl::OpAdd>(in, 1, n, scratch, aligned, stream)
+                              : launch_tile_aggregates<ovl::OpMul>(in, 1, n, scratch, aligned, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    e = (op == 0) ? launch_scan_aggregates<ovl::OpAdd>(scratch, 1, n, nullptr, out_total, false, stream)
+                  : launch_scan_aggregates<ovl::OpMul>(scratch, 1, n, nullptr, out_total, false, stream);
+    if (e != cudaSuccess) return cuda_fail(e);
+    return OVL_OK;
+}
+
+extern "C" int ovl_scan_f32_finish(int op, const float* in, float* out, uint64_t n, const double* carry, void* scratch,
+                                   uint64_t scratch_bytes, void* cuda_stream) {
+    if (!out) return OVL_ERR_NULL;
+    int st = check_scan_args(op, in, 1, n, carry, scratch, scratch_bytes);
+    if (st != OVL_OK) return st;
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const bool aligned = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    if (op == 0) return finish_scan<ovl::OpAdd>(in, out, 1, n, carry, scratch, aligned, stream);
+    return finish_scan<ovl::OpMul>(in, out, 1, n, carry, scratch, aligned, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -461,7 +568,7 @@ extern "C" int ovl_scan_f32_static(int op, const float* in, float* out, uint64_t
     if (lines == 0 || n == 0) return OVL_ERR_INVALID;
     if (carry && lines != 1) return OVL_ERR_INVALID;
     // size check first, in a form that cannot overflow
-    const uint64_t per_line = tiles_per_line(n);
+    const uint64_t per_line = tiles_per_line(n, true);
     const uint64_t max_tiles = (OVL_SCAN_STATIC_SCRATCH_BYTES - sizeof(ovl::ScanHeader)) / sizeof(ovl::TileDesc<double>);
     if (per_line > max_tiles || lines > max_tiles / per_line) return OVL_ERR_TOO_LARGE;
     void* scratch = nullptr;

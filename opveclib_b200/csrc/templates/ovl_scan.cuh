@@ -28,6 +28,7 @@ constexpr int kScanVpt = 4;              // 128-bit vectors per thread
 constexpr int kScanLookbackWarps = 8;    // look-back windows (of 32 tiles each) inspected in parallel
 constexpr uint32_t kScanSpinLimit = 1u << 22;
 constexpr int32_t kErrTimeout = 8;  // OVL_ERR_TIMEOUT
+constexpr int kScanOneTile = 0, kScanLookback = 1, kScanPrefixed = 2;
 
 struct OpAdd {
     template <typename A> static __device__ __forceinline__ A identity() { return A(0); }
@@ -144,14 +145,20 @@ __device__ __forceinline__ void fetch_tile(Vec<T, VEC> (*stage)[BLOCK], T (&raw)
 // One launch scans `lines` lines of `n` elements.
 //  ALIGNED    every line start is VEC-aligned (n % VEC == 0 or a single line) and the base pointers are 16-byte
 //             aligned, so whole vectors move with one instruction.
-//  LOOKBACK   lines are longer than one tile.  false: one tile per line, tiles are handed out statically
-//             (blockIdx, blockIdx + gridDim, ...), nothing is published and no block ever waits for another.
-//             true: tiles are claimed in order from the atomic counter and prefixes travel through descriptors.
-// While a block works on one tile, the data of its next tile is already on its way into shared memory
+//  MODE       kScanOneTile: every line fits one tile; nothing is published, no block waits for another.
+//             kScanPrefixed: lines are cut into several tiles and the prefix in front of every tile is already
+//             known (array of Acc after the scratch header, written by tile_aggregates + scan_aggregates); again
+//             no block waits for another.
+//             kScanLookback: several tiles per line, single pass: prefixes travel from tile to tile through
+//             descriptors (decoupled look-back); blocks wait for the aggregates of earlier tiles, so the whole
+//             grid must be resident (cooperative launch).
+// Tiles are handed out statically (blockIdx, blockIdx + gridDim, ...).  While a block works on one tile, the data of its next tile is already on its way into shared memory
 // (cp.async), so global loads overlap the scan, the look-back and the stores of the current tile.
-template <typename T, typename Acc, class Op, int VEC, bool ALIGNED, bool HAS_CARRY, bool LOOKBACK>
+template <typename T, typename Acc, class Op, int VEC, bool ALIGNED, bool HAS_CARRY, int MODE>
 __device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry,
                                            const uint64_t lines, const uint64_t n, void* scratch) {
+    constexpr bool LOOKBACK = MODE == kScanLookback;
+    constexpr bool PREFIXED = MODE == kScanPrefixed;
     constexpr int BLOCK = LOOKBACK ? kScanBlockLookback : kScanBlock;
     constexpr int VPT = kScanVpt;
     constexpr int WARPS = BLOCK / 32;
@@ -161,7 +168,8 @@ __device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restri
 
     ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
     TileDesc<Acc>* desc = reinterpret_cast<TileDesc<Acc>*>(hdr + 1);
-    const uint64_t tiles_per_line = LOOKBACK ? (n + TILE - 1) / TILE : 1;
+    const Acc* tile_prefix = reinterpret_cast<const Acc*>(hdr + 1);
+    const uint64_t tiles_per_line = (LOOKBACK || PREFIXED) ? (n + TILE - 1) / TILE : 1;
     const uint64_t total_tiles = tiles_per_line * lines;
 
     __shared__ Vec<T, VEC> s_stage[VPT][BLOCK];   // staging slots, [j][thread]
@@ -237,7 +245,9 @@ __device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restri
 
         // ---- prefix of the tiles to the left inside the line
         Acc exclusive = Op::template identity<Acc>();
-        if (tile_in_line == 0) {
+        if (PREFIXED) {
+            exclusive = tile_prefix[tile];      // carry already folded in by scan_aggregates
+        } else if (tile_in_line == 0) {
             if (HAS_CARRY) exclusive = *carry;
             if (LOOKBACK && threadIdx.x == 0) {
                 desc[tile].prefix = Op::apply(exclusive, aggregate);
@@ -334,194 +344,126 @@ __device__ __forceinline__ void scan_lines(const T* __restrict__ in, T* __restri
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// One long line: wave scan.
-//
-// Look-back hands prefixes from tile to tile through L2, a window of descriptors per round trip; for a single
-// line of millions of tiles that relay, not HBM, sets the pace.  Here the blocks of a (cooperative, fully
-// resident) grid advance in waves: in wave w block b owns tile w*G + b.  Every block publishes its tile
-// aggregate in slot b of a wave buffer (16-byte {value, wave tag} written and read as one transaction), then
-// reads ALL G slots of the wave once: the ordered sum of the slots before b is its prefix inside the wave, the
-// sum of all slots advances the running prefix that every block keeps for itself in a register.  Nothing is
-// relayed: one publish and one gather per wave, independent of the line's length.  Two wave buffers alternate;
-// a block can only publish into a buffer again after a complete gather of the wave in between, which in turn
-// needs every block to have finished reading the older wave.
-constexpr int kWaveMaxBlocks = 1024;   // slots per wave buffer
-constexpr int kWaveSlotsPerThread = kWaveMaxBlocks / kScanBlockLookback;
-
-__host__ __device__ constexpr uint64_t wave_scratch_bytes() { return sizeof(ScanHeader) + 2ull * kWaveMaxBlocks * 16ull; }
-
-__device__ __forceinline__ void st_slot(void* p, unsigned long long value_bits, unsigned long long tag) {
-    asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(value_bits), "l"(tag) : "memory");
-}
-__device__ __forceinline__ void ld_slot(const void* p, unsigned long long& value_bits, unsigned long long& tag) {
-    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(value_bits), "=l"(tag) : "l"(p) : "memory");
-}
-template <typename Acc>
-__device__ __forceinline__ unsigned long long acc_bits(Acc v) {
-    unsigned long long b = 0;
-    memcpy(&b, &v, sizeof(Acc));
-    return b;
-}
-template <typename Acc>
-__device__ __forceinline__ Acc bits_acc(unsigned long long b) {
-    Acc v;
-    memcpy(&v, &b, sizeof(Acc));
-    return v;
-}
-
-template <typename T, typename Acc, class Op, int VEC, bool ALIGNED, bool HAS_CARRY>
-__device__ __forceinline__ void scan_long_line(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry,
-                                               const uint64_t n, void* scratch) {
-    constexpr int BLOCK = kScanBlockLookback;
+// Scan in three passes for lines of several tiles, with no waiting between blocks:
+//   tile_aggregates   reads every tile once and writes its reduction (Acc) to agg[tile]            4 B/elem
+//   scan_aggregates   turns agg[] into the exclusive prefix in front of every tile, per line      (tiny)
+//   scan_lines<kScanPrefixed>  scans every tile seeded with its prefix                              8 B/elem
+// Twelve bytes per element instead of the single pass's eight, but every pass streams at copy speed, which on
+// this device beats handing prefixes from block to block through L2.
+template <typename T, typename Acc, class Op, int VEC, bool ALIGNED>
+__device__ __forceinline__ void tile_aggregates(const T* __restrict__ in, const uint64_t lines, const uint64_t n,
+                                                Acc* __restrict__ agg) {
+    constexpr int BLOCK = kScanBlock;
     constexpr int VPT = kScanVpt;
     constexpr int WARPS = BLOCK / 32;
-    constexpr int SPT = kWaveSlotsPerThread;
     constexpr uint32_t TILE = BLOCK * VPT * VEC;
     constexpr uint32_t WARP_ELEMS = 32 * VPT * VEC;
-
-    ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
-    char* slots = reinterpret_cast<char*>(hdr + 1);
-    const uint64_t total_tiles = (n + TILE - 1) / TILE;
-    const uint32_t G = gridDim.x;                      // <= kWaveMaxBlocks, all resident
-    const uint32_t b = blockIdx.x;
-
     __shared__ Vec<T, VEC> s_stage[VPT][BLOCK];
-    __shared__ Acc s_warp_total[2][WARPS];
-    __shared__ Acc s_gather_lt[2][WARPS];
-    __shared__ Acc s_gather_all[2][WARPS];
-
-    const int lane = threadIdx.x & 31;
-    const int wid = threadIdx.x >> 5;
+    __shared__ Acc s_part[2][WARPS];
+    const uint64_t tiles_per_line = (n + TILE - 1) / TILE;
+    const uint64_t total_tiles = tiles_per_line * lines;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     int parity = 0;
-    Acc running = Op::template identity<Acc>();        // prefix of all complete waves so far
-    if (HAS_CARRY) running = *carry;
-
-    uint64_t tile = b;
-    if (tile < total_tiles) stage_tile<T, Op, VEC, VPT, BLOCK, ALIGNED>(in, 0, tile * TILE + (uint64_t)wid * WARP_ELEMS, n, lane, s_stage);
-
-    for (uint64_t wave = 0; wave * G < total_tiles; ++wave, tile += G) {
-        const bool active = tile < total_tiles;
-        const uint64_t remaining = total_tiles - wave * G;
-        const uint32_t in_wave = (uint32_t)(remaining < G ? remaining : G);    // tiles of this wave
-        const uint64_t warp_off = tile * TILE + (uint64_t)wid * WARP_ELEMS;
-
+    uint64_t tile = blockIdx.x;
+    if (tile < total_tiles) {
+        const uint64_t line = tile / tiles_per_line;
+        stage_tile<T, Op, VEC, VPT, BLOCK, ALIGNED>(in, line * n, (tile - line * tiles_per_line) * TILE + (uint64_t)wid * WARP_ELEMS,
+                                                    n, lane, s_stage);
+    }
+    while (tile < total_tiles) {
         T raw[VPT][VEC];
-        Acc base[VPT];
-        Acc warp_excl = Op::template identity<Acc>();
-        if (active) {
-            fetch_tile<T, VEC, VPT, BLOCK>(s_stage, raw);
-            const uint64_t next = tile + G;
-            if (next < total_tiles)
-                stage_tile<T, Op, VEC, VPT, BLOCK, ALIGNED>(in, 0, next * TILE + (uint64_t)wid * WARP_ELEMS, n, lane, s_stage);
-
-            // ---- pass 1
-            Acc run = Op::template identity<Acc>();
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                Acc t = (Acc)raw[j][0];
-#pragma unroll
-                for (int e = 1; e < VEC; ++e) t = Op::apply(t, (Acc)raw[j][e]);
-#pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    const Acc y = shfl_up_any(t, d);
-                    if (lane >= d) t = Op::apply(y, t);
-                }
-                Acc excl = shfl_up_any(t, 1);
-                if (lane == 0) excl = Op::template identity<Acc>();
-                base[j] = Op::apply(run, excl);
-                run = Op::apply(run, shfl_any(t, 31));
-            }
-            if (lane == 0) s_warp_total[parity][wid] = run;
+        fetch_tile<T, VEC, VPT, BLOCK>(s_stage, raw);
+        const uint64_t next = tile + gridDim.x;
+        if (next < total_tiles) {
+            const uint64_t nline = next / tiles_per_line;
+            stage_tile<T, Op, VEC, VPT, BLOCK, ALIGNED>(in, nline * n,
+                                                        (next - nline * tiles_per_line) * TILE + (uint64_t)wid * WARP_ELEMS, n, lane,
+                                                        s_stage);
         }
+        // ordered reduction: vectors of a warp are laid out j-major, lanes within j
+        Acc run = Op::template identity<Acc>();
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            Acc t = (Acc)raw[j][0];
+#pragma unroll
+            for (int e = 1; e < VEC; ++e) t = Op::apply(t, (Acc)raw[j][e]);
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const Acc far = shfl_down_any(t, d);
+                if (lane + d < 32) t = Op::apply(t, far);
+            }
+            run = Op::apply(run, t);     // valid in lane 0
+        }
+        if (lane == 0) s_part[parity][wid] = run;
         __syncthreads();
-        if (active) {
-            Acc aggregate = Op::template identity<Acc>();
+        if (threadIdx.x == 0) {
+            Acc a = Op::template identity<Acc>();
 #pragma unroll
-            for (int w = 0; w < WARPS; ++w) {
-                const Acc v = s_warp_total[parity][w];
-                if (w < wid) warp_excl = Op::apply(warp_excl, v);
-                aggregate = Op::apply(aggregate, v);
-            }
-            if (threadIdx.x == 0)
-                st_slot(slots + ((wave & 1) * kWaveMaxBlocks + b) * 16ull, acc_bits<Acc>(aggregate), wave + 1);
+            for (int w = 0; w < WARPS; ++w) a = Op::apply(a, s_part[parity][w]);
+            agg[tile] = a;
         }
-
-        // ---- gather the wave: thread t owns slots [t*SPT, (t+1)*SPT)
-        Acc lt = Op::template identity<Acc>();      // ordered sum of my slots that lie before block b
-        Acc all = Op::template identity<Acc>();     // ordered sum of all my slots
-#pragma unroll
-        for (int k = 0; k < SPT; ++k) {
-            const uint32_t slot = threadIdx.x * SPT + k;
-            if (slot < in_wave) {
-                const char* p = slots + ((wave & 1) * kWaveMaxBlocks + slot) * 16ull;
-                unsigned long long bits, tag;
-                uint32_t spins = 0;
-                ld_slot(p, bits, tag);
-                while (tag != wave + 1 && spins < kScanSpinLimit) {
-                    if (spins > 8) __nanosleep(32);
-                    ld_slot(p, bits, tag);
-                    ++spins;
-                }
-                Acc v = bits_acc<Acc>(bits);
-                if (tag != wave + 1) {
-                    atomicExch(&hdr->status, kErrTimeout);
-                    v = Op::template identity<Acc>();
-                }
-                all = Op::apply(all, v);
-                if (slot < b) lt = Op::apply(lt, v);
-            }
-        }
-        // ordered block reduction of both sums (threads hold consecutive slot ranges)
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const Acc far_lt = shfl_down_any(lt, d);
-            const Acc far_all = shfl_down_any(all, d);
-            if (lane + d < 32) {
-                lt = Op::apply(lt, far_lt);
-                all = Op::apply(all, far_all);
-            }
-        }
-        if (lane == 0) {
-            s_gather_lt[parity][wid] = lt;
-            s_gather_all[parity][wid] = all;
-        }
-        __syncthreads();
-        Acc in_wave_excl = Op::template identity<Acc>();
-        Acc wave_total = Op::template identity<Acc>();
-#pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
-            in_wave_excl = Op::apply(in_wave_excl, s_gather_lt[parity][w]);
-            wave_total = Op::apply(wave_total, s_gather_all[parity][w]);
-        }
-        const Acc offset = Op::apply(Op::apply(running, in_wave_excl), warp_excl);
-        running = Op::apply(running, wave_total);
         parity ^= 1;
-
-        // ---- pass 2
-        if (active) {
-#pragma unroll
-            for (int j = 0; j < VPT; ++j) {
-                const uint64_t off = warp_off + (uint64_t)(j * 32 + lane) * VEC;
-                Acc p = Op::apply(offset, base[j]);
-                if (ALIGNED && off + VEC <= n) {
-                    Vec<T, VEC> v;
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) {
-                        p = Op::apply(p, (Acc)raw[j][e]);
-                        v.v[e] = (T)p;
-                    }
-                    store_vec<T, VEC>(out + off, v);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) {
-                        p = Op::apply(p, (Acc)raw[j][e]);
-                        if (off + e < n) out[off + e] = (T)p;
-                    }
-                }
-            }
-        }
+        tile = next;
     }
     cp_async_wait_all();
+}
+
+// One block per line (grid-stride over lines): agg[line][0..tiles) becomes the exclusive prefix of the tile
+// aggregates, seeded with *carry when HAS_CARRY (single line).  total_out[line] (optional) receives the
+// reduction of the whole line without the carry.  WRITE_PREFIX = false only computes the totals.
+// The line is walked in rounds of BLOCK * IPT consecutive values (coalesced), each round a block-wide scan.
+template <typename Acc, class Op, bool HAS_CARRY, bool WRITE_PREFIX>
+__device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uint64_t lines, const uint64_t tiles_per_line,
+                                                const Acc* __restrict__ carry, Acc* __restrict__ total_out) {
+    constexpr int BLOCK = kScanBlock;
+    constexpr int WARPS = BLOCK / 32;
+    constexpr int IPT = 8;
+    __shared__ Acc s_warp[2][WARPS];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    int parity = 0;
+    for (uint64_t line = blockIdx.x; line < lines; line += gridDim.x) {
+        Acc* a = agg + line * tiles_per_line;
+        Acc running = Op::template identity<Acc>();     // everything before the current round (without carry)
+        for (uint64_t round0 = 0; round0 < tiles_per_line; round0 += (uint64_t)BLOCK * IPT) {
+            const uint64_t lo = round0 + (uint64_t)threadIdx.x * IPT;
+            Acc v[IPT];
+#pragma unroll
+            for (int k = 0; k < IPT; ++k) v[k] = (lo + k < tiles_per_line) ? a[lo + k] : Op::template identity<Acc>();
+            Acc mine = v[0];
+#pragma unroll
+            for (int k = 1; k < IPT; ++k) mine = Op::apply(mine, v[k]);
+            Acc t = mine;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const Acc y = shfl_up_any(t, d);
+                if (lane >= d) t = Op::apply(y, t);
+            }
+            if (lane == 31) s_warp[parity][wid] = t;
+            __syncthreads();
+            Acc before = Op::template identity<Acc>();
+            Acc round_total = Op::template identity<Acc>();
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const Acc x = s_warp[parity][w];
+                if (w < wid) before = Op::apply(before, x);
+                round_total = Op::apply(round_total, x);
+            }
+            parity ^= 1;
+            if (WRITE_PREFIX) {
+                Acc excl = shfl_up_any(t, 1);
+                if (lane == 0) excl = Op::template identity<Acc>();
+                Acc p = Op::apply(Op::apply(running, before), excl);
+                if (HAS_CARRY) p = Op::apply(*carry, p);
+#pragma unroll
+                for (int k = 0; k < IPT; ++k) {
+                    if (lo + k < tiles_per_line) a[lo + k] = p;
+                    p = Op::apply(p, v[k]);
+                }
+            }
+            running = Op::apply(running, round_total);
+        }
+        if (total_out != nullptr && threadIdx.x == 0) total_out[line] = running;
+    }
 }
 
 // Reduction of n elements to one Acc, combination order fixed by the launch shape: per-thread strided partials,

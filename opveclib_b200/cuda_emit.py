@@ -40,14 +40,12 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv10'
+TEMPLATE_VERSION = 'tv12'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
-SCAN_BLOCK_LOOKBACK = 256
 SCAN_VPT = 4
 SCAN_HEADER_BYTES = 16
-WAVE_MAX_BLOCKS = 1024      # kWaveMaxBlocks
 
 
 def ctype(dtype):
@@ -431,31 +429,35 @@ def emit_cuda(kernel, name):
         acc = 'double' if spec.dtype.is_float else t
         acc_size = 8 if spec.dtype.is_float else spec.dtype.itemsize
         vec = max(1, min(4, 16 // spec.dtype.itemsize))
-        lookback = spec.n > SCAN_BLOCK * SCAN_VPT * vec
-        block = SCAN_BLOCK_LOOKBACK if lookback else SCAN_BLOCK
-        tile = block * SCAN_VPT * vec
-        tiles = ((spec.n + tile - 1) // tile if lookback else 1) * spec.lines
-        desc = 32 if acc_size == 8 else 16
-        wave = lookback and spec.lines == 1
-        scratch = SCAN_HEADER_BYTES + (2 * WAVE_MAX_BLOCKS * 16 if wave else tiles * desc)
+        tile = SCAN_BLOCK * SCAN_VPT * vec
+        multi = spec.n > tile                       # several tiles per line: three passes
+        tpl = (spec.n + tile - 1) // tile if multi else 1
+        tiles = tpl * spec.lines
+        scratch = SCAN_HEADER_BYTES + tiles * max(acc_size, 8)
         op = 'ovl::OpAdd' if spec.op == 'add' else 'ovl::OpMul'
         can_align = spec.lines == 1 or spec.n % vec == 0
-        variants = [('scanu', 'false')] + ([('scan', 'true')] if can_align else [])
-        for suffix, aligned in variants:
-            head = 'extern "C" __global__ void __launch_bounds__(' + str(block) + ', ' + ('4' if lookback else '2') + \
-                ') ' + name + '_' + suffix + '(const ' + t + '* __restrict__ in0, ' + t + \
-                '* __restrict__ out0, void* scratch) {'
-            if wave:
-                call = '    ovl::scan_long_line<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned + \
-                    ', false>(in0, out0, nullptr, ' + str(spec.n) + 'ull, scratch);'
-            else:
-                call = '    ovl::scan_lines<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned + \
-                    ', false, ' + ('true' if lookback else 'false') + '>(in0, out0, nullptr, ' + str(spec.lines) + \
-                    'ull, ' + str(spec.n) + 'ull, scratch);'
-            src += [head, call, '}', '']
-        meta['scan'] = {'symbol': name + '_scan' if can_align else None, 'symbol_unaligned': name + '_scanu',
-                        'block': block, 'tiles': tiles, 'scratch_bytes': scratch,
-                        'zero_bytes': scratch if lookback else SCAN_HEADER_BYTES, 'blocks_per_sm': 4 if lookback else 2,
-                        'lookback': bool(lookback), 'max_grid': WAVE_MAX_BLOCKS if wave else None,
-                        'align_bytes': vec * spec.dtype.itemsize, 'lines': spec.lines, 'n': spec.n, 'op': spec.op}
+        agg_ptr = '(' + acc + '*)((char*)scratch + ' + str(SCAN_HEADER_BYTES) + ')'
+        mode = 'ovl::kScanPrefixed' if multi else 'ovl::kScanOneTile'
+        for suffix, aligned in [('u', 'false')] + ([('', 'true')] if can_align else []):
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(SCAN_BLOCK) + ', 2) ' + name + '_scan' + suffix +
+                    '(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0, void* scratch) {',
+                    '    ovl::scan_lines<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned + ', false, ' +
+                    mode + '>(in0, out0, nullptr, ' + str(spec.lines) + 'ull, ' + str(spec.n) + 'ull, scratch);',
+                    '}', '']
+            if multi:
+                src += ['extern "C" __global__ void __launch_bounds__(' + str(SCAN_BLOCK) + ', 2) ' + name + '_agg' +
+                        suffix + '(const ' + t + '* __restrict__ in0, void* scratch) {',
+                        '    ovl::tile_aggregates<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + aligned +
+                        '>(in0, ' + str(spec.lines) + 'ull, ' + str(spec.n) + 'ull, ' + agg_ptr + ');',
+                        '}', '']
+        if multi:
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(SCAN_BLOCK) + ') ' + name +
+                    '_pfx(void* scratch) {',
+                    '    ovl::scan_aggregates<' + acc + ', ' + op + ', false, true>(' + agg_ptr + ', ' + str(spec.lines) +
+                    'ull, ' + str(tpl) + 'ull, nullptr, nullptr);',
+                    '}', '']
+        meta['scan'] = {'name': name, 'aligned_variant': bool(can_align), 'three_pass': bool(multi),
+                        'block': SCAN_BLOCK, 'tiles': tiles, 'scratch_bytes': scratch, 'zero_bytes': SCAN_HEADER_BYTES,
+                        'blocks_per_sm': 2, 'align_bytes': vec * spec.dtype.itemsize, 'lines': spec.lines, 'n': spec.n,
+                        'op': spec.op}
     return '\n'.join(src), meta

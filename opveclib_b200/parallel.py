@@ -6,13 +6,14 @@ slab - no communication.  The one exchange this backend knows is the carry of a 
 sharded axis (the reference has no multi-GPU support at all; its rank-1 ``accumulate`` is a single worker,
 opveclib/examples/test_accumulate.py:40-41):
 
-1. every rank reduces its shard to one fp64 total (read-only pass, built-in reduction kernel);
+1. every rank reads its shard once, keeping one fp64 aggregate per tile and the shard total (``ovl_scan_f32_begin``);
 2. the totals are all-gathered (8 bytes per rank, NCCL on GPUs, gloo in CPU tests) into local memory;
-3. every rank combines the totals of the ranks before it into its carry and runs the single-pass scan seeded
-   with that carry.
+3. every rank combines the totals of the ranks before it into its carry, turns the tile aggregates into tile
+   prefixes seeded with the carry and scans its tiles (``ovl_scan_f32_finish``).
 
-Per element this moves 4 bytes in step 1 and 8 in step 3; with contiguous shards nothing cheaper exists, because
-a rank's carry depends on all data of the ranks before it.
+Per element this moves 4 bytes in step 1 and 8 in step 3 - exactly what the unsharded scan of a long line moves
+(its three passes are the same kernels without the exchange in the middle), so sharding costs one tiny
+collective and nothing else.
 """
 import ctypes
 
@@ -72,9 +73,7 @@ class ShardedScan(object):
         lib = launcher.library()
         self.lib = lib
         self.scan_bytes = int(lib.ovl_scan_f32_scratch_bytes(1, self.shard_len))
-        self.reduce_bytes = int(lib.ovl_reduce_f32_scratch_bytes(self.shard_len))
         self.scan_scratch = torch.empty(self.scan_bytes, dtype=torch.uint8, device=self.device)
-        self.reduce_scratch = torch.empty(self.reduce_bytes, dtype=torch.uint8, device=self.device)
         self.total = torch.zeros(1, dtype=torch.float64, device=self.device)
         self.totals = torch.zeros(self.world, dtype=torch.float64, device=self.device)
         self.carry = torch.zeros(1, dtype=torch.float64, device=self.device)
@@ -89,23 +88,27 @@ class ShardedScan(object):
         if out is None:
             out = torch.empty_like(x)
         stream = torch.cuda.current_stream(self.device).cuda_stream
-        carry_ptr = None
-        if self.world > 1:
-            launcher.check(self.lib.ovl_reduce_f32(self.code, x.data_ptr(), self.shard_len, self.total.data_ptr(),
-                                                   self.reduce_scratch.data_ptr(), self.reduce_bytes, stream),
-                           'shard reduction')
-            self.dist.all_gather_into_tensor(self.totals, self.total, group=self.group)
-            if self.op == 'add':
-                torch.sum(torch.where(self.before, self.totals, torch.zeros_like(self.totals)), dim=0, keepdim=True,
-                          out=self.carry)
-            else:
-                torch.prod(torch.where(self.before, self.totals, torch.ones_like(self.totals)), dim=0, keepdim=True,
-                           out=self.carry)
-            carry_ptr = self.carry.data_ptr()
+        if self.world == 1:
+            launcher.check(self.lib.ovl_scan_f32(self.code, x.data_ptr(), out.data_ptr(), 1, self.shard_len, None,
+                                                 self.scan_scratch.data_ptr(), self.scan_bytes, stream), 'scan')
             self.launches += 1
-        launcher.check(self.lib.ovl_scan_f32(self.code, x.data_ptr(), out.data_ptr(), 1, self.shard_len, carry_ptr,
-                                             self.scan_scratch.data_ptr(), self.scan_bytes, stream), 'shard scan')
-        self.launches += 1
+            return out
+        # step 1: tile aggregates (kept in the scratch) and the shard total
+        launcher.check(self.lib.ovl_scan_f32_begin(self.code, x.data_ptr(), self.shard_len, self.total.data_ptr(),
+                                                   self.scan_scratch.data_ptr(), self.scan_bytes, stream), 'shard totals')
+        # step 2: exchange, carry = combination of the totals of the ranks before this one
+        self.dist.all_gather_into_tensor(self.totals, self.total, group=self.group)
+        if self.op == 'add':
+            torch.sum(torch.where(self.before, self.totals, torch.zeros_like(self.totals)), dim=0, keepdim=True,
+                      out=self.carry)
+        else:
+            torch.prod(torch.where(self.before, self.totals, torch.ones_like(self.totals)), dim=0, keepdim=True,
+                       out=self.carry)
+        # step 3: prefixes of the aggregates seeded with the carry, then the seeded tile scans
+        launcher.check(self.lib.ovl_scan_f32_finish(self.code, x.data_ptr(), out.data_ptr(), self.shard_len,
+                                                    self.carry.data_ptr(), self.scan_scratch.data_ptr(),
+                                                    self.scan_bytes, stream), 'shard scan')
+        self.launches += 2
         return out
 
     def check_status(self):

@@ -51,44 +51,54 @@ class KernelPlan(object):
             self._sms[device] = _torch().cuda.get_device_properties(device).multi_processor_count
         return self._sms[device]
 
-    def _variant(self, which, device):
-        key = (which, device)
-        if key in self._variants:
-            return self._variants[key]
+    def _make(self, device, symbol, grid, block, use_in, use_out, aligns, scratch=0, zero=0):
+        """A launchable kernel of this plan's module taking inputs[use_in] and outputs[use_out]."""
+        key = (symbol, device)
+        if key not in self._variants:
+            types = [self.in_types[i] for i in use_in] + [self.out_types[i] for i in use_out]
+            self._variants[key] = (launcher.Kernel(self._module(device), symbol, grid, block,
+                                                   [t.dtype.code for t in types], [t.size for t in types], len(use_in),
+                                                   aligns, scratch, zero), use_in, use_out)
+        return self._variants[key]
+
+    def _passes(self, which, device):
+        """The launches that make up one execution of the chosen variant, in order."""
         meta = self.meta
-        dtypes = [t.dtype.code for t in self.in_types + self.out_types]
-        lens = [t.size for t in self.in_types + self.out_types]
-        n_in = len(self.in_types)
         sms = self._sm_count(device)
-        aligns = [0] * len(dtypes)
-        scratch = zero = 0
-        cooperative = 0
+        n_in, n_out = len(self.in_types), len(self.out_types)
+        all_in, all_out = list(range(n_in)), list(range(n_out))
         if which in ('gen', 'vec'):
             m = meta[which]
             block = m['block']
             grid = max(1, min((m['items'] + block - 1) // block, sms * (2048 // block)))
-            symbol = m['symbol']
+            aligns = [0] * (n_in + n_out)
             if which == 'vec':
                 for kind, idx in m['aligned']:
                     aligns[idx if kind == 'in' else n_in + idx] = 16
+            return [self._make(device, m['symbol'], grid, block, all_in, all_out, aligns)]
+        m = meta['scan']
+        block, name = m['block'], m['name']
+        suffix = '' if which == 'scan' else 'u'
+        al = m['align_bytes'] if which == 'scan' else 0
+        cap = sms * m['blocks_per_sm']
+        scratch = m['scratch_bytes']
+        passes = []
+        if m['three_pass']:
+            passes.append(self._make(device, name + '_agg' + suffix, max(1, min(m['tiles'], cap)), block, [0], [], [al],
+                                     scratch, m['zero_bytes']))
+            passes.append(self._make(device, name + '_pfx', max(1, min(m['lines'], cap)), block, [], [], [], scratch, 0))
+            passes.append(self._make(device, name + '_scan' + suffix, max(1, min(m['tiles'], cap)), block, [0], [0],
+                                     [al, al], scratch, 0))
         else:
-            m = meta['scan']
-            block = m['block']
-            grid = max(1, min(m['tiles'], sms * m.get('blocks_per_sm', 2), m.get('max_grid') or (1 << 30)))
-            symbol = m['symbol'] if which == 'scan' else m['symbol_unaligned']
-            scratch, zero = m['scratch_bytes'], m['zero_bytes']
-            cooperative = 1 if m.get('lookback') else 0
-            if which == 'scan':
-                aligns = [m['align_bytes']] * len(dtypes)
-        k = launcher.Kernel(self._module(device), symbol, grid, block, dtypes, lens, n_in, aligns, scratch, zero, 0, cooperative)
-        self._variants[key] = k
-        return k
+            passes.append(self._make(device, name + '_scan' + suffix, max(1, min(m['tiles'], cap)), block, [0], [0],
+                                     [al, al], scratch, m['zero_bytes']))
+        return passes
 
     def choose(self, in_ptrs, out_ptrs):
         meta = self.meta
         if meta.get('scan'):
             al = meta['scan']['align_bytes']
-            if meta['scan']['symbol'] and all(p % al == 0 for p in in_ptrs + out_ptrs):
+            if meta['scan']['aligned_variant'] and all(p % al == 0 for p in in_ptrs + out_ptrs):
                 return 'scan'
             return 'scanu'
         if meta.get('vec'):
@@ -102,33 +112,40 @@ class KernelPlan(object):
         return 'gen'
 
     def launch(self, ins, outs, stream_ptr, device, iterations=None):
-        """ins/outs: torch CUDA tensors.  Enqueues one launch (or ``iterations`` timed launches, returning the
-        milliseconds of each)."""
+        """ins/outs: torch CUDA tensors.  Enqueues one execution (or ``iterations`` timed ones, returning the
+        milliseconds of each, summed over the passes of a multi-pass kernel)."""
         torch = _torch()
         in_ptrs = [t.data_ptr() for t in ins]
         out_ptrs = [t.data_ptr() for t in outs]
         which = self.choose(in_ptrs, out_ptrs)
-        k = self._variant(which, device)
+        passes = self._passes(which, device)
         self.last_variant = which
-        in_arr = launcher.tensor_array([(p, t.dtype.code, t.size) for p, t in zip(in_ptrs, self.in_types)])
-        out_arr = launcher.tensor_array([(p, t.dtype.code, t.size) for p, t in zip(out_ptrs, self.out_types)])
         scratch_ptr, scratch_bytes = None, 0
-        if k.scratch_bytes:
+        need = max(k.scratch_bytes for k, _, _ in passes)
+        if need:
             key = (device, stream_ptr)
             buf = self._scratch.get(key)
-            if buf is None or buf.numel() < k.scratch_bytes:
-                buf = torch.empty(k.scratch_bytes, dtype=torch.uint8, device='cuda:%d' % device)
+            if buf is None or buf.numel() < need:
+                buf = torch.empty(need, dtype=torch.uint8, device='cuda:%d' % device)
                 self._scratch[key] = buf
             scratch_ptr, scratch_bytes = buf.data_ptr(), buf.numel()
-        if iterations is None:
-            st = k.launch(in_arr, len(ins), out_arr, len(outs), scratch_ptr, scratch_bytes, stream_ptr)
-            launcher.check(st, 'launching ' + self.kernel.name)
-            self.launches += 1
-            return None
-        st, ms = k.profile(in_arr, len(ins), out_arr, len(outs), scratch_ptr, scratch_bytes, stream_ptr, iterations)
-        launcher.check(st, 'profiling ' + self.kernel.name)
-        self.launches += iterations
-        return ms
+        total_ms = None
+        for k, use_in, use_out in passes:
+            in_arr = launcher.tensor_array([(in_ptrs[i], self.in_types[i].dtype.code, self.in_types[i].size)
+                                            for i in use_in])
+            out_arr = launcher.tensor_array([(out_ptrs[i], self.out_types[i].dtype.code, self.out_types[i].size)
+                                             for i in use_out])
+            sp, sb = (scratch_ptr, scratch_bytes) if k.scratch_bytes else (None, 0)
+            if iterations is None:
+                st = k.launch(in_arr, len(use_in), out_arr, len(use_out), sp, sb, stream_ptr)
+                launcher.check(st, 'launching ' + self.kernel.name)
+                self.launches += 1
+            else:
+                st, ms = k.profile(in_arr, len(use_in), out_arr, len(use_out), sp, sb, stream_ptr, iterations)
+                launcher.check(st, 'profiling ' + self.kernel.name)
+                self.launches += iterations
+                total_ms = ms if total_ms is None else [a + b for a, b in zip(total_ms, ms)]
+        return total_ms
 
     def check_status(self, stream_ptr, device):
         """Raise if a bounded device-side wait of this kernel expired (scan kernels only)."""

@@ -33,14 +33,12 @@ def test_status_strings_and_size_queries_work_without_a_device():
     assert lib.ovl_status_string(0) == b'ok'
     assert b'element count' in lib.ovl_status_string(2)
     assert b'wait expired' in lib.ovl_status_string(8)
-    # 16-byte header + one 32-byte descriptor per tile: a line of up to 8192 elements is one tile, longer lines
-    # are cut into tiles of 4096
+    # 16-byte header + one 32-byte slot per tile: a line of up to 8192 elements is one tile, longer lines are
+    # sized for tiles of 4096 (the finer of the two tilings in use)
     assert lib.ovl_scan_f32_scratch_bytes(1, 8192) == 16 + 32
     assert lib.ovl_scan_f32_scratch_bytes(3, 8193) == 16 + 32 * 9
     assert lib.ovl_scan_f32_scratch_bytes(4096, 8192) == 16 + 32 * 4096
-    # one long line: two wave buffers of 1024 16-byte slots, whatever the length
-    assert lib.ovl_scan_f32_scratch_bytes(1, 8193) == 16 + 2 * 1024 * 16
-    assert lib.ovl_scan_f32_scratch_bytes(1, 1 << 31) == 16 + 2 * 1024 * 16
+    assert lib.ovl_scan_f32_scratch_bytes(1, 1 << 31) == 16 + 32 * (1 << 19)
 
 
 def test_argument_validation_happens_before_any_cuda_call():

@@ -74,6 +74,70 @@ def test_rank_emulation_on_one_gpu_reduce_carry_scan(op, world):
     np.testing.assert_allclose(np.concatenate(parts), _reference(x, op), rtol=1.3e-7, atol=0)
 
 
+@pytest.mark.parametrize('op', ['add', 'mul'])
+@pytest.mark.parametrize('world', [2, 8])
+def test_rank_emulation_begin_exchange_finish(op, world):
+    """The split entry points the sharded runner uses: begin (tile aggregates + shard total), host-side carry,
+    finish (seeded scan), all ranks run one after the other on one device."""
+    import torch
+    lib = launcher.library()
+    code = 0 if op == 'add' else 1
+    n = 70001 * world + 5
+    rs = np.random.RandomState(10 + world)
+    x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.999, 1.001, n)).astype(np.float32)
+    shards = [torch.from_numpy(np.ascontiguousarray(parallel.shard_leading_axis(x, r, world))).cuda()
+              for r in range(world)]
+    stream = torch.cuda.current_stream().cuda_stream
+    totals = torch.zeros(world, dtype=torch.float64, device='cuda')
+    scratches = []
+    for r, s in enumerate(shards):
+        nbytes = int(lib.ovl_scan_f32_scratch_bytes(1, s.numel()))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device='cuda')
+        scratches.append((scratch, nbytes))
+        launcher.check(lib.ovl_scan_f32_begin(code, s.data_ptr(), s.numel(), totals[r:].data_ptr(), scratch.data_ptr(),
+                                              nbytes, stream), 'begin')
+    host_totals = totals.cpu().numpy()
+    parts = []
+    for r, s in enumerate(shards):
+        carry = torch.tensor([parallel.exclusive_carry(host_totals, r, op)], dtype=torch.float64, device='cuda')
+        out = torch.empty_like(s)
+        scratch, nbytes = scratches[r]
+        launcher.check(lib.ovl_scan_f32_finish(code, s.data_ptr(), out.data_ptr(), s.numel(), carry.data_ptr(),
+                                               scratch.data_ptr(), nbytes, stream), 'finish')
+        parts.append(out.cpu().numpy())
+    np.testing.assert_allclose(np.concatenate(parts), _reference(x, op), rtol=1.3e-7, atol=0)
+
+
+def test_single_pass_lookback_mode_agrees_with_three_pass_mode():
+    """OVL_SCAN_MODE=lookback selects the decoupled look-back kernel for lines of several tiles; it is read once
+    per process, so the check runs in a child process.  Both modes accumulate in fp64 and must give the same
+    correctly rounded results."""
+    import subprocess
+    import sys
+    code = """
+import numpy as np, torch, ctypes, sys
+sys.path.insert(0, %r)
+from opveclib_b200 import launcher
+lib = launcher.library()
+rs = np.random.RandomState(3)
+for lines, n, op in ((1, 300007, 0), (5, 20000, 0), (3, 40001, 1), (1, 1 << 22, 0)):
+    x = (rs.normal(0, 1, (lines, n)) if op == 0 else rs.uniform(0.9999, 1.0001, (lines, n))).astype(np.float32)
+    d = torch.from_numpy(x).cuda(); y = torch.empty_like(d)
+    nb = int(lib.ovl_scan_f32_scratch_bytes(lines, n)); scratch = torch.empty(nb, dtype=torch.uint8, device='cuda')
+    st = torch.cuda.current_stream().cuda_stream
+    launcher.check(lib.ovl_scan_f32(op, d.data_ptr(), y.data_ptr(), lines, n, None, scratch.data_ptr(), nb, st), 'scan')
+    status = ctypes.c_int32(-1); lib.ovl_read_kernel_status(scratch.data_ptr(), st, ctypes.byref(status))
+    assert status.value == 0, status.value
+    x64 = x.astype(np.float64)
+    want = (np.cumsum(x64, axis=1) if op == 0 else np.cumprod(x64, axis=1)).astype(np.float32)
+    np.testing.assert_allclose(y.cpu().numpy(), want, rtol=1.3e-7, atol=0)
+print('lookback ok')
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, OVL_SCAN_MODE='lookback')
+    res = subprocess.run([sys.executable, '-c', code], env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and 'lookback ok' in res.stdout, res.stdout + res.stderr
+
+
 def _nccl_rank(rank, world, port, op, n, queue):
     import torch
     import torch.distributed as dist
