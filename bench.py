@@ -127,6 +127,8 @@ def build_graph(workload, rows_local=None, n_local=None):
     z = lambda *shape: np.zeros(shape, dtype=f32)     # noqa: E731  (only the type matters for tracing)
     if workload == 'c4':
         return [cases.chain16(ns, z(rows_local, C4_COLS))], rows_local * C4_COLS, 8
+    if workload == 'light16':
+        return [cases.chain16_light(ns, z(rows_local or C4_ROWS, C4_COLS))], (rows_local or C4_ROWS) * C4_COLS, 8
     if workload == 'c2_cumsum':
         return [ns.cumsum(z(4096, 8192), axis=1)], 4096 * 8192, 8
     if workload == 'c2_cumprod':
@@ -149,12 +151,12 @@ def precompile():
     from opveclib_b200 import runtime
     for n in (1, 2, 4, 8):
         runtime.compile_outputs(build_graph('c4', rows_local=C4_ROWS // n)[0])
-    for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad'):
+    for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'light16'):
         runtime.compile_outputs(build_graph(w)[0])
 
 
 def input_distribution(workload, index):
-    if workload == 'c4':
+    if workload in ('c4', 'light16'):
         return ('uniform', -2.0, 2.0)
     if workload == 'c2_cumprod':
         return ('uniform', 0.99, 1.01)
@@ -256,6 +258,7 @@ def run_reference_arm(args, workload):
 def workload_config(workload, n):
     names = {
         'c4': 'fused 16-op element-wise chain, fp32 [8, 2^27] uniform[-2,2], rows sharded over the GPUs',
+        'light16': 'fused 16-op element-wise chain without transcendentals (add/mul/where), fp32 [8, 2^27]',
         'c2_cumsum': 'cumsum along axis 1, fp32 [4096, 8192] normal(0,1)',
         'c2_cumprod': 'cumprod along axis 1, fp32 [4096, 8192] uniform[0.99,1.01]',
         'c1': 'fused chain expm1(log1p(|x|))*0.5+x, fp32 [2^20] uniform[-1,1]',
@@ -269,7 +272,7 @@ def workload_config(workload, n):
     if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
         names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
-            'l2': 'inputs larger than L2 (126 MB)' if workload in ('c4', 'c5', 'c2_cumsum', 'c2_cumprod')
+            'l2': 'inputs larger than L2 (126 MB)' if workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod')
             else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
 
 
@@ -340,7 +343,7 @@ def main():
         ins = make_device_inputs(torch, workload, dag.input_types, device, SEED + rank)
         out_bufs = [torch.empty(prog.plans[o].out_types[k].shape, dtype=torch.float32, device=device)
                     for o, k in prog.dag.outputs]
-        small = sum(t.size * 4 for t in dag.input_types) < (256 << 20)
+        small = sum(t.size * 4 for t in dag.input_types) <= 126 * 10 ** 6     # inputs that fit in L2
         if small:
             flush = torch.empty(192 << 20, dtype=torch.uint8, device=device)
 
@@ -477,6 +480,8 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
     ns = cases.impl()
     if workload == 'c4':
         return [cases.chain16(ns, np_inputs[0])]
+    if workload == 'light16':
+        return [cases.chain16_light(ns, np_inputs[0])]
     if workload == 'c2_cumsum':
         return [ns.cumsum(np_inputs[0], axis=1)]
     if workload == 'c2_cumprod':

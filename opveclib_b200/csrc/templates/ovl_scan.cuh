@@ -380,20 +380,15 @@ __device__ __forceinline__ void tile_aggregates(const T* __restrict__ in, const 
                                                         (next - nline * tiles_per_line) * TILE + (uint64_t)wid * WARP_ELEMS, n, lane,
                                                         s_stage);
         }
-        // ordered reduction: vectors of a warp are laid out j-major, lanes within j
-        Acc run = Op::template identity<Acc>();
+        // thread-local sum of the 16 values, then one tree over the warp.  (The summation order differs from the
+        // scan pass; in fp64 that changes the aggregate by parts in 1e16, far below the rounding to T.)
+        Acc run = (Acc)raw[0][0];
 #pragma unroll
-        for (int j = 0; j < VPT; ++j) {
-            Acc t = (Acc)raw[j][0];
+        for (int j = 0; j < VPT; ++j)
 #pragma unroll
-            for (int e = 1; e < VEC; ++e) t = Op::apply(t, (Acc)raw[j][e]);
+            for (int e = (j == 0 ? 1 : 0); e < VEC; ++e) run = Op::apply(run, (Acc)raw[j][e]);
 #pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const Acc far = shfl_down_any(t, d);
-                if (lane + d < 32) t = Op::apply(t, far);
-            }
-            run = Op::apply(run, t);     // valid in lane 0
-        }
+        for (int d = 16; d > 0; d >>= 1) run = Op::apply(run, shfl_down_any(run, d));
         if (lane == 0) s_part[parity][wid] = run;
         __syncthreads();
         if (threadIdx.x == 0) {

@@ -145,6 +145,28 @@ def chain16(ns, x):
     return u.ew_add(o, e)
 
 
+def chain16_light(ns, x):
+    """Sixteen element-wise operators without transcendentals (add, mul, where on a comparison): the same graph
+    shape as chain16 with a body light enough to be limited by memory bandwidth."""
+    u = user_ops(ns)
+    a = u.ew_mulc(x, c=0.5)
+    b = u.ew_addc(a, c=1.0)
+    c = u.ew_mul(b, a)
+    d = u.ew_add(c, x)
+    e = u.where_greater(d, a)
+    f = u.ew_mulc(e, c=0.25)
+    g = u.ew_mul(f, b)
+    h = u.ew_add(g, d)
+    i = u.ew_addc(h, c=-0.5)
+    j = u.ew_mul(i, i)
+    k = u.where_greater(j, h)
+    l = u.ew_mulc(k, c=0.125)
+    m = u.ew_add(l, e)
+    n = u.ew_mul(m, a)
+    o = u.ew_addc(n, c=2.0)
+    return u.ew_add(o, x)
+
+
 # ---------------------------------------------------------------------------------------------------------
 def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
@@ -260,6 +282,11 @@ def case_lstm_fwd_bias_odd(ns):
 def case_chain16(ns):
     x = _f32(np.random.RandomState(30).uniform(-2, 2, (3, 1000)))
     return [chain16(ns, x)], [x]
+
+
+def case_chain16_light(ns):
+    x = _f32(np.random.RandomState(35).uniform(-2, 2, (3, 1000)))
+    return [chain16_light(ns, x)], [x]
 
 
 def case_stdops_lstm(ns):

@@ -12,9 +12,10 @@ import ctypes
 import numpy as np
 import pytest
 
+from helpers import DRYRUN
 from opveclib_b200 import launcher
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(DRYRUN, reason='needs a device')]
 
 STATIC_BYTES = 1 << 20
 
