@@ -121,7 +121,9 @@ class Operator(object):
     """A lazily evaluated operator application: a traced kernel plus where its inputs come from."""
     __array_priority__ = 1
 
-    def __init__(self, kernel, inputs, grad_dag, from_gradient, name, grad_function=None, constants=None):
+    def __init__(self, kernel, inputs, grad_dag, from_gradient, name, generator=None, constants=None):
+        self.generator = generator      # the OpGenerator and constants that produced this application, so the
+        self.constants = constants      # same operator can be traced again for another input shape
         self.kernel = kernel
         self.inputs = inputs
         self.output_types = kernel.output_types
@@ -331,7 +333,7 @@ class OpGenerator(object):
                 # first, then one gradient per operator output
                 grad_dag = build_op_dag(*grad_outputs, leaf_order=grad_inputs)
 
-        return Operator(kernel, resolved_inputs, grad_dag, from_gradient, self.name)
+        return Operator(kernel, resolved_inputs, grad_dag, from_gradient, self.name, self, dict(defined_constants))
 
     def add_grad(self, grad_function):
         if self.grad_function is not None:

@@ -37,6 +37,7 @@ class KernelPlan(object):
         self._modules = {}
         self._variants = {}
         self._scratch = {}
+        self._arrays = {}
         self._sms = {}
         self.last_variant = None
         self.launches = 0
@@ -130,11 +131,18 @@ class KernelPlan(object):
                 self._scratch[key] = buf
             scratch_ptr, scratch_bytes = buf.data_ptr(), buf.numel()
         total_ms = None
-        for k, use_in, use_out in passes:
-            in_arr = launcher.tensor_array([(in_ptrs[i], self.in_types[i].dtype.code, self.in_types[i].size)
-                                            for i in use_in])
-            out_arr = launcher.tensor_array([(out_ptrs[i], self.out_types[i].dtype.code, self.out_types[i].size)
-                                             for i in use_out])
+        for pi, (k, use_in, use_out) in enumerate(passes):
+            akey = (which, pi, tuple(in_ptrs), tuple(out_ptrs))
+            arrays = self._arrays.get(akey)
+            if arrays is None:
+                if len(self._arrays) > 64:
+                    self._arrays.clear()
+                arrays = (launcher.tensor_array([(in_ptrs[i], self.in_types[i].dtype.code, self.in_types[i].size)
+                                                 for i in use_in]),
+                          launcher.tensor_array([(out_ptrs[i], self.out_types[i].dtype.code, self.out_types[i].size)
+                                                 for i in use_out]))
+                self._arrays[akey] = arrays
+            in_arr, out_arr = arrays
             sp, sb = (scratch_ptr, scratch_bytes) if k.scratch_bytes else (None, 0)
             if iterations is None:
                 st = k.launch(in_arr, len(use_in), out_arr, len(use_out), sp, sb, stream_ptr)
@@ -148,16 +156,17 @@ class KernelPlan(object):
         return total_ms
 
     def check_status(self, stream_ptr, device):
-        """Raise if a bounded device-side wait of this kernel expired (scan kernels only)."""
-        buf = self._scratch.get((device, stream_ptr))
-        if buf is None:
-            return
+        """Raise if a bounded device-side wait of this kernel expired (scan kernels only).  Looks at the scratch
+        buffer of every stream the kernel ran on, on this device."""
         import ctypes
-        status = ctypes.c_int32(0)
-        launcher.check(launcher.library().ovl_read_kernel_status(buf.data_ptr(), stream_ptr, ctypes.byref(status)),
-                       'reading kernel status')
-        if status.value != 0:
-            raise launcher.OvlError(status.value, 'kernel ' + self.kernel.name)
+        for (dev, _), buf in list(self._scratch.items()):
+            if dev != device:
+                continue
+            status = ctypes.c_int32(0)
+            launcher.check(launcher.library().ovl_read_kernel_status(buf.data_ptr(), stream_ptr, ctypes.byref(status)),
+                           'reading kernel status')
+            if status.value != 0:
+                raise launcher.OvlError(status.value, 'kernel ' + self.kernel.name)
 
 
 class Program(object):
@@ -198,6 +207,22 @@ class Program(object):
             for key in [key for key, last in self.last_use.items() if last == op_index and key not in self.keep]:
                 buffers.pop(key, None)
         return [buffers[o] for o in self.dag.outputs], times
+
+    def capture(self, leaf_tensors, device, out_buffers):
+        """Record one execution of the graph into a CUDA graph (``torch.cuda.CUDAGraph``) over fixed input and
+        output tensors; ``replay()`` then costs one launch call whatever the number of kernels.  For loops whose
+        kernels are shorter than the time it takes to enqueue them."""
+        torch = _torch()
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            # first run outside the capture: loads modules, creates kernels and this stream's scratch buffers
+            self.run(leaf_tensors, device, side.cuda_stream, None, out_buffers)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            self.run(leaf_tensors, device, side.cuda_stream, None, out_buffers)
+        return graph
 
     def check_status(self, device, stream_ptr):
         for plan in self.plans:
@@ -257,6 +282,24 @@ def profile(output_list, target_language='b200', profiling_iterations=1, opt_lev
         else:
             leaves.append(torch.from_numpy(np.ascontiguousarray(x)))
     dev = 'cuda:%d' % device
+    if not any(_is_torch(x) for x in dag.inputs) and profiling_iterations == 1:
+        # host-resident inputs: stream slabs of rows through the device when the graph allows it
+        from . import streaming
+        splan = streaming.plan(output_list if isinstance(output_list, (list, tuple)) else [output_list], dag, prog,
+                               opt_level)
+        if splan is not None:
+            out_types = [prog.plans[o].out_types[k] for o, k in prog.dag.outputs]
+            if out is None:
+                host_out = [np.empty(t.shape, dtype=t.dtype.as_numpy()) for t in out_types]
+            else:
+                host_out = list(out)
+                if len(host_out) != len(out_types) or any(
+                        a.shape != tuple(t.shape) or a.dtype != t.dtype.as_numpy() or not a.flags['C_CONTIGUOUS']
+                        for a, t in zip(host_out, out_types)):
+                    raise ValueError('out must hold one C-contiguous array of the right shape and dtype per output')
+            host_in = [np.ascontiguousarray(x) for x in dag.inputs]
+            streaming.run(splan, host_in, host_out, out_types, device)
+            return host_out, {plan.name: np.array([np.nan]) for plan in splan['prog'].plans}
     with torch.cuda.device(device):
         stream_ptr = torch.cuda.current_stream().cuda_stream
         staged = [x.contiguous() if x.is_cuda else x.to(dev, non_blocking=True) for x in leaves]
