@@ -74,9 +74,6 @@ typedef struct OvlKernelSpec {
     uint64_t scratch_bytes;      /* device scratch the kernel needs (0 = none); provided by the caller */
     uint64_t scratch_zero_bytes; /* leading part of the scratch that must be zero when the kernel starts;
                                     ovl_launch clears it on the stream before the kernel */
-    uint32_t cooperative;        /* non-zero: thread blocks wait for one another (look-back scans), so the kernel is
-                                    started as a cooperative launch and grid_x is clamped to the number of blocks
-                                    the device can hold at once */
 } OvlKernelSpec;
 
 /* Library / device ------------------------------------------------------------------------------------- */

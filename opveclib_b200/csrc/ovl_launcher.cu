@@ -22,6 +22,8 @@ thread_local int g_last_cuda_error = 0;
 
 inline int cuda_fail(cudaError_t e) {
     g_last_cuda_error = (int)e;
+    (void)cudaGetLastError();   // the runtime also remembers the error; clear it so that a later, unrelated
+                                // cudaGetLastError() after a kernel launch does not report it again
     return OVL_ERR_CUDA;
 }
 #define OVL_CUDA(call)                                   \
@@ -55,7 +57,6 @@ struct OvlKernel {
     std::vector<uint32_t> align;
     uint32_t n_in, n_out;
     uint64_t scratch_bytes, scratch_zero_bytes;
-    uint32_t cooperative;
 };
 
 extern "C" const char* ovl_version(void) { return "ovl_b200 0.1.0 (sm_100a)"; }
@@ -123,6 +124,7 @@ extern "C" int ovl_kernel_create(OvlModule* module, const OvlKernelSpec* spec, O
     cudaError_t e = cudaLibraryGetKernel(&fn, module->lib, spec->symbol);
     if (e != cudaSuccess) {
         g_last_cuda_error = (int)e;
+        (void)cudaGetLastError();
         return OVL_ERR_NOT_FOUND;
     }
     OvlKernel* k = new OvlKernel();
@@ -139,7 +141,6 @@ extern "C" int ovl_kernel_create(OvlModule* module, const OvlKernelSpec* spec, O
     else k->align.assign(n, 0);
     k->scratch_bytes = spec->scratch_bytes;
     k->scratch_zero_bytes = spec->scratch_zero_bytes;
-    k->cooperative = spec->cooperative;
     for (uint32_t i = 0; i < n; ++i)
         if (dtype_size(k->dtypes[i]) == 0) {
             delete k;
@@ -188,21 +189,6 @@ int enqueue(const OvlKernel* k, const OvlTensor* in, size_t n_in, const OvlTenso
     if (k->scratch_bytes) ptrs[n++] = scratch;
     for (size_t i = 0; i < n; ++i) args[i] = &ptrs[i];
     if (k->scratch_zero_bytes) OVL_CUDA(cudaMemsetAsync(scratch, 0, k->scratch_zero_bytes, stream));
-    if (k->cooperative) {
-        // blocks of this kernel wait for one another: all of them have to be resident
-        uint32_t grid = k->grid_x;
-        int per_sm = 0, dev = 0, sms = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, (const void*)k->fn, (int)k->block_x, k->dynamic_smem) ==
-                cudaSuccess && per_sm > 0 && cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0) {
-            const uint64_t cap = (uint64_t)per_sm * (uint64_t)sms;
-            if (grid > cap) grid = (uint32_t)cap;
-        } else {
-            (void)cudaGetLastError();
-        }
-        OVL_CUDA(cudaLaunchCooperativeKernel((const void*)k->fn, dim3(grid), dim3(k->block_x), args, k->dynamic_smem, stream));
-        return OVL_OK;
-    }
     OVL_CUDA(cudaLaunchKernel((const void*)k->fn, dim3(k->grid_x), dim3(k->block_x), args, k->dynamic_smem, stream));
     return OVL_OK;
 }
