@@ -60,7 +60,8 @@ typedef struct OvlModule OvlModule; /* a loaded cubin */
 typedef struct OvlKernel OvlKernel; /* one kernel of a module together with its signature and launch shape */
 
 /* Launch description of one generated kernel.  Kernel parameters are, in order: the input pointers, the
- * output pointers, then the scratch pointer if scratch_bytes > 0. */
+ * output pointers, then the scratch pointer if scratch_bytes > 0.  More than 48 KiB of dynamic shared memory is
+ * opted into when the kernel is created. */
 typedef struct OvlKernelSpec {
     const char* symbol;          /* name of the __global__ function inside the module */
     uint32_t grid_x;             /* number of thread blocks */
@@ -74,7 +75,12 @@ typedef struct OvlKernelSpec {
     uint64_t scratch_bytes;      /* device scratch the kernel needs (0 = none); provided by the caller */
     uint64_t scratch_zero_bytes; /* leading part of the scratch that must be zero when the kernel starts;
                                     ovl_launch clears it on the stream before the kernel */
+    uint32_t flags;              /* OVL_KERNEL_* bits */
 } OvlKernelSpec;
+
+/* The kernel's blocks wait for one another (always with a bound), so the whole grid must be resident at once:
+ * launched with cudaLaunchCooperativeKernel, which refuses a grid the device cannot hold. */
+#define OVL_KERNEL_COOPERATIVE 1u
 
 /* Library / device ------------------------------------------------------------------------------------- */
 const char* ovl_version(void);

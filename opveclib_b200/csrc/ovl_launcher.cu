@@ -57,6 +57,7 @@ struct OvlKernel {
     std::vector<uint32_t> align;
     uint32_t n_in, n_out;
     uint64_t scratch_bytes, scratch_zero_bytes;
+    bool cooperative;
 };
 
 extern "C" const char* ovl_version(void) { return "ovl_b200 0.1.0 (sm_100a)"; }
@@ -141,6 +142,15 @@ extern "C" int ovl_kernel_create(OvlModule* module, const OvlKernelSpec* spec, O
     else k->align.assign(n, 0);
     k->scratch_bytes = spec->scratch_bytes;
     k->scratch_zero_bytes = spec->scratch_zero_bytes;
+    k->cooperative = (spec->flags & OVL_KERNEL_COOPERATIVE) != 0;
+    if (k->dynamic_smem > 48u * 1024u) {
+        // beyond the default limit: opt in, for the current device
+        e = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k->dynamic_smem);
+        if (e != cudaSuccess) {
+            delete k;
+            return cuda_fail(e);
+        }
+    }
     for (uint32_t i = 0; i < n; ++i)
         if (dtype_size(k->dtypes[i]) == 0) {
             delete k;
@@ -189,7 +199,10 @@ int enqueue(const OvlKernel* k, const OvlTensor* in, size_t n_in, const OvlTenso
     if (k->scratch_bytes) ptrs[n++] = scratch;
     for (size_t i = 0; i < n; ++i) args[i] = &ptrs[i];
     if (k->scratch_zero_bytes) OVL_CUDA(cudaMemsetAsync(scratch, 0, k->scratch_zero_bytes, stream));
-    OVL_CUDA(cudaLaunchKernel((const void*)k->fn, dim3(k->grid_x), dim3(k->block_x), args, k->dynamic_smem, stream));
+    if (k->cooperative)
+        OVL_CUDA(cudaLaunchCooperativeKernel((const void*)k->fn, dim3(k->grid_x), dim3(k->block_x), args, k->dynamic_smem, stream));
+    else
+        OVL_CUDA(cudaLaunchKernel((const void*)k->fn, dim3(k->grid_x), dim3(k->block_x), args, k->dynamic_smem, stream));
     return OVL_OK;
 }
 
@@ -320,6 +333,13 @@ __global__ void __launch_bounds__(ovl::kScanBlock) reduce_f32_kernel(const float
     ovl::reduce_all<float, double, Op, 4, ALIGNED>(in, n, out_total, scratch);
 }
 
+template <class Op, bool HAS_CARRY>
+__global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                                            const double* __restrict__ carry, uint64_t n,
+                                                                            void* scratch) {
+    ovl::scan_ring<float, double, Op, 4, HAS_CARRY>(in, out, carry, n, scratch);
+}
+
 // a line of at most kTile elements is one tile; longer lines are cut into tiles of kTile elements (three-pass
 // scan) or kTileLookback elements (single-pass look-back scan)
 constexpr uint64_t kTile = (uint64_t)ovl::kScanBlock * ovl::kScanVpt * 4;
@@ -344,16 +364,22 @@ int sm_count_cached() {
     return sms;
 }
 
-// OVL_SCAN_MODE=lookback selects the single-pass decoupled look-back kernel for lines of several tiles; the
-// default is the three-pass scan, which is faster on this device (no waiting between thread blocks)
-bool use_lookback() {
+// How a single line of several tiles is scanned.  Default: the ring scan (one launch, 8 bytes per element).
+// OVL_SCAN_MODE=threepass selects the three streaming passes (12 bytes per element; also what lines that are not
+// 16-byte aligned and several long lines in one call use), OVL_SCAN_MODE=lookback the single-pass decoupled
+// look-back kernel.
+enum { kModeRing = 0, kModeThreePass = 1, kModeLookback = 2 };
+int long_line_mode() {
     static int cached = -1;
     if (cached < 0) {
         const char* e = getenv("OVL_SCAN_MODE");
-        cached = (e && strcmp(e, "lookback") == 0) ? 1 : 0;
+        if (e && strcmp(e, "lookback") == 0) cached = kModeLookback;
+        else if (e && strcmp(e, "threepass") == 0) cached = kModeThreePass;
+        else cached = kModeRing;
     }
-    return cached == 1;
+    return cached;
 }
+bool use_lookback() { return long_line_mode() == kModeLookback; }
 
 inline uint32_t clamp_grid(uint64_t tiles, uint64_t per_sm) {
     const uint64_t cap = (uint64_t)sm_count_cached() * per_sm;
@@ -424,6 +450,22 @@ cudaError_t launch_scan_pass(const float* in, float* out, uint64_t lines, uint64
     return launch_scan_mode<Op, false, false>(in, out, lines, n, carry, scratch, mode, stream);
 }
 
+// ring scan of one line: clear the aggregate words, then one cooperative launch with a block per SM
+template <class Op>
+int launch_ring(const float* in, float* out, uint64_t n, const double* carry, void* scratch, cudaStream_t stream) {
+    const uint64_t tiles = (n + kTile - 1) / kTile;
+    uint64_t cap = (uint64_t)sm_count_cached();
+    if (cap > (uint64_t)ovl::kRingMaxGrid) cap = ovl::kRingMaxGrid;
+    const uint32_t grid = (uint32_t)(tiles < cap ? tiles : cap);
+    const size_t smem = (size_t)ovl::kRingSlots * kTile * sizeof(float) + ovl::kRingCtlBytes;
+    const void* kernel = carry ? (const void*)scan_ring_f32_kernel<Op, true> : (const void*)scan_ring_f32_kernel<Op, false>;
+    OVL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader) + tiles * 16, stream));
+    void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&n, (void*)&scratch};
+    OVL_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(ovl::kRingThreads), args, smem, stream));
+    return OVL_OK;
+}
+
 int check_scan_args(int op, const void* in, uint64_t lines, uint64_t n, const double* carry, const void* scratch,
                     uint64_t scratch_bytes) {
     if (!in) return OVL_ERR_NULL;
@@ -463,6 +505,7 @@ int run_scan(const float* in, float* out, uint64_t lines, uint64_t n, const doub
         cudaError_t e = launch_scan_pass<Op>(in, out, lines, n, carry, scratch, aligned, ovl::kScanOneTile, stream);
         return e == cudaSuccess ? OVL_OK : cuda_fail(e);
     }
+    if (lines == 1 && aligned && long_line_mode() == kModeRing) return launch_ring<Op>(in, out, n, carry, scratch, stream);
     if (use_lookback()) {
         // the descriptors must start out empty
         OVL_CUDA(cudaMemsetAsync(scratch, 0, ovl_scan_f32_scratch_bytes(lines, n), stream));

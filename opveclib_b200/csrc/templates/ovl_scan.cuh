@@ -98,6 +98,17 @@ __device__ __forceinline__ A shfl_any(A v, int lane) {
     }
 }
 
+template <typename A>
+__device__ __forceinline__ A shfl_xor_any(A v, int mask) {
+    if constexpr (sizeof(A) == 8) {
+        long long x = *reinterpret_cast<long long*>(&v);
+        x = __shfl_xor_sync(0xffffffffu, x, mask);
+        return *reinterpret_cast<A*>(&x);
+    } else {
+        return __shfl_xor_sync(0xffffffffu, v, mask);
+    }
+}
+
 // Asynchronous copy of one vector (BYTES = 4, 8 or 16) from global to shared memory, and the group fence.
 template <int BYTES>
 __device__ __forceinline__ void cp_async_vec(void* smem_dst, const void* gmem_src) {
@@ -459,6 +470,392 @@ __device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uin
         }
         if (total_out != nullptr && threadIdx.x == 0) total_out[line] = running;
     }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Ring scan: ONE long line in a single launch; every element is read from memory once and written once
+// (8 bytes per fp32 element) and no thread block ever waits for the block before it.
+//
+// One persistent block per SM.  Tile t belongs to block t % gridDim.x; the tiles b, b + G, b + 2G ... of block b
+// are its "waves" 0, 1, 2 ...  A tile travels through a ring of kRingSlots tile-sized slots in shared memory.
+// The block's warps have four roles, coupled only through shared-memory barriers (mbarrier):
+//   copy warp      one thread streams the block's tiles into free slots with bulk asynchronous copies
+//                  (cp.async.bulk, completion counted on the slot's `full` barrier), up to a whole ring ahead;
+//   reduce warps   as soon as a tile has landed they reduce it to its aggregate and publish that to global memory;
+//   prefix warp    for every wave, gathers the aggregates all blocks published for that wave and forms
+//                  carry-so-far (+) aggregates of the blocks to the left (`ready` barrier); each block keeps its
+//                  own copy of the carry over the waves, computed in the same order everywhere, so no block depends
+//                  on a value another block derived - only on the aggregates themselves;
+//   scan warps     scan the tile, seeded with that prefix, out of its slot, store the result and release the slot
+//                  (`empty` barrier).
+// Reduction runs ahead of the scan by as many tiles as the ring holds, which hides the trip of the aggregates
+// through L2; in steady state nobody waits.  Aggregates travel as two 8-byte words, each carrying 32 payload bits
+// and a 32-bit tag, so a word is valid on its own whenever its tag is set and no fence is needed; the host clears
+// the words before the launch.
+//
+// All blocks must be resident (cooperative launch, grid <= number of SMs).  Every wait is bounded: when one
+// expires the block records OVL_ERR_TIMEOUT in the status word, raises its abort flag, lets copies in flight
+// land, and leaves; nothing traps.
+constexpr int kRingSlots = 6;
+constexpr int kRingScanWarps = kScanBlock / 32;    // 16 warps scan a tile (VPT vectors per thread)
+constexpr int kRingReduceWarps = 4;                // 4 warps reduce a tile (4 * VPT vectors per thread)
+constexpr int kRingThreads = (kRingScanWarps + kRingReduceWarps + 2) * 32;
+constexpr int kRingMaxGrid = 256;
+constexpr int kRingGather = 8;                     // aggregates fetched per lane and round by the prefix warp
+constexpr uint32_t kRingSpinLimit = 1u << 22;
+constexpr uint32_t kRingCtlBytes = 1024;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bulk asynchronous copy global -> shared of `bytes` (multiple of 16, both addresses 16-byte aligned); completion
+// is counted in bytes on `bar`
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(smem_dst)),
+                 "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+template <int ID, int THREADS>
+__device__ __forceinline__ void named_bar_sync() {
+    asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(THREADS) : "memory");
+}
+
+template <typename Acc>
+struct RingCtl {
+    Acc prefix[kRingSlots];                        // exclusive prefix of the tile in the slot
+    Acc wtot[2][kRingScanWarps];                   // warp totals of the tile being scanned
+    Acc rpart[2][kRingReduceWarps];                // warp partials of the tile being reduced
+    uint64_t full[kRingSlots];                     // slot holds its tile             (copy thread + bytes landed)
+    uint64_t empty[kRingSlots];                    // slot has been read for the scan (one arrival per scan warp)
+    uint64_t ready[kRingSlots];                    // prefix[slot] is valid           (prefix warp)
+    int abort;
+    int stop[2];                                   // abort flag as latched for the scan warps' current step
+    int rstop[2];                                  // the same for the reduce warps
+};
+
+// bounded wait on a shared-memory barrier; gives up at once when the block is aborting
+__device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kRingSpinLimit; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void ring_fail(ScanHeader* hdr, volatile int* abort_flag) {
+    if (!*abort_flag) {
+        atomicExch(&hdr->status, kErrTimeout);
+        *abort_flag = 1;
+    }
+}
+
+template <typename Acc>
+__device__ __forceinline__ void ring_publish(uint64_t* desc, uint64_t tile, Acc a) {
+    uint64_t bits = 0;
+    memcpy(&bits, &a, sizeof(Acc));
+    const uint64_t w0 = (1ull << 32) | (bits & 0xffffffffull), w1 = (1ull << 32) | (bits >> 32);
+    asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(desc + 2 * tile), "l"(w0), "l"(w1) : "memory");
+}
+__device__ __forceinline__ void ring_peek(const uint64_t* desc, uint64_t tile, uint64_t& w0, uint64_t& w1) {
+    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(desc + 2 * tile) : "memory");
+}
+
+// slot index and barrier phase of a role's current wave, advanced without divisions
+struct RingCursor {
+    int slot;
+    uint32_t phase;
+    __device__ __forceinline__ RingCursor() : slot(0), phase(0) {}
+    __device__ __forceinline__ void advance() {
+        if (++slot == kRingSlots) {
+            slot = 0;
+            phase ^= 1u;
+        }
+    }
+};
+
+template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY>
+__device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry_in,
+                                          const uint64_t n, void* scratch) {
+    constexpr int VPT = kScanVpt;
+    constexpr int SW = kRingScanWarps, RW = kRingReduceWarps;
+    constexpr int RVPT = VPT * SW / RW;            // vectors per thread in the reduce warps
+    constexpr int R = kRingSlots;
+    constexpr uint32_t TILE = kScanBlock * VPT * VEC;
+    constexpr uint32_t TILE_BYTES = TILE * sizeof(T);
+    static_assert(sizeof(RingCtl<Acc>) <= kRingCtlBytes, "control block too large");
+    static_assert(TILE_BYTES % 16 == 0, "tiles must be whole 16-byte units");
+    static_assert(SW <= 32 && (SW & (SW - 1)) == 0, "warp totals are combined by one warp-wide scan");
+
+    extern __shared__ __align__(128) unsigned char ring_smem[];
+    RingCtl<Acc>* ctl = reinterpret_cast<RingCtl<Acc>*>(ring_smem + (size_t)R * TILE_BYTES);
+    volatile int* abort_flag = &ctl->abort;
+
+    ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
+    uint64_t* desc = reinterpret_cast<uint64_t*>(hdr + 1);
+    const uint64_t total_tiles = (n + TILE - 1) / TILE;
+    const uint32_t G = gridDim.x, b = blockIdx.x;
+    const uint32_t my_tiles = (total_tiles > b) ? (uint32_t)((total_tiles - b + G - 1) / G) : 0u;
+    const uint32_t tail = (uint32_t)(n - (total_tiles - 1) * TILE);      // valid elements of the last tile
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < R; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], SW);
+            mbar_init(&ctl->ready[s], 1);
+        }
+        ctl->abort = 0;
+        ctl->stop[0] = ctl->stop[1] = 0;
+        ctl->rstop[0] = ctl->rstop[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (wid < SW) {
+        // --------------------------------------------------------------------------------------- scan warps
+        RingCursor cur;
+        int parity = 0;
+        uint64_t tile = b;
+        for (uint32_t k = 0; k < my_tiles; ++k, tile += G, cur.advance(), parity ^= 1) {
+            if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
+            if (!ring_wait(&ctl->ready[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
+            const bool whole = (tile != total_tiles - 1) || tail == TILE;
+            const Vec<T, VEC>* sv = reinterpret_cast<const Vec<T, VEC>*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
+            const uint32_t v0 = (uint32_t)wid * 32 * VPT + lane;        // this thread's vectors: v0 + 32 j
+            Acc av[VPT][VEC];                                           // the tile's values, widened once
+            if (whole) {
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    const Vec<T, VEC> v = sv[v0 + j * 32];
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) av[j][e] = (Acc)v.v[e];
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < VPT; ++j) {
+                    const Vec<T, VEC> v = sv[v0 + j * 32];
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e)
+                        av[j][e] = ((v0 + j * 32) * VEC + e < tail) ? (Acc)v.v[e] : Op::template identity<Acc>();
+                }
+            }
+            const Acc exclusive = ctl->prefix[cur.slot];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->empty[cur.slot]);          // the slot may be refilled
+            // sweep 1: totals of each vector, scanned across the warp; base[j] = prefix in front of vector j
+            Acc base[VPT];
+            Acc run = Op::template identity<Acc>();
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                Acc t = av[j][0];
+#pragma unroll
+                for (int e = 1; e < VEC; ++e) t = Op::apply(t, av[j][e]);
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const Acc y = shfl_up_any(t, d);
+                    if (lane >= d) t = Op::apply(y, t);
+                }
+                Acc excl = shfl_up_any(t, 1);
+                if (lane == 0) excl = Op::template identity<Acc>();
+                base[j] = Op::apply(run, excl);
+                run = Op::apply(run, shfl_any(t, 31));
+            }
+            if (lane == 0) ctl->wtot[parity][wid] = run;
+            if (threadIdx.x == 0) ctl->stop[parity] = *abort_flag;
+            named_bar_sync<1, SW * 32>();
+            if (ctl->stop[parity]) break;                               // same value for every scan thread
+            // prefix of the warps to the left: one scan over the SW warp totals, by every warp
+            Acc w = (lane < SW) ? ctl->wtot[parity][lane] : Op::template identity<Acc>();
+#pragma unroll
+            for (int d = 1; d < SW; d <<= 1) {
+                const Acc y = shfl_up_any(w, d);
+                if (lane >= d) w = Op::apply(y, w);
+            }
+            Acc warp_excl = shfl_any(w, (wid + 31) & 31);
+            if (wid == 0) warp_excl = Op::template identity<Acc>();
+            const Acc offset = Op::apply(exclusive, warp_excl);
+            // sweep 2: running values, rounded to T on store
+            T* dst = out + tile * TILE;
+#pragma unroll
+            for (int j = 0; j < VPT; ++j) {
+                const uint32_t off = (v0 + j * 32) * VEC;
+                Acc p = Op::apply(offset, base[j]);
+                if (whole) {
+                    Vec<T, VEC> v;
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) {
+                        p = Op::apply(p, av[j][e]);
+                        v.v[e] = (T)p;
+                    }
+                    store_vec<T, VEC>(dst + off, v);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) {
+                        p = Op::apply(p, av[j][e]);
+                        if (off + e < tail) dst[off + e] = (T)p;
+                    }
+                }
+            }
+        }
+    } else if (wid < SW + RW) {
+        // ------------------------------------------------------------------------------------- reduce warps
+        RingCursor cur;
+        int parity = 0;
+        const int rw = wid - SW;
+        uint64_t tile = b;
+        for (uint32_t k = 0; k < my_tiles; ++k, tile += G, cur.advance(), parity ^= 1) {
+            if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
+            const bool whole = (tile != total_tiles - 1) || tail == TILE;
+            const Vec<T, VEC>* sv = reinterpret_cast<const Vec<T, VEC>*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
+            const uint32_t v0 = (uint32_t)rw * 32 * RVPT + lane;
+            Acc part[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) part[u] = Op::template identity<Acc>();
+            if (whole) {
+#pragma unroll
+                for (int j = 0; j < RVPT; ++j) {
+                    const Vec<T, VEC> v = sv[v0 + j * 32];
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) part[j & 3] = Op::apply(part[j & 3], (Acc)v.v[e]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < RVPT; ++j) {
+                    const Vec<T, VEC> v = sv[v0 + j * 32];
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e)
+                        if ((v0 + j * 32) * VEC + e < tail) part[j & 3] = Op::apply(part[j & 3], (Acc)v.v[e]);
+                }
+            }
+            Acc run = Op::apply(Op::apply(part[0], part[1]), Op::apply(part[2], part[3]));
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) run = Op::apply(run, shfl_down_any(run, d));
+            if (lane == 0) ctl->rpart[parity][rw] = run;
+            if (rw == 0 && lane == 0) ctl->rstop[parity] = *abort_flag;
+            named_bar_sync<2, RW * 32>();
+            if (ctl->rstop[parity]) break;                              // same value for every reduce thread
+            if (rw == 0 && lane == 0) {
+                Acc a = ctl->rpart[parity][0];
+#pragma unroll
+                for (int w = 1; w < RW; ++w) a = Op::apply(a, ctl->rpart[parity][w]);
+                ring_publish<Acc>(desc, tile, a);
+            }
+        }
+    } else if (wid == SW + RW) {
+        // ---------------------------------------------------------------------------------------- copy warp
+        if (lane == 0) {
+            RingCursor cur;
+            uint32_t issued = 0;
+            uint64_t tile = b;
+            for (uint32_t k = 0; k < my_tiles; ++k, tile += G, cur.advance()) {
+                // second and later uses of a slot: wait until the scan of its previous tile has read it
+                if (k >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag)) {
+                    ring_fail(hdr, abort_flag);
+                    break;
+                }
+                const uint32_t valid = (tile == total_tiles - 1) ? tail : TILE;
+                const uint32_t bulk = (uint32_t)(valid * sizeof(T)) & ~15u;
+                const T* src = in + tile * TILE;
+                T* slot_data = reinterpret_cast<T*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
+                for (uint32_t i = bulk / (uint32_t)sizeof(T); i < valid; ++i) slot_data[i] = src[i];   // ragged end
+                if (bulk) {
+                    mbar_arrive_expect_tx(&ctl->full[cur.slot], bulk);
+                    bulk_load(slot_data, src, bulk, &ctl->full[cur.slot]);
+                } else {
+                    mbar_arrive(&ctl->full[cur.slot]);
+                }
+                issued = k + 1;
+            }
+            if (*abort_flag) {
+                // let the copies that may still be in flight land before the block gives up its shared memory
+                for (uint32_t k = (issued > (uint32_t)R) ? issued - R : 0; k < issued; ++k)
+                    for (uint32_t i = 0; i < kRingSpinLimit; ++i)
+                        if (mbar_try_wait(&ctl->full[k % R], (k / R) & 1u)) break;
+            }
+        }
+    } else {
+        // -------------------------------------------------------------------------------------- prefix warp
+        RingCursor cur;
+        Acc carry = Op::template identity<Acc>();
+        if (HAS_CARRY) carry = *carry_in;
+        uint64_t first = 0;
+        for (uint32_t j = 0; j < my_tiles; ++j, first += G, cur.advance()) {
+            if (*abort_flag) break;
+            const uint32_t gj = (uint32_t)((total_tiles - first < G) ? (total_tiles - first) : G);
+            Acc excl = Op::template identity<Acc>(), tot = Op::template identity<Acc>();
+            bool failed = false;
+            for (uint32_t base_i = 0; base_i < gj; base_i += 32 * kRingGather) {
+                uint64_t w0[kRingGather], w1[kRingGather];
+#pragma unroll
+                for (int i = 0; i < kRingGather; ++i) {
+                    const uint32_t idx = base_i + i * 32 + lane;
+                    w0[i] = w1[i] = 0;
+                    if (idx < gj) ring_peek(desc, first + idx, w0[i], w1[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < kRingGather; ++i) {
+                    const uint32_t idx = base_i + i * 32 + lane;
+                    if (idx < gj) {
+                        uint32_t spins = 0;
+                        while (((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) && spins < kRingSpinLimit && !*abort_flag) {
+                            if (spins > 4) __nanosleep(64);
+                            ring_peek(desc, first + idx, w0[i], w1[i]);
+                            ++spins;
+                        }
+                        if ((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) {
+                            failed = true;
+                        } else {
+                            const uint64_t bits = (w0[i] & 0xffffffffull) | (w1[i] << 32);
+                            Acc v;
+                            memcpy(&v, &bits, sizeof(Acc));
+                            tot = Op::apply(tot, v);
+                            if (idx < b) excl = Op::apply(excl, v);
+                        }
+                    }
+                }
+            }
+            if (__any_sync(0xffffffffu, failed)) {
+                if (lane == 0) ring_fail(hdr, abort_flag);
+                break;
+            }
+            // lanes hold interleaved partial results; combine in a fixed butterfly so that every block derives
+            // the same carry
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                tot = Op::apply(tot, shfl_xor_any(tot, d));
+                excl = Op::apply(excl, shfl_xor_any(excl, d));
+            }
+            // prefix[slot] of the slot's previous tile must have been read
+            if (j >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag)) {
+                if (lane == 0) ring_fail(hdr, abort_flag);
+                break;
+            }
+            if (lane == 0) {
+                ctl->prefix[cur.slot] = Op::apply(carry, excl);
+                mbar_arrive(&ctl->ready[cur.slot]);
+            }
+            carry = Op::apply(carry, tot);
+        }
+    }
+    __syncthreads();
 }
 
 // Reduction of n elements to one Acc, combination order fixed by the launch shape: per-thread strided partials,

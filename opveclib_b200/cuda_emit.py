@@ -40,12 +40,17 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv13'
+TEMPLATE_VERSION = 'tv14'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
 SCAN_VPT = 4
 SCAN_HEADER_BYTES = 16
+# must match kRingThreads / kRingSlots / kRingCtlBytes / kRingMaxGrid of csrc/templates/ovl_scan.cuh
+RING_THREADS = 704
+RING_SLOTS = 6
+RING_CTL_BYTES = 1024
+RING_MAX_GRID = 256
 
 
 def ctype(dtype):
@@ -433,7 +438,7 @@ def emit_cuda(kernel, name):
         multi = spec.n > tile                       # several tiles per line: three passes
         tpl = (spec.n + tile - 1) // tile if multi else 1
         tiles = tpl * spec.lines
-        scratch = SCAN_HEADER_BYTES + tiles * max(acc_size, 8)
+        scratch = SCAN_HEADER_BYTES + tiles * 16     # one fp64 / two tagged words per tile
         op = 'ovl::OpAdd' if spec.op == 'add' else 'ovl::OpMul'
         can_align = spec.lines == 1 or spec.n % vec == 0
         agg_ptr = '(' + acc + '*)((char*)scratch + ' + str(SCAN_HEADER_BYTES) + ')'
@@ -456,7 +461,18 @@ def emit_cuda(kernel, name):
                     '    ovl::scan_aggregates<' + acc + ', ' + op + ', false, true>(' + agg_ptr + ', ' + str(spec.lines) +
                     'ull, ' + str(tpl) + 'ull, nullptr, nullptr);',
                     '}', '']
-        meta['scan'] = {'name': name, 'aligned_variant': bool(can_align), 'three_pass': bool(multi),
+        ring = None
+        if multi and spec.lines == 1:
+            # one long line, pointers aligned: a single cooperative launch that moves every element once
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(RING_THREADS) + ', 1) ' + name +
+                    '_ring(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0, void* scratch) {',
+                    '    ovl::scan_ring<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', false>(in0, out0, nullptr, ' +
+                    str(spec.n) + 'ull, scratch);',
+                    '}', '']
+            ring = {'symbol': name + '_ring', 'block': RING_THREADS, 'max_grid': RING_MAX_GRID,
+                    'smem': RING_SLOTS * tile * spec.dtype.itemsize + RING_CTL_BYTES,
+                    'zero_bytes': SCAN_HEADER_BYTES + tiles * 16}
+        meta['scan'] = {'name': name, 'aligned_variant': bool(can_align), 'three_pass': bool(multi), 'ring': ring,
                         'block': SCAN_BLOCK, 'tiles': tiles, 'scratch_bytes': scratch, 'zero_bytes': SCAN_HEADER_BYTES,
                         'blocks_per_sm': 2, 'align_bytes': vec * spec.dtype.itemsize, 'lines': spec.lines, 'n': spec.n,
                         'op': spec.op}

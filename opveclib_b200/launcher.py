@@ -14,7 +14,11 @@ class OvlKernelSpec(ctypes.Structure):
                 ('dynamic_smem_bytes', ctypes.c_uint32), ('n_inputs', ctypes.c_uint32),
                 ('n_outputs', ctypes.c_uint32), ('dtypes', ctypes.POINTER(ctypes.c_int32)),
                 ('lens', ctypes.POINTER(ctypes.c_uint64)), ('align_bytes', ctypes.POINTER(ctypes.c_uint32)),
-                ('scratch_bytes', ctypes.c_uint64), ('scratch_zero_bytes', ctypes.c_uint64)]
+                ('scratch_bytes', ctypes.c_uint64), ('scratch_zero_bytes', ctypes.c_uint64),
+                ('flags', ctypes.c_uint32)]
+
+
+KERNEL_COOPERATIVE = 1
 
 
 EXPORTS = ['ovl_version', 'ovl_status_string', 'ovl_last_cuda_error', 'ovl_device_sm_count', 'ovl_module_load',
@@ -104,14 +108,14 @@ class Kernel(object):
     """One launchable kernel: symbol + signature + launch shape."""
 
     def __init__(self, module, symbol, grid, block, dtypes, lens, n_inputs, aligns=None, scratch_bytes=0,
-                 scratch_zero_bytes=0, smem=0):
+                 scratch_zero_bytes=0, smem=0, cooperative=False):
         n = len(dtypes)
         self._dt = (ctypes.c_int32 * max(1, n))(*dtypes)
         self._ln = (ctypes.c_uint64 * max(1, n))(*lens)
         self._al = (ctypes.c_uint32 * max(1, n))(*(aligns or [0] * n))
         self._sym = symbol.encode()
         spec = OvlKernelSpec(self._sym, grid, block, smem, n_inputs, n - n_inputs, self._dt, self._ln, self._al,
-                             scratch_bytes, scratch_zero_bytes)
+                             scratch_bytes, scratch_zero_bytes, KERNEL_COOPERATIVE if cooperative else 0)
         self.handle = ctypes.c_void_p()
         self.module = module
         self.scratch_bytes = scratch_bytes

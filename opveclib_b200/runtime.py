@@ -52,14 +52,14 @@ class KernelPlan(object):
             self._sms[device] = _torch().cuda.get_device_properties(device).multi_processor_count
         return self._sms[device]
 
-    def _make(self, device, symbol, grid, block, use_in, use_out, aligns, scratch=0, zero=0):
+    def _make(self, device, symbol, grid, block, use_in, use_out, aligns, scratch=0, zero=0, smem=0, cooperative=False):
         """A launchable kernel of this plan's module taking inputs[use_in] and outputs[use_out]."""
         key = (symbol, device)
         if key not in self._variants:
             types = [self.in_types[i] for i in use_in] + [self.out_types[i] for i in use_out]
             self._variants[key] = (launcher.Kernel(self._module(device), symbol, grid, block,
                                                    [t.dtype.code for t in types], [t.size for t in types], len(use_in),
-                                                   aligns, scratch, zero), use_in, use_out)
+                                                   aligns, scratch, zero, smem, cooperative), use_in, use_out)
         return self._variants[key]
 
     def _passes(self, which, device):
@@ -84,6 +84,11 @@ class KernelPlan(object):
         cap = sms * m['blocks_per_sm']
         scratch = m['scratch_bytes']
         passes = []
+        ring = m.get('ring')
+        if ring and which == 'scan' and os.environ.get('OVL_SCAN_MODE') != 'threepass':
+            grid = max(1, min(m['tiles'], sms, ring['max_grid']))
+            return [self._make(device, ring['symbol'], grid, ring['block'], [0], [0], [al, al], scratch,
+                               ring['zero_bytes'], ring['smem'], True)]
         if m['three_pass']:
             passes.append(self._make(device, name + '_agg' + suffix, max(1, min(m['tiles'], cap)), block, [0], [], [al],
                                      scratch, m['zero_bytes']))
