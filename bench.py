@@ -332,7 +332,8 @@ def main():
 
         def step():
             scan(x, out=y)
-        kernels_per_step = 3 if world == 1 else 4     # tile aggregates, aggregate prefixes (x2 when sharded), tile scans
+        # one GPU: the ring scan (one kernel); sharded: tile aggregates, shard total, aggregate prefixes, tile scans
+        kernels_per_step = 1 if world == 1 else 4
         finish = scan.check_status
     else:
         if workload != 'c4' and world > 1:

@@ -30,6 +30,10 @@ constexpr uint32_t kScanSpinLimit = 1u << 22;
 constexpr int32_t kErrTimeout = 8;  // OVL_ERR_TIMEOUT
 constexpr int kScanOneTile = 0, kScanLookback = 1, kScanPrefixed = 2;
 
+template <typename A> struct IsDouble { static constexpr bool value = false; };
+template <> struct IsDouble<double> { static constexpr bool value = true; };
+#define OVL_IS_DOUBLE(A) (ovl::IsDouble<A>::value)
+
 struct OpAdd {
     template <typename A> static __device__ __forceinline__ A identity() { return A(0); }
     template <typename A> static __device__ __forceinline__ A apply(A a, A b) { return a + b; }
@@ -69,7 +73,7 @@ __device__ __forceinline__ void st_flag(uint32_t* p, uint32_t v) {
 
 template <typename A>
 __device__ __forceinline__ A shfl_up_any(A v, int delta) {
-    if constexpr (sizeof(A) == 8) {
+    if constexpr (sizeof(A) == 8 && !OVL_IS_DOUBLE(A)) {
         long long x = *reinterpret_cast<long long*>(&v);
         x = __shfl_up_sync(0xffffffffu, x, delta);
         return *reinterpret_cast<A*>(&x);
@@ -79,7 +83,7 @@ __device__ __forceinline__ A shfl_up_any(A v, int delta) {
 }
 template <typename A>
 __device__ __forceinline__ A shfl_down_any(A v, int delta) {
-    if constexpr (sizeof(A) == 8) {
+    if constexpr (sizeof(A) == 8 && !OVL_IS_DOUBLE(A)) {
         long long x = *reinterpret_cast<long long*>(&v);
         x = __shfl_down_sync(0xffffffffu, x, delta);
         return *reinterpret_cast<A*>(&x);
@@ -89,7 +93,7 @@ __device__ __forceinline__ A shfl_down_any(A v, int delta) {
 }
 template <typename A>
 __device__ __forceinline__ A shfl_any(A v, int lane) {
-    if constexpr (sizeof(A) == 8) {
+    if constexpr (sizeof(A) == 8 && !OVL_IS_DOUBLE(A)) {
         long long x = *reinterpret_cast<long long*>(&v);
         x = __shfl_sync(0xffffffffu, x, lane);
         return *reinterpret_cast<A*>(&x);
@@ -100,7 +104,7 @@ __device__ __forceinline__ A shfl_any(A v, int lane) {
 
 template <typename A>
 __device__ __forceinline__ A shfl_xor_any(A v, int mask) {
-    if constexpr (sizeof(A) == 8) {
+    if constexpr (sizeof(A) == 8 && !OVL_IS_DOUBLE(A)) {
         long long x = *reinterpret_cast<long long*>(&v);
         x = __shfl_xor_sync(0xffffffffu, x, mask);
         return *reinterpret_cast<A*>(&x);
@@ -481,13 +485,15 @@ __device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uin
 // The block's warps have four roles, coupled only through shared-memory barriers (mbarrier):
 //   copy warp      one thread streams the block's tiles into free slots with bulk asynchronous copies
 //                  (cp.async.bulk, completion counted on the slot's `full` barrier), up to a whole ring ahead;
-//   reduce warps   as soon as a tile has landed they reduce it to its aggregate and publish that to global memory;
+//   reduce warps   as soon as a tile has landed they total its sixteen chunks (`reduced` barrier) and publish the sum
+//                  of those, the tile aggregate, to global memory;
 //   prefix warp    for every wave, gathers the aggregates all blocks published for that wave and forms
-//                  carry-so-far (+) aggregates of the blocks to the left (`ready` barrier); each block keeps its
-//                  own copy of the carry over the waves, computed in the same order everywhere, so no block depends
-//                  on a value another block derived - only on the aggregates themselves;
-//   scan warps     scan the tile, seeded with that prefix, out of its slot, store the result and release the slot
-//                  (`empty` barrier).
+//                  carry-so-far (+) aggregates of the blocks to the left; each block keeps its own copy of the carry
+//                  over the waves, computed in the same order everywhere, so no block depends on a value another
+//                  block derived - only on the aggregates themselves.  It then leaves the prefix in front of every
+//                  chunk of the tile in shared memory (`ready` barrier);
+//   scan warps     each scans one chunk of the tile out of its slot, seeded with the chunk's prefix, stores the
+//                  result and releases the slot (`empty` barrier); the sixteen scan warps never wait for each other.
 // Reduction runs ahead of the scan by as many tiles as the ring holds, which hides the trip of the aggregates
 // through L2; in steady state nobody waits.  Aggregates travel as two 8-byte words, each carrying 32 payload bits
 // and a 32-bit tag, so a word is valid on its own whenever its tag is set and no fence is needed; the host clears
@@ -498,12 +504,12 @@ __device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uin
 // land, and leaves; nothing traps.
 constexpr int kRingSlots = 6;
 constexpr int kRingScanWarps = kScanBlock / 32;    // 16 warps scan a tile (VPT vectors per thread)
-constexpr int kRingReduceWarps = 4;                // 4 warps reduce a tile (4 * VPT vectors per thread)
+constexpr int kRingReduceWarps = 8;                // 8 warps reduce a tile (2 * VPT vectors per thread)
 constexpr int kRingThreads = (kRingScanWarps + kRingReduceWarps + 2) * 32;
 constexpr int kRingMaxGrid = 256;
 constexpr int kRingGather = 8;                     // aggregates fetched per lane and round by the prefix warp
 constexpr uint32_t kRingSpinLimit = 1u << 22;
-constexpr uint32_t kRingCtlBytes = 1024;
+constexpr uint32_t kRingCtlBytes = 2048;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -540,19 +546,20 @@ __device__ __forceinline__ void named_bar_sync() {
 
 template <typename Acc>
 struct RingCtl {
-    Acc prefix[kRingSlots];                        // exclusive prefix of the tile in the slot
-    Acc wtot[2][kRingScanWarps];                   // warp totals of the tile being scanned
-    Acc rpart[2][kRingReduceWarps];                // warp partials of the tile being reduced
+    Acc wprefix[kRingSlots][kRingScanWarps];       // exclusive prefix of each scan warp's chunk of the tile in the slot
+    Acc ctot[kRingSlots][kRingScanWarps];          // totals of those chunks
+    Acc rpart[2][kRingReduceWarps];                // per-warp partials of the tile being reduced
     uint64_t full[kRingSlots];                     // slot holds its tile             (copy thread + bytes landed)
+    uint64_t reduced[kRingSlots];                  // ctot[slot] is valid             (one arrival per reduce warp)
+    uint64_t ready[kRingSlots];                    // wprefix[slot] is valid          (prefix warp)
     uint64_t empty[kRingSlots];                    // slot has been read for the scan (one arrival per scan warp)
-    uint64_t ready[kRingSlots];                    // prefix[slot] is valid           (prefix warp)
     int abort;
-    int stop[2];                                   // abort flag as latched for the scan warps' current step
-    int rstop[2];                                  // the same for the reduce warps
+    int rstop[2];                                  // abort flag as latched for the reduce warps' current step
 };
 
 // bounded wait on a shared-memory barrier; gives up at once when the block is aborting
 __device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
     for (uint32_t i = 0; i < kRingSpinLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
@@ -595,13 +602,13 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                                           const uint64_t n, void* scratch) {
     constexpr int VPT = kScanVpt;
     constexpr int SW = kRingScanWarps, RW = kRingReduceWarps;
-    constexpr int RVPT = VPT * SW / RW;            // vectors per thread in the reduce warps
+    constexpr int CPR = SW / RW;                   // chunks (one per scan warp) handled by one reduce warp
     constexpr int R = kRingSlots;
     constexpr uint32_t TILE = kScanBlock * VPT * VEC;
     constexpr uint32_t TILE_BYTES = TILE * sizeof(T);
     static_assert(sizeof(RingCtl<Acc>) <= kRingCtlBytes, "control block too large");
     static_assert(TILE_BYTES % 16 == 0, "tiles must be whole 16-byte units");
-    static_assert(SW <= 32 && (SW & (SW - 1)) == 0, "warp totals are combined by one warp-wide scan");
+    static_assert(SW <= 32 && (SW & (SW - 1)) == 0 && SW % RW == 0, "chunk totals are scanned by one warp");
 
     extern __shared__ __align__(128) unsigned char ring_smem[];
     RingCtl<Acc>* ctl = reinterpret_cast<RingCtl<Acc>*>(ring_smem + (size_t)R * TILE_BYTES);
@@ -618,11 +625,11 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
     if (threadIdx.x == 0) {
         for (int s = 0; s < R; ++s) {
             mbar_init(&ctl->full[s], 1);
-            mbar_init(&ctl->empty[s], SW);
+            mbar_init(&ctl->reduced[s], RW);
             mbar_init(&ctl->ready[s], 1);
+            mbar_init(&ctl->empty[s], SW);
         }
         ctl->abort = 0;
-        ctl->stop[0] = ctl->stop[1] = 0;
         ctl->rstop[0] = ctl->rstop[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -631,16 +638,18 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
 
     if (wid < SW) {
         // --------------------------------------------------------------------------------------- scan warps
+        // warp `wid` scans chunk `wid` (32 * VPT vectors) of every tile of the block, on its own: the prefix in
+        // front of the chunk is already in shared memory when the warp starts, so warps never wait for each other
         RingCursor cur;
-        int parity = 0;
         uint64_t tile = b;
-        for (uint32_t k = 0; k < my_tiles; ++k, tile += G, cur.advance(), parity ^= 1) {
+        const uint32_t v0 = (uint32_t)wid * 32 * VPT + lane;            // this thread's vectors: v0 + 32 j
+        for (uint32_t k = 0; k < my_tiles; ++k, tile += G, cur.advance()) {
             if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
             if (!ring_wait(&ctl->ready[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
+            if (*abort_flag) break;
             const bool whole = (tile != total_tiles - 1) || tail == TILE;
             const Vec<T, VEC>* sv = reinterpret_cast<const Vec<T, VEC>*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
-            const uint32_t v0 = (uint32_t)wid * 32 * VPT + lane;        // this thread's vectors: v0 + 32 j
-            Acc av[VPT][VEC];                                           // the tile's values, widened once
+            Acc av[VPT][VEC];                                           // the chunk's values, widened once
             if (whole) {
 #pragma unroll
                 for (int j = 0; j < VPT; ++j) {
@@ -657,12 +666,12 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                         av[j][e] = ((v0 + j * 32) * VEC + e < tail) ? (Acc)v.v[e] : Op::template identity<Acc>();
                 }
             }
-            const Acc exclusive = ctl->prefix[cur.slot];
+            const Acc offset = ctl->wprefix[cur.slot][wid];
             __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl->empty[cur.slot]);          // the slot may be refilled
+            if (lane == 0) mbar_arrive(&ctl->empty[cur.slot]);          // this warp is done with the slot
             // sweep 1: totals of each vector, scanned across the warp; base[j] = prefix in front of vector j
             Acc base[VPT];
-            Acc run = Op::template identity<Acc>();
+            Acc run = offset;
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 Acc t = av[j][0];
@@ -676,28 +685,14 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                 Acc excl = shfl_up_any(t, 1);
                 if (lane == 0) excl = Op::template identity<Acc>();
                 base[j] = Op::apply(run, excl);
-                run = Op::apply(run, shfl_any(t, 31));
+                if (j + 1 < VPT) run = Op::apply(run, shfl_any(t, 31));
             }
-            if (lane == 0) ctl->wtot[parity][wid] = run;
-            if (threadIdx.x == 0) ctl->stop[parity] = *abort_flag;
-            named_bar_sync<1, SW * 32>();
-            if (ctl->stop[parity]) break;                               // same value for every scan thread
-            // prefix of the warps to the left: one scan over the SW warp totals, by every warp
-            Acc w = (lane < SW) ? ctl->wtot[parity][lane] : Op::template identity<Acc>();
-#pragma unroll
-            for (int d = 1; d < SW; d <<= 1) {
-                const Acc y = shfl_up_any(w, d);
-                if (lane >= d) w = Op::apply(y, w);
-            }
-            Acc warp_excl = shfl_any(w, (wid + 31) & 31);
-            if (wid == 0) warp_excl = Op::template identity<Acc>();
-            const Acc offset = Op::apply(exclusive, warp_excl);
             // sweep 2: running values, rounded to T on store
             T* dst = out + tile * TILE;
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const uint32_t off = (v0 + j * 32) * VEC;
-                Acc p = Op::apply(offset, base[j]);
+                Acc p = base[j];
                 if (whole) {
                     Vec<T, VEC> v;
 #pragma unroll
@@ -717,6 +712,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         }
     } else if (wid < SW + RW) {
         // ------------------------------------------------------------------------------------- reduce warps
+        // reduce warp rw totals the chunks CPR*rw .. CPR*rw + CPR - 1 of every tile as soon as it has landed
         RingCursor cur;
         int parity = 0;
         const int rw = wid - SW;
@@ -725,31 +721,39 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
             if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
             const bool whole = (tile != total_tiles - 1) || tail == TILE;
             const Vec<T, VEC>* sv = reinterpret_cast<const Vec<T, VEC>*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
-            const uint32_t v0 = (uint32_t)rw * 32 * RVPT + lane;
-            Acc part[4];
+            Acc part[CPR];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) part[u] = Op::template identity<Acc>();
-            if (whole) {
+            for (int q = 0; q < CPR; ++q) {
+                const uint32_t v0 = (uint32_t)(rw * CPR + q) * 32 * VPT + lane;
+                Acc pj[VPT];
 #pragma unroll
-                for (int j = 0; j < RVPT; ++j) {
+                for (int j = 0; j < VPT; ++j) {
                     const Vec<T, VEC> v = sv[v0 + j * 32];
-#pragma unroll
-                    for (int e = 0; e < VEC; ++e) part[j & 3] = Op::apply(part[j & 3], (Acc)v.v[e]);
-                }
-            } else {
-#pragma unroll
-                for (int j = 0; j < RVPT; ++j) {
-                    const Vec<T, VEC> v = sv[v0 + j * 32];
+                    pj[j] = Op::template identity<Acc>();
 #pragma unroll
                     for (int e = 0; e < VEC; ++e)
-                        if ((v0 + j * 32) * VEC + e < tail) part[j & 3] = Op::apply(part[j & 3], (Acc)v.v[e]);
+                        if (whole || (v0 + j * 32) * VEC + e < tail) pj[j] = Op::apply(pj[j], (Acc)v.v[e]);
                 }
-            }
-            Acc run = Op::apply(Op::apply(part[0], part[1]), Op::apply(part[2], part[3]));
+                part[q] = pj[0];
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) run = Op::apply(run, shfl_down_any(run, d));
-            if (lane == 0) ctl->rpart[parity][rw] = run;
-            if (rw == 0 && lane == 0) ctl->rstop[parity] = *abort_flag;
+                for (int j = 1; j < VPT; ++j) part[q] = Op::apply(part[q], pj[j]);
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1)
+#pragma unroll
+                for (int q = 0; q < CPR; ++q) part[q] = Op::apply(part[q], shfl_down_any(part[q], d));
+            if (lane == 0) {
+                Acc sum = part[0];
+                ctl->ctot[cur.slot][rw * CPR] = part[0];
+#pragma unroll
+                for (int q = 1; q < CPR; ++q) {
+                    ctl->ctot[cur.slot][rw * CPR + q] = part[q];
+                    sum = Op::apply(sum, part[q]);
+                }
+                ctl->rpart[parity][rw] = sum;
+                mbar_arrive(&ctl->reduced[cur.slot]);
+                if (rw == 0) ctl->rstop[parity] = *abort_flag;
+            }
             named_bar_sync<2, RW * 32>();
             if (ctl->rstop[parity]) break;                              // same value for every reduce thread
             if (rw == 0 && lane == 0) {
@@ -843,15 +847,24 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                 tot = Op::apply(tot, shfl_xor_any(tot, d));
                 excl = Op::apply(excl, shfl_xor_any(excl, d));
             }
-            // prefix[slot] of the slot's previous tile must have been read
-            if (j >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag)) {
+            // wprefix[slot] of the slot's previous tile must have been read, and this tile's chunk totals written
+            if ((j >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag)) ||
+                !ring_wait(&ctl->reduced[cur.slot], cur.phase, abort_flag)) {
                 if (lane == 0) ring_fail(hdr, abort_flag);
                 break;
             }
-            if (lane == 0) {
-                ctl->prefix[cur.slot] = Op::apply(carry, excl);
-                mbar_arrive(&ctl->ready[cur.slot]);
+            // exclusive scan of the chunk totals, seeded with the prefix in front of the tile
+            Acc c = (lane < SW) ? ctl->ctot[cur.slot][lane] : Op::template identity<Acc>();
+#pragma unroll
+            for (int d = 1; d < SW; d <<= 1) {
+                const Acc y = shfl_up_any(c, d);
+                if (lane >= d) c = Op::apply(y, c);
             }
+            Acc cexcl = shfl_up_any(c, 1);
+            if (lane == 0) cexcl = Op::template identity<Acc>();
+            if (lane < SW) ctl->wprefix[cur.slot][lane] = Op::apply(Op::apply(carry, excl), cexcl);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->ready[cur.slot]);
             carry = Op::apply(carry, tot);
         }
     }

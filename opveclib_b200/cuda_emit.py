@@ -40,16 +40,16 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv14'
+TEMPLATE_VERSION = 'tv19'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
 SCAN_VPT = 4
 SCAN_HEADER_BYTES = 16
 # must match kRingThreads / kRingSlots / kRingCtlBytes / kRingMaxGrid of csrc/templates/ovl_scan.cuh
-RING_THREADS = 704
+RING_THREADS = 832
 RING_SLOTS = 6
-RING_CTL_BYTES = 1024
+RING_CTL_BYTES = 2048
 RING_MAX_GRID = 256
 
 
