@@ -143,6 +143,9 @@ def build_graph(workload, rows_local=None, n_local=None):
     if workload == 'c3_grad':
         op = ns.lstm_grad(z(512, 4096), z(512, 1024), z(512, 1024), z(512, 1024), forget_bias=0.0)
         return [op[0], op[1]], 512 * 1024, 48
+    if workload == 'matvec':
+        # reduction loop per row (documentation/programming.rst:320-344): the matrix is read once, 4 B per element
+        return [cases.user_ops(ns).matvec(z(16384, 8192), z(8192))], 16384 * 8192, 4
     raise ValueError('unknown workload ' + workload)
 
 
@@ -151,7 +154,7 @@ def precompile():
     from opveclib_b200 import runtime
     for n in (1, 2, 4, 8):
         runtime.compile_outputs(build_graph('c4', rows_local=C4_ROWS // n)[0])
-    for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'light16'):
+    for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'light16', 'matvec'):
         runtime.compile_outputs(build_graph(w)[0])
 
 
@@ -200,7 +203,7 @@ def cpu_reference_run(workload, iterations):
     else:
         table = {'c2_cumsum': 'c2_cumsum_4096x8192', 'c2_cumprod': 'c2_cumprod_4096x8192', 'c1': 'c1_chain_1048576',
                  'c1_shift': 'c1_shift_1048576', 'c3': 'c3_lstm_512x1024', 'c3_grad': 'c3_lstm_grad_512x1024'}
-        name, sample = table[workload], 'the full workload'
+        name, sample = table.get(workload, workload), 'the full workload'
         outs, elements, _ = build_graph(workload)
         from opveclib_b200.opgraph import build_op_dag
         types = build_op_dag(*outs).input_types
@@ -223,7 +226,7 @@ def cpu_reference_run(workload, iterations):
         elif workload == 'c5':
             outs = [ns.cumsum(inputs[0])]
         else:
-            raise RuntimeError('oracle/_ref is missing and no port is wired for ' + workload)
+            outs = rebuild_with_inputs(workload, inputs, None)
         threads = runner.hardware_threads()
         _, times = runner.profile(outs, num_threads=0, iterations=iterations)
         ms = sum(times.values())
@@ -266,13 +269,14 @@ def workload_config(workload, n):
         'c3': 'LSTM cell forward, gates fp32 [512, 4096], c [512, 1024]',
         'c3_grad': 'LSTM cell gradient, gates fp32 [512, 4096], c/dc/dh [512, 1024]',
         'c5': 'cumsum along the sharded axis, fp32 [2^31] normal(0,1), contiguous shards, fp64 carry exchange',
+        'matvec': 'matrix-vector product as a per-row reduction loop, fp32 [16384, 8192] x [8192] normal(0,1)',
     }
     if workload == 'c5' and C5_TOTAL != 1 << 31:
         names['c5'] = 'cumsum along the sharded axis, fp32 [%d] normal(0,1) (reduced case)' % C5_TOTAL
     if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
         names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
-            'l2': 'inputs larger than L2 (126 MB)' if workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod')
+            'l2': 'inputs larger than L2 (126 MB)' if workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec')
             else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
 
 
@@ -495,6 +499,8 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
         return [cases.c1_chain(ns, np_inputs[0])]
     if workload == 'c1_shift':
         return [cases.user_ops(ns).shift_cyclic(np_inputs[0])]
+    if workload == 'matvec':
+        return [cases.user_ops(ns).matvec(np_inputs[0], np_inputs[1])]
     if workload == 'c3':
         op = ns.lstm(np_inputs[0], np_inputs[1], forget_bias=0.0)
         return [op[0], op[1]]

@@ -128,9 +128,12 @@ int ovl_read_kernel_status(const void* scratch, void* cuda_stream, int32_t* out_
 /* Inclusive scan (op: 0 = sum, 1 = product) of `lines` contiguous lines of `n` fp32 elements each, device
  * memory in and out, with the same cooperative kernels the code generator uses for recognised accumulate loops
  * (the reference's one-worker-per-line loop: opveclib/examples/test_accumulate.py:22-78).  Accumulation is in
- * fp64.  Lines of at most 8192 elements are scanned in one pass by one thread block each; longer lines in three
- * streaming passes (tile aggregates, prefixes of the aggregates, seeded tile scans) or, with the environment
- * variable OVL_SCAN_MODE=lookback, in a single pass with decoupled look-back.
+ * fp64.  Lines of at most 8192 elements are scanned in one pass by one thread block each.  A single longer line
+ * with 16-byte aligned pointers is scanned by the ring scan: one cooperative launch (a block per SM, so nothing
+ * else should occupy the device's SMs meanwhile) that reads and writes every element once.  Several long lines,
+ * or unaligned pointers, take three streaming passes (tile aggregates, prefixes of the aggregates, seeded tile
+ * scans).  The environment variable OVL_SCAN_MODE=threepass forces the three passes, OVL_SCAN_MODE=lookback
+ * selects a single pass with decoupled look-back.
  * `carry` (device pointer to one double, or NULL) is combined into every element of a single line (lines
  * must be 1 when it is given).  `scratch` must hold ovl_scan_f32_scratch_bytes(lines, n) bytes. */
 uint64_t ovl_scan_f32_scratch_bytes(uint64_t lines, uint64_t n);
@@ -160,9 +163,9 @@ int ovl_reduce_f32(int op, const float* in, uint64_t n, double* out_total, void*
  * (OVL_SCAN_STATIC_SCRATCH_BYTES of device memory, held by every GPU that loads the library until the process
  * exits).  This entry point has no counterpart in the reference.
  *
- *  - Limit: ovl_scan_f32_scratch_bytes(lines, n) must not exceed OVL_SCAN_STATIC_SCRATCH_BYTES (32767 tiles:
- *    that many lines of up to 8192 elements, or about 134 million elements in longer lines, which are cut into
- *    tiles of 4096); larger requests return OVL_ERR_TOO_LARGE.
+ *  - Limit: ovl_scan_f32_scratch_bytes(lines, n) must not exceed OVL_SCAN_STATIC_SCRATCH_BYTES (32767 slots of
+ *    32 bytes: that many lines of up to 8192 elements, or about 134 million elements in longer lines, which are
+ *    budgeted one slot per 4096 elements); larger requests return OVL_ERR_TOO_LARGE.
  *  - The first call on each device looks up the array's device address (with that device current); make that
  *    first call before starting any stream capture.  No call allocates or frees memory.
  *  - All calls share the one array, and it keeps whatever the previous call left in it: each call clears the part

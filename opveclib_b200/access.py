@@ -125,6 +125,12 @@ def analyze(kernel):
                 src = info.forms.get(id(node.args[0]))
                 if src is not None and not node.dtype.is_float and _fits(src, node.dtype, info.ranges):
                     info.forms[id(node)] = src
+            elif k == 'variable':
+                # a variable nobody assigns to is a named constant (e.g. a loop bound taken from a shape)
+                src = info.forms.get(id(node.args[0]))
+                if (src is not None and id(node) not in assign_count and not node.dtype.is_float
+                        and _fits(src, node.dtype, info.ranges)):
+                    info.forms[id(node)] = src
             elif k == 'read':
                 tensor, index = node.args
                 iform = info.forms.get(id(index))

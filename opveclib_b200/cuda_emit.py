@@ -40,7 +40,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv19'
+TEMPLATE_VERSION = 'tv21'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -51,6 +51,11 @@ RING_THREADS = 832
 RING_SLOTS = 6
 RING_CTL_BYTES = 2048
 RING_MAX_GRID = 256
+# reduction loops: threads that share one worker's loop - a warp, or a whole block when there are too few workers
+# to fill the device with warps and the loop is long enough to feed a block
+REDUCE_BLOCK = 256
+REDUCE_BLOCK_TRIPS = 2048
+REDUCE_FEW_WORKERS = 2048
 
 
 def ctype(dtype):
@@ -370,7 +375,7 @@ def emit_cuda(kernel, name):
             '    for (' + widx_t + ' worker_index = (' + widx_t + ')blockIdx.x * ' + str(BLOCK_THREADS) +
             'u + threadIdx.x; worker_index < ' + str(W) + 'ull; worker_index += ovl_stride) {'] + em.lines + \
            ['    }', '}', '']
-    meta = {'gen': {'symbol': name + '_gen', 'block': BLOCK_THREADS, 'items': W}, 'vec': None, 'scan': None}
+    meta = {'gen': {'symbol': name + '_gen', 'block': BLOCK_THREADS, 'items': W}, 'vec': None, 'scan': None, 'red': None}
 
     # ---- vectorised kernel
     plan = plan_vectorisation(kernel, info)
@@ -426,6 +431,48 @@ def emit_cuda(kernel, name):
             em.lines + [ind + '}'] + [ind + l for l in post] + ['    }', '}', '']
         meta['vec'] = {'symbol': name + '_vec', 'block': BLOCK_THREADS, 'items': groups, 'lanes': L,
                        'aligned': sorted(aligned_tensors)}
+    # ---- cooperative reduction loop
+    red = patterns.match_reduce(kernel, info)
+    if red is not None:
+        src.insert(2, '#include "ovl_reduce.cuh"')
+        group = REDUCE_BLOCK if (red.n >= REDUCE_BLOCK_TRIPS and W < REDUCE_FEW_WORKERS) else 32
+        per_block = REDUCE_BLOCK // group
+        top = kernel.body.nodes
+        at = [i for i, x in enumerate(top) if x is red.loop][0]
+        em = BodyEmitter(kernel, 2, position_text=pos_text)
+        for node in top[:at]:
+            em.node(node)
+        acc_t = ctype(red.acc.dtype)
+        opname = 'ovl::OpAdd' if red.op == 'add' else 'ovl::OpMul'
+        ivar = em.name(red.loop.args[0])
+        em.put(acc_t + ' ovl_partial = ' + opname + '::identity<' + acc_t + '>();')
+        em.put('#pragma unroll 4')
+        em.put('for(' + ivar + ' = ovl_member; ' + ivar + ' < ' + str(red.n) + '; ' + ivar + ' += ' + str(group) + '){')
+        em.depth += 1
+        for node in red.loop.body.nodes:
+            if node is red.update:
+                em.put('ovl_partial = ' + opname + '::apply<' + acc_t + '>(ovl_partial, ' + em.name(red.term) + ');')
+            else:
+                em.node(node)
+        em.depth -= 1
+        em.put('}')
+        em.put(em.name(red.acc) + ' = ' + opname + '::apply<' + acc_t + '>(' + em.name(red.acc) + ', ovl::group_reduce<' +
+               acc_t + ', ' + opname + ', ' + str(group) + '>(ovl_partial, ovl_red_smem));')
+        em.put('if (ovl_member == 0) {')
+        em.depth += 1
+        for node in top[at + 1:]:
+            em.node(node)
+        em.depth -= 1
+        em.put('}')
+        src += ['extern "C" __global__ void __launch_bounds__(' + str(REDUCE_BLOCK) + ') ' + name + '_red(' + params + ') {',
+                '    __shared__ ' + acc_t + ' ovl_red_smem[' + str(REDUCE_BLOCK // 32) + '];',
+                '    const uint32_t ovl_member = threadIdx.x % ' + str(group) + 'u;',
+                '    const ' + widx_t + ' ovl_stride = (' + widx_t + ')gridDim.x * ' + str(per_block) + 'u;',
+                '    for (' + widx_t + ' worker_index = (' + widx_t + ')blockIdx.x * ' + str(per_block) + 'u + threadIdx.x / ' +
+                str(group) + 'u; worker_index < ' + str(W) + 'ull; worker_index += ovl_stride) {'] + em.lines + \
+               ['    }', '}', '']
+        meta['red'] = {'symbol': name + '_red', 'block': REDUCE_BLOCK, 'workers_per_block': per_block, 'items': W,
+                       'group': group, 'trips': red.n, 'op': red.op}
     # ---- cooperative scan
     spec = patterns.match_scan(kernel, info)
     if spec is not None and spec.n >= patterns.SCAN_MIN_AXIS:

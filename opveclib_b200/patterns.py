@@ -1,9 +1,12 @@
 """Recognition of loop idioms that have a cooperative kernel template.
 
-The only idiom so far is the inclusive scan: one worker per line walks the line serially, combining a running
-value with each element and storing it (``accumulate`` in opveclib/examples/test_accumulate.py:22-78, also the
-zero-seeded form of opveclib/test/test_operator_merge.py:56-68).  Recognition is deliberately narrow - anything
-that does not match exactly runs through the generic one-thread-per-worker kernel, which is always correct.
+Two idioms: the inclusive scan - one worker per line walks the line serially, combining a running value with
+each element and storing it (``accumulate`` in opveclib/examples/test_accumulate.py:22-78, also the zero-seeded
+form of opveclib/test/test_operator_merge.py:56-68) - and the per-worker reduction loop - a worker folds a
+computed term into one accumulator over a counted loop and uses the result afterwards (``dot`` in
+opveclib/test/test_dot_product.py:18-34, the matrix-vector product of documentation/programming.rst:320-344).
+Recognition is deliberately narrow - anything that does not match exactly runs through the generic
+one-thread-per-worker kernel, which is always correct.
 """
 from .access import analyze
 from .kernel import iter_nodes
@@ -144,3 +147,98 @@ def match_scan(kernel, info=None):
     if x.dtype.name == 'float16':
         return None
     return ScanSpec(op, lines, n, x.dtype)
+
+
+#: reduction loops shorter than this stay on the generic kernel
+REDUCE_MIN_TRIPS = 128
+
+
+class ReduceSpec(object):
+    """A worker's counted loop ``acc = acc (op) term(position, i)`` for i in [0, n): ``loop`` is the loop node,
+    ``acc`` the accumulator variable, ``update`` the assignment inside the loop, ``term`` the folded-in expression."""
+
+    def __init__(self, op, n, loop, acc, update, term):
+        self.op = op
+        self.n = n
+        self.loop = loop
+        self.acc = acc
+        self.update = update
+        self.term = term
+
+
+def _depends_on(node, targets, seen=None):
+    seen = seen if seen is not None else set()
+    if id(node) in seen:
+        return False
+    seen.add(id(node))
+    if id(node) in targets:
+        return True
+    return any(_depends_on(a, targets, seen) for a in getattr(node, 'args', ()) if a is not None)
+
+
+def match_reduce(kernel, info=None):
+    """ReduceSpec if every worker of the kernel is: statements, ONE counted loop (start 0, step 1, constant trip
+    count) whose only effect is folding a term into one accumulator with + or *, statements - else None.  The
+    term may be any expression of the position, the loop variable and tensor reads; nothing inside the loop may
+    write a tensor or observe the accumulator."""
+    top = kernel.body.nodes
+    all_nodes = list(iter_nodes(kernel.body))
+    if any(n.kind in ('if', 'local') for n in all_nodes):
+        return None
+    loops = [n for n in all_nodes if n.kind == 'for']
+    if len(loops) != 1 or not any(x is loops[0] for x in top):
+        return None
+    loop = loops[0]
+    info = info or analyze(kernel)
+    var = loop.args[0]
+    sym = info.loop_vars.get(id(var))
+    if sym is None:
+        return None
+    step = info.form_of(loop.args[3])
+    if step is None or not step.is_const() or step.const != 1:
+        return None
+    start, last = info.ranges[sym]
+    if start != 0:
+        return None
+    n = last + 1
+    if n < REDUCE_MIN_TRIPS:
+        return None
+    assigns = [a for a in all_nodes if a.kind == 'assign_var']
+    in_loop = list(iter_nodes(loop.body))
+    in_loop_ids = set(id(x) for x in in_loop)
+    if len(assigns) != 1 or id(assigns[0]) not in in_loop_ids:
+        return None
+    update = assigns[0]
+    acc, value = update.args
+    if acc.kind != 'variable' or not any(x is acc for x in top) or acc is var or acc.dtype.name == 'float16':
+        return None
+    if value.kind != 'binary' or value.attr['fn'] not in ('add', 'mul') or value.dtype != acc.dtype:
+        return None
+    a, b = value.args
+    if a is acc and b is not acc:
+        term = b
+    elif b is acc and a is not acc:
+        term = a
+    else:
+        return None
+    if _depends_on(term, {id(acc), id(value)}):
+        return None
+    # inside the loop only the update may mention the accumulator; nothing may write a tensor
+    for node in in_loop:
+        if node.kind == 'assign_tensor':
+            return None
+        if node is value or node is update:
+            continue
+        if any(x is acc for x in getattr(node, 'args', ()) if x is not None):
+            return None
+    # before the loop the accumulator is only declared; after it the loop variable is dead
+    at = [i for i, x in enumerate(top) if x is loop][0]
+    for node in top[:at]:
+        if node is not acc and any(x is acc for x in getattr(node, 'args', ()) if x is not None):
+            return None
+    if acc.args[0].kind != 'const':
+        return None
+    for node in top[at + 1:]:
+        if any(x is var for x in getattr(node, 'args', ()) if x is not None):
+            return None
+    return ReduceSpec(value.attr['fn'], n, loop, acc, update, term)

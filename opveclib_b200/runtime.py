@@ -26,7 +26,8 @@ def _torch():
 
 
 class KernelPlan(object):
-    """A compiled kernel with its launchable variants (generic / vectorised / scan), created on first use."""
+    """A compiled kernel with its launchable variants (generic / vectorised / scan / reduction), created on first
+    use."""
 
     def __init__(self, kernel):
         self.kernel = kernel
@@ -77,6 +78,11 @@ class KernelPlan(object):
                 for kind, idx in m['aligned']:
                     aligns[idx if kind == 'in' else n_in + idx] = 16
             return [self._make(device, m['symbol'], grid, block, all_in, all_out, aligns)]
+        if which == 'red':
+            m = meta['red']
+            blocks = (m['items'] + m['workers_per_block'] - 1) // m['workers_per_block']
+            grid = max(1, min(blocks, sms * (2048 // m['block'])))
+            return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
         m = meta['scan']
         block, name = m['block'], m['name']
         suffix = '' if which == 'scan' else 'u'
@@ -107,6 +113,8 @@ class KernelPlan(object):
             if meta['scan']['aligned_variant'] and all(p % al == 0 for p in in_ptrs + out_ptrs):
                 return 'scan'
             return 'scanu'
+        if meta.get('red'):
+            return 'red'
         if meta.get('vec'):
             ok = True
             for kind, idx in meta['vec']['aligned']:

@@ -110,7 +110,45 @@ def user_ops(ns):
         out[pos] = r
         return out
 
+    @ovl.operator()
+    def dot(input0, input1):
+        # per-row dot product with a float64 accumulator (opveclib/test/test_dot_product.py:18-34)
+        num_vectors = input0.shape[0]
+        dot_out = ovl.output(num_vectors, input0.dtype)
+        pos = ovl.position_in(num_vectors)[0]
+        accum = ovl.variable(0.0, ovl.float64)
+        num_elements = ovl.variable(input0.shape[1], ovl.uint32)
+        for i in ovl.arange(num_elements):
+            accum <<= accum + input0[pos, i] * input1[pos, i]
+        dot_out[pos] = accum
+        return dot_out
+
+    @ovl.operator()
+    def matvec(mat, vec):
+        # matrix-vector product, one worker per row (documentation/programming.rst:320-344)
+        assert mat.rank == 2 and vec.rank == 1 and mat.shape[1] == vec.shape[0] and mat.dtype == vec.dtype
+        rows, cols = mat.shape[0], mat.shape[1]
+        y = ovl.output(rows, mat.dtype)
+        row = ovl.position_in(rows)[0]
+        accum = ovl.variable(0, mat.dtype)
+        for col in ovl.arange(cols):
+            accum <<= accum + mat[row, col] * vec[col]
+        y[row] = accum
+        return y
+
+    @ovl.operator()
+    def rowprod_scaled(x, scale):
+        # product over the last axis of a rank-3 tensor, then scaled: statements after the loop use the result
+        out = ovl.output([x.shape[0], x.shape[1]], x.dtype)
+        pos = ovl.position_in([x.shape[0], x.shape[1]])
+        accum = ovl.variable(1, x.dtype)
+        for i in ovl.arange(x.shape[2]):
+            accum <<= x[pos[0], pos[1], i] * accum
+        out[pos] = accum * scale[pos[1]]
+        return out
+
     ops = types.SimpleNamespace(shift_cyclic=shift_cyclic, absolute=absolute, halfplus=halfplus, ew_exp=ew_exp,
+                                dot=dot, matvec=matvec, rowprod_scaled=rowprod_scaled,
                                 ew_tanh=ew_tanh, ew_add=ew_add, ew_mul=ew_mul, ew_addc=ew_addc, ew_mulc=ew_mulc,
                                 where_greater=where_greater)
     _cache[key] = ops
@@ -545,6 +583,49 @@ def case_merge_graph(ns):
     return [stack3(sum0, prod0, sum1), sum0], [in0]
 
 
+def case_dot_reference_test(ns):
+    # the reference's own test: RandomState(1), uniform(-1, 1), 100 vectors of 10 elements
+    rng = np.random.RandomState(1)
+    x = rng.uniform(-1, 1, (100, 10))
+    y = rng.uniform(-1, 1, (100, 10))
+    return [user_ops(ns).dot(x, y)], [x, y]
+
+
+def case_dot_f64_rows(ns):
+    rs = np.random.RandomState(41)
+    x = rs.uniform(-1, 1, (37, 1003))
+    y = rs.uniform(-1, 1, (37, 1003))
+    return [user_ops(ns).dot(x, y)], [x, y]
+
+
+def case_matvec_doc(ns):
+    # the documentation's example: [[0,1,2],[3,4,5],[6,7,8]] . [1,2,3] = [8, 26, 44]
+    m = _f32([[0, 1, 2], [3, 4, 5], [6, 7, 8]])
+    v = _f32([1, 2, 3])
+    return [user_ops(ns).matvec(m, v)], [m, v]
+
+
+def case_matvec_f32_long(ns):
+    rs = np.random.RandomState(42)
+    m = _f32(rs.uniform(-1, 1, (5, 9001)))
+    v = _f32(rs.uniform(-1, 1, 9001))
+    return [user_ops(ns).matvec(m, v)], [m, v]
+
+
+def case_matvec_i32(ns):
+    rs = np.random.RandomState(43)
+    m = rs.randint(-1000, 1000, (19, 300)).astype(np.int32)
+    v = rs.randint(-1000, 1000, 300).astype(np.int32)
+    return [user_ops(ns).matvec(m, v)], [m, v]
+
+
+def case_rowprod_scaled(ns):
+    rs = np.random.RandomState(44)
+    x = _f32(rs.uniform(0.99, 1.01, (3, 7, 500)))
+    s = _f32(rs.uniform(0.5, 2, 7))
+    return [user_ops(ns).rowprod_scaled(x, s)], [x, s]
+
+
 CASES = {name[len('case_'):]: fn for name, fn in sorted(globals().items()) if name.startswith('case_')}
 
 # cases whose outputs involve libm transcendentals (compared with a tolerance on the GPU)
@@ -552,3 +633,5 @@ TRANSCENDENTAL = {'c1_chain', 'c1_chain_odd', 'expm1_f64', 'log1p_f64', 'lstm_fw
                   'chain16', 'stdops_lstm', 'stdops_binary_f32', 'unary_f32', 'unary_f64', 'binary_f32', 'binary_f64'}
 # cases that contain a re-associated scan on the GPU (compared with a scaled absolute tolerance)
 SCANS = {'cumsum_rows_f32', 'cumprod_rows_f32', 'cumsum_rank1_f32', 'cumsum_f64'}
+# cases that contain a re-associated reduction loop on the GPU (floating point: compared with a tolerance)
+REDUCTIONS = {'dot_f64_rows', 'matvec_f32_long', 'rowprod_scaled'}

@@ -36,6 +36,9 @@ def _check(name, got, want, source):
             w64 = w.astype(np.float64)
             line_max = np.max(np.abs(w64), axis=-1, keepdims=True)
             assert_close(g, w, rtol=1e-5, atol=1e-5 * line_max * np.ones_like(w64), what=what)
+        elif name in cases.REDUCTIONS:
+            tight = 1e-5 if g.dtype == np.float32 else 1e-12
+            assert_close(g, w, rtol=tight, atol=tight * float(np.max(np.abs(w))), what=what)
         elif name in cases.TRANSCENDENTAL:
             tight = 1e-5 if g.dtype == np.float32 else 1e-12
             fin = np.isfinite(w)
@@ -78,3 +81,36 @@ def test_cuda_matches_oracle_at_both_opt_levels(name, opt_level):
     if len(outs) == 1:
         got, want = [got], [want]
     _check(name, got, want, 'oracle opt%d' % opt_level)
+
+
+@pytest.mark.parametrize('name,group', [('dot_f64_rows', 32), ('matvec_i32', 32), ('rowprod_scaled', 32),
+                                        ('matvec_f32_long', 256)])
+def test_reduction_loops_run_on_the_cooperative_kernel(name, group):
+    """Recognised reduction loops are launched as `_red` kernels (a warp or a block per worker), and agree with
+    the oracle's serial loop."""
+    from oracle import runner
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    outs, _ = cases.CASES[name](ns)
+    got = ns.ovl.evaluate(outs, target_language='b200')
+    prog, _ = runtime.compile_outputs(outs)
+    plan = prog.plans[0]
+    assert plan.meta['red'] is not None and plan.meta['red']['group'] == group
+    if not DRYRUN:
+        assert plan.last_variant == 'red'
+        _check(name, [got], [runner.evaluate(outs)], 'oracle')
+
+
+def test_large_matrix_vector_product():
+    """fp32 [4096, 4096] times a vector, against numpy in fp64: every row within rtol 1e-5 of its exact value
+    (scaled by the sum of the magnitudes of its terms)."""
+    if DRYRUN:
+        pytest.skip('needs a device')
+    ns = cases.impl()
+    rs = np.random.RandomState(7)
+    m = rs.uniform(-1, 1, (4096, 4096)).astype(np.float32)
+    v = rs.uniform(-1, 1, 4096).astype(np.float32)
+    got = ns.ovl.evaluate([cases.user_ops(ns).matvec(m, v)], target_language='b200')
+    exact = m.astype(np.float64) @ v.astype(np.float64)
+    scale = np.abs(m.astype(np.float64)) @ np.abs(v.astype(np.float64))
+    assert np.all(np.abs(got - exact) <= 1e-5 * scale)
