@@ -155,6 +155,14 @@ uint64_t ovl_reduce_f32_scratch_bytes(uint64_t n);
 int ovl_reduce_f32(int op, const float* in, uint64_t n, double* out_total, void* scratch, uint64_t scratch_bytes,
                    void* cuda_stream);
 
+/* Self-test of the bounded device-side waits (no counterpart in the reference).  Runs the ring scan (cumsum of one
+ * line of n > 8192 fp32 elements, 16-byte aligned pointers) with the first thread block keeping its tile aggregates
+ * to itself, so that every block's wait for them runs into its limit (about two seconds).  Nothing hangs or traps:
+ * the kernel ends, `out` is unspecified, and ovl_read_kernel_status(scratch, ...) then reports OVL_ERR_TIMEOUT;
+ * the context stays usable.  For hosts that want to check their error path. */
+int ovl_selftest_scan_timeout(const float* in, float* out, uint64_t n, void* scratch, uint64_t scratch_bytes,
+                              void* cuda_stream);
+
 /* Allocation-free scan ----------------------------------------------------------------------------------- */
 /* Same scan as ovl_scan_f32, for hosts that may not allocate device memory: for example a plugin running inside
  * an engine whose memory pool owns the whole GPU and forbids cudaMalloc from plugin code, or a latency-critical

@@ -336,8 +336,8 @@ __global__ void __launch_bounds__(ovl::kScanBlock) reduce_f32_kernel(const float
 template <class Op, bool HAS_CARRY>
 __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
                                                                             const double* __restrict__ carry, uint64_t n,
-                                                                            void* scratch) {
-    ovl::scan_ring<float, double, Op, 4, HAS_CARRY>(in, out, carry, n, scratch);
+                                                                            void* scratch, int withhold_block) {
+    ovl::scan_ring<float, double, Op, 4, HAS_CARRY>(in, out, carry, n, scratch, withhold_block);
 }
 
 // a line of at most kTile elements is one tile; longer lines are cut into tiles of kTile elements (three-pass
@@ -452,7 +452,8 @@ cudaError_t launch_scan_pass(const float* in, float* out, uint64_t lines, uint64
 
 // ring scan of one line: clear the aggregate words, then one cooperative launch with a block per SM
 template <class Op>
-int launch_ring(const float* in, float* out, uint64_t n, const double* carry, void* scratch, cudaStream_t stream) {
+int launch_ring(const float* in, float* out, uint64_t n, const double* carry, void* scratch, cudaStream_t stream,
+                int withhold_block = -1) {
     const uint64_t tiles = (n + kTile - 1) / kTile;
     uint64_t cap = (uint64_t)sm_count_cached();
     if (cap > (uint64_t)ovl::kRingMaxGrid) cap = ovl::kRingMaxGrid;
@@ -461,7 +462,7 @@ int launch_ring(const float* in, float* out, uint64_t n, const double* carry, vo
     const void* kernel = carry ? (const void*)scan_ring_f32_kernel<Op, true> : (const void*)scan_ring_f32_kernel<Op, false>;
     OVL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader) + tiles * 16, stream));
-    void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&n, (void*)&scratch};
+    void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&n, (void*)&scratch, (void*)&withhold_block};
     OVL_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(ovl::kRingThreads), args, smem, stream));
     return OVL_OK;
 }
@@ -529,6 +530,15 @@ extern "C" int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines,
     OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader), stream));   // status word
     if (op == 0) return run_scan<ovl::OpAdd>(in, out, lines, n, carry, scratch, aligned, stream);
     return run_scan<ovl::OpMul>(in, out, lines, n, carry, scratch, aligned, stream);
+}
+
+extern "C" int ovl_selftest_scan_timeout(const float* in, float* out, uint64_t n, void* scratch, uint64_t scratch_bytes,
+                                         void* cuda_stream) {
+    if (!out) return OVL_ERR_NULL;
+    int st = check_scan_args(0, in, 1, n, nullptr, scratch, scratch_bytes);
+    if (st != OVL_OK) return st;
+    if (n <= kTile || ((uintptr_t)in % 16) != 0 || ((uintptr_t)out % 16) != 0) return OVL_ERR_INVALID;
+    return launch_ring<ovl::OpAdd>(in, out, n, nullptr, scratch, (cudaStream_t)cuda_stream, /*withhold_block=*/0);
 }
 
 extern "C" int ovl_scan_f32_begin(int op, const float* in, uint64_t n, double* out_total, void* scratch,

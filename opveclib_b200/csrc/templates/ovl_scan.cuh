@@ -508,7 +508,7 @@ constexpr int kRingReduceWarps = 8;                // 8 warps reduce a tile (2 *
 constexpr int kRingThreads = (kRingScanWarps + kRingReduceWarps + 2) * 32;
 constexpr int kRingMaxGrid = 256;
 constexpr int kRingGather = 8;                     // aggregates fetched per lane and round by the prefix warp
-constexpr uint32_t kRingSpinLimit = 1u << 22;
+constexpr long long kRingWaitCycles = 1ll << 32;   // bound of every wait, in SM clock cycles (about two seconds)
 constexpr uint32_t kRingCtlBytes = 2048;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -560,7 +560,8 @@ struct RingCtl {
 // bounded wait on a shared-memory barrier; gives up at once when the block is aborting
 __device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < kRingSpinLimit; ++i) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < kRingWaitCycles) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
     }
@@ -599,7 +600,7 @@ struct RingCursor {
 
 template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY>
 __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry_in,
-                                          const uint64_t n, void* scratch) {
+                                          const uint64_t n, void* scratch, const int withhold_block = -1) {
     constexpr int VPT = kScanVpt;
     constexpr int SW = kRingScanWarps, RW = kRingReduceWarps;
     constexpr int CPR = SW / RW;                   // chunks (one per scan warp) handled by one reduce warp
@@ -760,7 +761,8 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                 Acc a = ctl->rpart[parity][0];
 #pragma unroll
                 for (int w = 1; w < RW; ++w) a = Op::apply(a, ctl->rpart[parity][w]);
-                ring_publish<Acc>(desc, tile, a);
+                // (self-test of the bounded waits: one block may be told to keep its aggregates to itself)
+                if ((int)b != withhold_block) ring_publish<Acc>(desc, tile, a);
             }
         }
     } else if (wid == SW + RW) {
@@ -790,9 +792,10 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
             }
             if (*abort_flag) {
                 // let the copies that may still be in flight land before the block gives up its shared memory
+                const long long t0 = clock64();
                 for (uint32_t k = (issued > (uint32_t)R) ? issued - R : 0; k < issued; ++k)
-                    for (uint32_t i = 0; i < kRingSpinLimit; ++i)
-                        if (mbar_try_wait(&ctl->full[k % R], (k / R) & 1u)) break;
+                    while (!mbar_try_wait(&ctl->full[k % R], (k / R) & 1u) && clock64() - t0 < kRingWaitCycles) {
+                    }
             }
         }
     } else {
@@ -819,10 +822,10 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                     const uint32_t idx = base_i + i * 32 + lane;
                     if (idx < gj) {
                         uint32_t spins = 0;
-                        while (((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) && spins < kRingSpinLimit && !*abort_flag) {
-                            if (spins > 4) __nanosleep(64);
+                        const long long t0 = clock64();
+                        while (((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) && clock64() - t0 < kRingWaitCycles && !*abort_flag) {
+                            if (++spins > 4) __nanosleep(64);
                             ring_peek(desc, first + idx, w0[i], w1[i]);
-                            ++spins;
                         }
                         if ((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) {
                             failed = true;

@@ -25,7 +25,7 @@ EXPORTS = ['ovl_version', 'ovl_status_string', 'ovl_last_cuda_error', 'ovl_devic
            'ovl_module_load_file', 'ovl_module_unload', 'ovl_kernel_create', 'ovl_kernel_destroy', 'ovl_launch',
            'ovl_profile', 'ovl_run_host', 'ovl_read_kernel_status', 'ovl_scan_f32_scratch_bytes', 'ovl_scan_f32',
            'ovl_reduce_f32_scratch_bytes', 'ovl_reduce_f32', 'ovl_scan_f32_static', 'ovl_scan_f32_static_status', 'ovl_scan_f32_begin',
-           'ovl_scan_f32_finish']
+           'ovl_scan_f32_finish', 'ovl_selftest_scan_timeout']
 
 _lib = None
 
@@ -75,6 +75,7 @@ def library():
     lib.ovl_reduce_f32.argtypes = [ctypes.c_int, vp, u64, vp, vp, u64, vp]
     lib.ovl_scan_f32_begin.argtypes = [ctypes.c_int, vp, u64, vp, vp, u64, vp]
     lib.ovl_scan_f32_finish.argtypes = [ctypes.c_int, vp, vp, u64, vp, vp, u64, vp]
+    lib.ovl_selftest_scan_timeout.argtypes = [vp, vp, u64, vp, u64, vp]
     lib.ovl_scan_f32_static.argtypes = [ctypes.c_int, vp, vp, u64, u64, vp, vp]
     lib.ovl_scan_f32_static_status.argtypes = [vp, ctypes.POINTER(i32)]
     _lib = lib

@@ -140,3 +140,30 @@ def test_generated_scan_of_a_long_line(dtype, fn):
         # integer scans wrap exactly like the serial loop of the reference's operator
         want = (np.cumsum(x, dtype=x.dtype) if fn == 'cumsum' else np.cumprod(x, dtype=x.dtype))
         np.testing.assert_array_equal(got, want)
+
+
+def test_a_wait_that_nothing_satisfies_ends_with_a_status_not_a_hang():
+    """The library's self-test entry point withholds one block's aggregates: every block's bounded wait expires
+    (about two seconds), the kernel returns, the status word says OVL_ERR_TIMEOUT - and the same context then
+    scans the same data correctly."""
+    import time
+    import torch
+    lib = launcher.library()
+    stream = torch.cuda.current_stream().cuda_stream
+    n = 6 * TILE
+    x = np.random.RandomState(8).normal(0, 1, n).astype(np.float32)
+    dx = torch.from_numpy(x).cuda()
+    out = torch.empty_like(dx)
+    nbytes = int(lib.ovl_scan_f32_scratch_bytes(1, n))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device='cuda')
+    t0 = time.time()
+    launcher.check(lib.ovl_selftest_scan_timeout(dx.data_ptr(), out.data_ptr(), n, scratch.data_ptr(), nbytes, stream),
+                   'self-test launch')
+    status = ctypes.c_int32(-1)
+    launcher.check(lib.ovl_read_kernel_status(scratch.data_ptr(), stream, ctypes.byref(status)), 'status')
+    elapsed = time.time() - t0
+    assert status.value == 8                      # OVL_ERR_TIMEOUT
+    assert 0.2 < elapsed < 30.0
+    assert lib.ovl_status_string(status.value).decode().startswith('bounded device-side wait')
+    got = _scan(dx, 0).cpu().numpy()
+    np.testing.assert_allclose(got, _exact(x, 0), rtol=1.3e-7, atol=0)
