@@ -13,6 +13,11 @@ Row locality is proven from the affine index forms (access.py): an access qualif
 workgroup's, or when it does not depend on ``position[0]`` at all and the tensor is small (replicated to every
 slab).  Anything else - loops, unproven indices, a tensor with another leading extent - and the graph is
 evaluated in one piece as usual.
+
+The first and the last slab travel alone (nothing to overlap with), so slabs should be small against the whole.
+A graph with few rows is cut finer when it is *element-local*: all tensors have one shape and every worker
+touches exactly the element at its own position.  Such a graph does not care how the elements are arranged, so
+the tensors are viewed as ``[rows * k, columns / k, ...]`` (same memory) and streamed in slabs of those rows.
 """
 import numpy as np
 
@@ -21,7 +26,8 @@ from .kernel import iter_nodes
 from .opgraph import GradientPlaceholder, Operator, OperatorOutput, _resolve_output
 
 MIN_BYTES = 32 << 20          # below this much leaf data one piece is as fast
-MAX_SLABS = 8
+MAX_SLABS = 8                 # row-local graphs
+FINE_SLABS = 32               # element-local graphs
 _plans = {}
 
 
@@ -55,6 +61,41 @@ def _row_local(kernel, rows):
     return not _position_value_escapes(kernel, info)
 
 
+def _element_local(kernel, shape):
+    """Every access of the kernel is the element at the worker's own position of a tensor of ``shape`` (the
+    workgroup's shape), and the position is used for nothing else."""
+    if list(kernel.workgroup_shape) != list(shape):
+        return False
+    if any(n.kind in ('for', 'local') for n in iter_nodes(kernel.body)):
+        return False
+    info = analyze(kernel)
+    strides = [1]
+    for d in range(len(shape) - 1, 0, -1):
+        strides.append(strides[-1] * shape[d])
+    strides.reverse()
+    want = {('p', d): st for d, st in enumerate(strides) if shape[d] > 1}
+    for acc in info.accesses:
+        f, t = acc.form, acc.tensor
+        if f is None or f.mod is not None or t.kind not in ('input', 'output') or list(t.shape) != list(shape):
+            return False
+        if f.const != 0 or {k: v for k, v in f.coefs.items()} != want:
+            return False
+    # no position entry may feed a value or a condition
+    tainted = set()
+    for n in iter_nodes(kernel.body):
+        if n.kind == 'read' and n.args[0].kind == 'position':
+            tainted.add(id(n))
+        elif n.kind in ('cast', 'unary', 'binary') and any(id(a) in tainted for a in n.args):
+            tainted.add(id(n))
+        elif n.kind == 'assign_var' and id(n.args[1]) in tainted:
+            return False
+        elif n.kind == 'assign_tensor' and id(n.args[2]) in tainted:
+            return False
+        elif n.kind == 'if' and any(c is not None and id(c) in tainted for c in n.conds):
+            return False
+    return True
+
+
 def _position_value_escapes(kernel, info):
     """True when position[0] feeds a stored value or a condition instead of only tensor indices."""
     tainted = set()
@@ -74,9 +115,10 @@ def _position_value_escapes(kernel, info):
     return False
 
 
-def _retrace(outputs, rows, slab_rows):
-    """The same operator graph traced for slabs of ``slab_rows`` rows.  Returns (slab outputs, leaf map: original
-    leaf id -> placeholder), or None when an operator cannot be traced again."""
+def _retrace(outputs, rows, slab_rows, trailing=None):
+    """The same operator graph traced for slabs of ``slab_rows`` rows (with the trailing extents ``trailing``
+    instead of the leaves' own when given).  Returns (slab outputs, leaf map: original leaf id -> placeholder),
+    or None when an operator cannot be traced again."""
     memo, leaves = {}, {}
 
     def leaf(x):
@@ -84,7 +126,8 @@ def _retrace(outputs, rows, slab_rows):
             shape = list(x.shape)
             if not shape or shape[0] != rows:
                 return None
-            leaves[id(x)] = (x, GradientPlaceholder([slab_rows] + shape[1:], x.dtype))
+            rest = shape[1:] if trailing is None else list(trailing)
+            leaves[id(x)] = (x, GradientPlaceholder([slab_rows] + rest, x.dtype))
         return leaves[id(x)][1]
 
     def build(op):
@@ -135,7 +178,9 @@ def plan(output_list, dag, prog, opt_level):
                 ok = False
             rows = t.shape[0] if t.shape else None
         total = sum(t.size * t.dtype.itemsize for t in dag.input_types)
-        if ok and rows and rows >= 2 and total >= MIN_BYTES:
+        if ok and rows and total >= MIN_BYTES:
+            result = _plan_element_local(output_list, dag, prog, opt_level, rows)
+        if result is None and ok and rows and rows >= 2 and total >= MIN_BYTES:
             slabs = next((c for c in range(min(MAX_SLABS, rows), 1, -1) if rows % c == 0), None)
             if slabs and all(_row_local(k, rows) for k in prog.dag.kernels):
                 out_ok = all(prog.plans[o].out_types[k].shape[0] == rows for o, k in prog.dag.outputs)
@@ -148,11 +193,44 @@ def plan(output_list, dag, prog, opt_level):
                         orig = next(o for o, p in leaves.values() if p is ph)
                         order.append(next(i for i, x in enumerate(dag.inputs) if x is orig))
                     result = {'slabs': slabs, 'rows': rows, 'slab_rows': rows // slabs, 'prog': slab_prog,
-                              'leaf_order': order}
+                              'leaf_order': order, 'view': None}
     except Exception:      # any doubt: evaluate in one piece
         result = None
     _plans[key] = result
     return result
+
+
+def _plan_element_local(output_list, dag, prog, opt_level, rows):
+    """Plan for a graph all of whose tensors share one shape and whose workers touch only their own element:
+    the tensors are viewed as [rows * k, columns / k, ...] and streamed in FINE_SLABS slabs or fewer."""
+    from . import runtime
+    shape = list(dag.input_types[0].shape)
+    if len(shape) < 2 or any(list(t.shape) != shape for t in dag.input_types):
+        return None
+    if any(list(prog.plans[o].out_types[k].shape) != shape for o, k in prog.dag.outputs):
+        return None
+    if not all(_element_local(k, shape) for k in prog.dag.kernels):
+        return None
+    cols = shape[1]
+    best = None
+    for k in range(1, FINE_SLABS + 1):
+        if cols % k == 0 and rows * k <= FINE_SLABS and (cols // k) % 4 == 0:
+            best = k
+    if best is None or rows * best < 2:
+        return None
+    view_rows, trailing = rows * best, [cols // best] + shape[2:]
+    # one slab per viewed row
+    traced = _retrace(output_list, rows, 1, trailing)
+    if traced is None:
+        return None
+    slab_outputs, leaves = traced
+    slab_prog, slab_dag = runtime.compile_outputs(slab_outputs, opt_level)
+    order = []
+    for ph in slab_dag.inputs:
+        orig = next(o for o, p in leaves.values() if p is ph)
+        order.append(next(i for i, x in enumerate(dag.inputs) if x is orig))
+    return {'slabs': view_rows, 'rows': view_rows, 'slab_rows': 1, 'prog': slab_prog, 'leaf_order': order,
+            'view': [view_rows] + trailing}
 
 
 def run(plan_, host_inputs, host_outputs, out_types, device):
@@ -164,6 +242,10 @@ def run(plan_, host_inputs, host_outputs, out_types, device):
     dev = 'cuda:%d' % device
     ins_h = [torch.from_numpy(host_inputs[i]) for i in plan_['leaf_order']]
     outs_h = [torch.from_numpy(a) for a in host_outputs]
+    if plan_.get('view') is not None:
+        # element-local graph: same memory, more and shorter rows
+        ins_h = [h.view(plan_['view']) for h in ins_h]
+        outs_h = [h.view(plan_['view']) for h in outs_h]
     with torch.cuda.device(device):
         main = torch.cuda.current_stream()
         s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()

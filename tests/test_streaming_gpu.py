@@ -26,12 +26,22 @@ def _both_ways(build, host_inputs):
     return plan, streamed, [w.cpu().numpy() for w in whole]
 
 
-def test_fused_chain_is_streamed_in_slabs_of_rows():
+def test_fused_chain_is_streamed_in_fine_slabs():
+    """An element-local graph over few long rows is viewed as more, shorter rows (same memory) so that the slabs
+    that travel alone at the start and at the end are small."""
     x = np.random.RandomState(0).uniform(-2, 2, (8, 1 << 21)).astype(np.float32)
     plan, streamed, whole = _both_ways(lambda ns, a: [cases.chain16(ns, a)], [x])
-    assert plan is not None and plan['slabs'] == 8 and plan['slab_rows'] == 1
+    assert plan is not None and plan['slabs'] == 32 and plan['slab_rows'] == 1 and plan['view'] == [32, 1 << 19]
     if streamed is not None:
         assert_exact(streamed[0], whole[0], 'streamed chain16')
+
+
+def test_odd_extents_fall_back_to_slabs_of_rows():
+    x = np.random.RandomState(2).uniform(-2, 2, (6, (1 << 21) + 4)).astype(np.float32)
+    plan, streamed, whole = _both_ways(lambda ns, a: [cases.chain16_light(ns, a)], [x])
+    assert plan is not None and plan['slabs'] * plan['slab_rows'] == plan['rows']
+    if streamed is not None:
+        assert_exact(streamed[0], whole[0], 'streamed light chain')
 
 
 def test_lstm_cell_is_streamed_over_the_batch():
