@@ -143,6 +143,14 @@ def build_graph(workload, rows_local=None, n_local=None):
     if workload == 'c3_grad':
         op = ns.lstm_grad(z(512, 4096), z(512, 1024), z(512, 1024), z(512, 1024), forget_bias=0.0)
         return [op[0], op[1]], 512 * 1024, 48
+    if workload.startswith('op_'):
+        # one operator of the 16-operator chain on its own (instruction cost per element), fp32 [1, 2^26]
+        u = cases.user_ops(ns)
+        x = z(1, 1 << 26)
+        single = {'op_tanh': lambda: u.ew_tanh(x), 'op_exp': lambda: u.ew_exp(x), 'op_log1p': lambda: ns.log1p(x),
+                  'op_expm1': lambda: ns.expm1(x), 'op_mulc': lambda: u.ew_mulc(x, c=0.5), 'op_add': lambda: u.ew_add(x, x),
+                  'op_where': lambda: u.where_greater(x, x)}
+        return [single[workload]()], 1 << 26, 8
     if workload == 'matvec':
         # reduction loop per row (documentation/programming.rst:320-344): the matrix is read once, 4 B per element
         return [cases.user_ops(ns).matvec(z(16384, 8192), z(8192))], 16384 * 8192, 4
@@ -156,12 +164,13 @@ def precompile():
         outs = build_graph('c4', rows_local=C4_ROWS // n)[0]
         prog, dag = runtime.compile_outputs(outs)
         streaming.plan(outs, dag, prog, 3)          # the slab-shaped kernels of the end-to-end leg
-    for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'light16', 'matvec'):
+    for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'light16', 'matvec', 'op_tanh', 'op_exp',
+              'op_log1p', 'op_expm1', 'op_mulc', 'op_add', 'op_where'):
         runtime.compile_outputs(build_graph(w)[0])
 
 
 def input_distribution(workload, index):
-    if workload in ('c4', 'light16'):
+    if workload in ('c4', 'light16') or workload.startswith('op_'):
         return ('uniform', -2.0, 2.0)
     if workload == 'c2_cumprod':
         return ('uniform', 0.99, 1.01)
@@ -273,12 +282,15 @@ def workload_config(workload, n):
         'c5': 'cumsum along the sharded axis, fp32 [2^31] normal(0,1), contiguous shards, fp64 carry exchange',
         'matvec': 'matrix-vector product as a per-row reduction loop, fp32 [16384, 8192] x [8192] normal(0,1)',
     }
+    if workload.startswith('op_'):
+        names[workload] = 'single operator ' + workload[3:] + ' of the 16-operator chain, fp32 [1, 2^26] uniform[-2,2]'
     if workload == 'c5' and C5_TOTAL != 1 << 31:
         names['c5'] = 'cumsum along the sharded axis, fp32 [%d] normal(0,1) (reduced case)' % C5_TOTAL
     if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
         names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
-            'l2': 'inputs larger than L2 (126 MB)' if workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec')
+            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec')
+                                                      or workload.startswith('op_'))
             else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
 
 
