@@ -121,6 +121,101 @@ class ShardedScan(object):
             raise launcher.OvlError(status.value, 'sharded scan')
 
 
+class HostScan(object):
+    """Inclusive cumsum / cumprod of a rank-1 fp32 array that lives in HOST memory, on one GPU.
+
+    The line is cut into chunks that travel through the device one after the other: while chunk i is scanned,
+    chunk i+1 is on its way in and chunk i-1 on its way out, so both directions of the host link are busy at
+    once and the device holds only a few chunks.  A chunk is scanned with the carry of everything before it
+    (``ovl_scan_f32`` with a device-side fp64 carry); the carry advances by the chunk's fp64 total
+    (``ovl_reduce_f32``), all on the device, so the host never waits inside the loop.  Results are those of the
+    one-piece scan: fp64 accumulation, rounded once.  Pinned host arrays make the copies asynchronous."""
+
+    def __init__(self, chunk_len=1 << 26, op='add', device=None):
+        import torch
+        self.torch = torch
+        self.op = op
+        self.code = _op_code(op)
+        self.chunk_len = int(chunk_len)
+        self.device = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+        self.lib = launcher.library()
+        self.scan_bytes = int(self.lib.ovl_scan_f32_scratch_bytes(1, self.chunk_len))
+        self.red_bytes = int(self.lib.ovl_reduce_f32_scratch_bytes(self.chunk_len))
+        dev = self.device
+        self.d_in = [torch.empty(self.chunk_len, dtype=torch.float32, device=dev) for _ in range(2)]
+        self.d_out = [torch.empty(self.chunk_len, dtype=torch.float32, device=dev) for _ in range(2)]
+        self.scan_scratch = torch.empty(self.scan_bytes, dtype=torch.uint8, device=dev)
+        self.red_scratch = torch.empty(self.red_bytes, dtype=torch.uint8, device=dev)
+        self.total = torch.zeros(1, dtype=torch.float64, device=dev)
+        # the scan's status word (first four bytes of its scratch) and the worst status seen over the chunks
+        self.status_word = self.scan_scratch[:4].view(torch.int32)
+        self.status_seen = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.carries = None
+        self.launches = 0
+
+    def __call__(self, host_in, host_out):
+        """``host_in`` / ``host_out``: rank-1 float32 torch CPU tensors of equal length (pinned for speed)."""
+        torch = self.torch
+        n = host_in.numel()
+        if host_in.dtype != torch.float32 or host_out.dtype != torch.float32 or host_in.dim() != 1 or \
+                host_out.numel() != n or not host_in.is_contiguous() or not host_out.is_contiguous():
+            raise ValueError('expected contiguous rank-1 float32 host tensors of equal length')
+        chunks = (n + self.chunk_len - 1) // self.chunk_len
+        identity = 0.0 if self.op == 'add' else 1.0
+        with torch.cuda.device(self.device):
+            main = torch.cuda.current_stream()
+            s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+            for st in (s_in, s_run, s_out):
+                st.wait_stream(main)
+            # carry in front of every chunk, advanced on the device
+            with torch.cuda.stream(s_run):
+                self.status_seen.zero_()
+                carries = torch.full((chunks + 1,), identity, dtype=torch.float64, device=self.device)
+            loaded, computed, stored = [None, None], [None, None], [None, None]
+            for i in range(chunks):
+                b = i % 2
+                lo = i * self.chunk_len
+                m = min(self.chunk_len, n - lo)
+                with torch.cuda.stream(s_in):
+                    if computed[b] is not None:
+                        s_in.wait_event(computed[b])
+                    self.d_in[b][:m].copy_(host_in[lo:lo + m], non_blocking=True)
+                    loaded[b] = torch.cuda.Event()
+                    loaded[b].record(s_in)
+                with torch.cuda.stream(s_run):
+                    s_run.wait_event(loaded[b])
+                    if stored[b] is not None:
+                        s_run.wait_event(stored[b])
+                    sp = s_run.cuda_stream
+                    launcher.check(self.lib.ovl_reduce_f32(self.code, self.d_in[b].data_ptr(), m, self.total.data_ptr(),
+                                                           self.red_scratch.data_ptr(), self.red_bytes, sp), 'chunk total')
+                    if self.op == 'add':
+                        torch.add(carries[i:i + 1], self.total, out=carries[i + 1:i + 2])
+                    else:
+                        torch.mul(carries[i:i + 1], self.total, out=carries[i + 1:i + 2])
+                    launcher.check(self.lib.ovl_scan_f32(self.code, self.d_in[b].data_ptr(), self.d_out[b].data_ptr(), 1, m,
+                                                         carries[i:].data_ptr(), self.scan_scratch.data_ptr(),
+                                                         self.scan_bytes, sp), 'chunk scan')
+                    torch.maximum(self.status_seen, self.status_word, out=self.status_seen)
+                    self.launches += 2
+                    computed[b] = torch.cuda.Event()
+                    computed[b].record(s_run)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(computed[b])
+                    host_out[lo:lo + m].copy_(self.d_out[b][:m], non_blocking=True)
+                    stored[b] = torch.cuda.Event()
+                    stored[b].record(s_out)
+            for st in (s_in, s_run, s_out):
+                main.wait_stream(st)
+            main.synchronize()
+            self.carries = carries
+            status = int(self.status_seen.item())
+            self.status_seen.zero_()
+            if status != 0:
+                raise launcher.OvlError(status, 'host scan')
+        return host_out
+
+
 def sharded_scan_host(shards, op='add'):
     """Host-side statement of the three steps over a list of numpy shards (rank order); returns the list of
     per-rank results.  Used by the CPU tests of the carry logic; the arithmetic mirrors the device path:

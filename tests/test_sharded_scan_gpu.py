@@ -182,3 +182,21 @@ def test_two_gpus_exchange_carries_over_nccl(op):
     x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.999, 1.001, n)).astype(np.float32)
     np.testing.assert_allclose(np.concatenate([parts[r] for r in range(world)]), _reference(x, op), rtol=1.3e-7,
                                atol=0)
+
+
+@pytest.mark.parametrize('op', ['add', 'mul'])
+def test_host_resident_line_is_scanned_chunk_by_chunk(op):
+    """`parallel.HostScan`: chunks of the line travel through the device while the previous one is scanned; the
+    carry between chunks stays on the device in fp64, so the result is the exact scan of the whole line."""
+    import torch
+    n = 3 * (1 << 20) + 12345
+    rs = np.random.RandomState(21)
+    x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.99999, 1.00001, n)).astype(np.float32)
+    host_in = torch.from_numpy(x).pin_memory()
+    host_out = torch.empty(n, dtype=torch.float32).pin_memory()
+    scan = parallel.HostScan(chunk_len=1 << 20, op=op)
+    scan(host_in, host_out)
+    np.testing.assert_allclose(host_out.numpy(), _reference(x, op), rtol=1.3e-7, atol=0)
+    # a second call reuses the buffers
+    scan(host_in, host_out)
+    np.testing.assert_allclose(host_out.numpy(), _reference(x, op), rtol=1.3e-7, atol=0)
