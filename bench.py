@@ -412,6 +412,18 @@ def main():
             stop.synchronize()
             elapsed_ms += start.elapsed_time(stop)
         barrier()
+    steady = None
+    if flush is not None:
+        # launch-bound sizes: also the steady state of back-to-back launches (inputs stay in L2 - reported apart,
+        # never as the headline)
+        reps = max(50, args.steps)
+        start.record()
+        for _ in range(reps):
+            step()
+        stop.record()
+        stop.synchronize()
+        steady = {'ms_per_step': start.elapsed_time(stop) / reps, 'steps': reps,
+                  'note': 'back-to-back launches without the L2 flush: inputs are L2-resident'}
     clocks = sampler.stop() if rank == 0 else None
     finish()
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
@@ -493,6 +505,8 @@ def main():
                          'traffic': profiled_traffic(workload, elements_local)},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': kernels_per_step * args.steps,
         }
+        if steady is not None:
+            line['steady_state'] = steady
         if world == 1 and not args.no_cpu:
             try:
                 line['cpu_baseline'], _ = cpu_reference_run(workload, 3)

@@ -3,3 +3,4 @@ from .accumulate import accumulate, cumsum, cumprod
 from .expm1 import expm1, expm1_grad
 from .log1p import log1p, log1p_grad
 from .lstm import lstm, lstm_grad
+from .conv1d import conv_1d

@@ -47,7 +47,7 @@ def build_harness(out_path):
 def load(cache_home):
     """Import the reference with its cache directory under ``cache_home``.  Returns a namespace with
     ``ovl`` (the package), ``opmod`` (the ``opveclib.operator`` module), ``stdops``, ``cumsum``, ``cumprod``,
-    ``expm1``, ``log1p``, ``lstm``, ``lstm_grad``."""
+    ``expm1``, ``log1p``, ``conv_1d``, ``lstm``, ``lstm_grad``."""
     if not available():
         raise RuntimeError('reference tree not found at ' + REFERENCE_ROOT)
     os.environ['PROTOCOL_BUFFERS_PYTHON_IMPLEMENTATION'] = 'python'
@@ -110,6 +110,14 @@ def load(cache_home):
     from opveclib.examples.test_expm1 import expm1
     from opveclib.examples.test_log1p import log1p
     ns.cumsum, ns.cumprod, ns.accumulate, ns.expm1, ns.log1p = cumsum, cumprod, accumulate, expm1, log1p
+    # examples/conv1D.py runs a TensorFlow comparison at import time; take the operator definition only (the text
+    # up to the first helper that follows it)
+    with open(os.path.join(REFERENCE_ROOT, 'opveclib', 'examples', 'conv1D.py')) as f:
+        text = f.read()
+    text = text[:text.index('\ndef reference(')]
+    scope = {'__name__': 'ref_conv1d'}
+    exec(compile(text, 'ref_conv1d.py', 'exec'), scope)
+    ns.conv_1d = scope['conv_1d']
 
     # lstm/lstm.py uses python-2 integer division at lines 35 and 66; run its text with '//' instead
     with open(os.path.join(REFERENCE_ROOT, 'lstm', 'lstm.py')) as f:

@@ -17,7 +17,7 @@ def impl():
     from opveclib_b200 import examples, stdops
     return types.SimpleNamespace(ovl=ovl, stdops=stdops, cumsum=examples.cumsum, cumprod=examples.cumprod,
                                  accumulate=examples.accumulate, expm1=examples.expm1, log1p=examples.log1p,
-                                 lstm=examples.lstm, lstm_grad=examples.lstm_grad)
+                                 lstm=examples.lstm, lstm_grad=examples.lstm_grad, conv_1d=examples.conv_1d)
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -624,6 +624,27 @@ def case_rowprod_scaled(ns):
     x = _f32(rs.uniform(0.99, 1.01, (3, 7, 500)))
     s = _f32(rs.uniform(0.5, 2, 7))
     return [user_ops(ns).rowprod_scaled(x, s)], [x, s]
+
+
+def case_conv1d_same_nce(ns):
+    rs = np.random.RandomState(51)
+    x = _f32(rs.uniform(-1, 1, (2, 3, 37)))
+    v = _f32(rs.uniform(-1, 1, (4, 3, 5)))
+    return [ns.conv_1d(x, v, mode='same', kernel_orientation='as-is', data_format='NCE')], [x, v]
+
+
+def case_conv1d_full_flipped_nec(ns):
+    rs = np.random.RandomState(52)
+    x = rs.uniform(-1, 1, (2, 29, 3))
+    v = rs.uniform(-1, 1, (2, 4, 3))
+    return [ns.conv_1d(x, v, mode='full', kernel_orientation='flipped', data_format='NEC')], [x, v]
+
+
+def case_conv1d_valid_nce(ns):
+    rs = np.random.RandomState(53)
+    x = _f32(rs.uniform(-1, 1, (1, 2, 64)))
+    v = _f32(rs.uniform(-1, 1, (3, 2, 7)))
+    return [ns.conv_1d(x, v, mode='valid', kernel_orientation='as-is', data_format='NCE')], [x, v]
 
 
 CASES = {name[len('case_'):]: fn for name, fn in sorted(globals().items()) if name.startswith('case_')}
