@@ -18,6 +18,6 @@ from .expr import arange, if_, elif_, else_
 # operators
 from .opgraph import operator, gradient
 from .runtime import evaluate, profile
-from .torch_bridge import as_torch
+from .torch_bridge import as_torch, as_tensorflow
 # local runtime environment
 from .local import version, logger, cuda_enabled, cache_directory, clear_op_cache

@@ -84,3 +84,11 @@ def as_torch(tensor_list, opt_level=3):
     results = _OvlFunction.apply(*leaves)
     results = list(results)
     return results[0] if single or len(results) == 1 else results
+
+
+def as_tensorflow(tensor_list, opt_level=3):
+    """The reference's TensorFlow bridge (opveclib/operator.py:2338-2354) has no counterpart here: this backend
+    hands results to PyTorch.  Kept under its old name so that code written for the reference fails with a
+    pointer to the replacement instead of an AttributeError."""
+    raise NotImplementedError('as_tensorflow is not available in the B200 backend: use as_torch(outputs), which '
+                              'returns differentiable torch CUDA tensors')

@@ -296,3 +296,25 @@ def test_kernel_text_is_structural():
     assert k1.text() == k2.text() and k1.digest() == k2.digest()
     assert k1.text() != k3.text()
     assert len(list(iter_nodes(k1.body))) > 10
+
+
+def test_every_name_the_reference_exports_is_present():
+    """The names of opveclib/__init__.py:11-48; ``as_tensorflow`` exists only to point at ``as_torch``."""
+    import opveclib_b200 as ovl
+    names = '''DType float32 float64 int8 int16 int32 int64 uint8 uint16 uint32 uint64 TensorType Scalar Variable
+        InputTensor OutputTensor PositionTensor LocalTensor position_in output output_like zeros ones variable cast
+        min_value max_value epsilon arccos arcsin arctan cos cosh sin sinh tan tanh exp log log10 sqrt ceil absolute
+        floor logical_not isinf isfinite isnan minimum maximum power arctan2 logical_and logical_or arange if_ elif_
+        else_ operator gradient evaluate profile as_tensorflow version logger cuda_enabled cache_directory
+        clear_op_cache'''.split()
+    missing = [n for n in names if not hasattr(ovl, n)]
+    assert not missing, missing
+    import pytest
+    with pytest.raises(NotImplementedError, match='as_torch'):
+        ovl.as_tensorflow([])
+    from opveclib_b200 import examples, stdops
+    for n in 'accumulate cumsum cumprod expm1 expm1_grad log1p log1p_grad'.split():
+        assert hasattr(examples, n), n
+    for n in '''neg tanh sin cos tan sigmoid split concat add sub mul div mod equal not_equal less less_equal greater
+             greater_equal'''.split():
+        assert hasattr(stdops, n), n
