@@ -243,6 +243,25 @@ class Program(object):
                 plan.check_status(stream_ptr, device)
 
 
+_host_scans = {}
+_HOST_SCAN_CHUNK = 1 << 26
+_HOST_SCAN_MIN = 1 << 25
+
+
+def _host_scan_plan(prog):
+    """('add' | 'mul', n) when the program is one scan of a single long fp32 line (the chunk-pipelined host path
+    handles exactly that), else None."""
+    if len(prog.plans) != 1 or len(prog.dag.outputs) != 1:
+        return None
+    plan = prog.plans[0]
+    m = plan.meta.get('scan')
+    if not m or m['lines'] != 1 or m['n'] < _HOST_SCAN_MIN:
+        return None
+    if plan.in_types[0].dtype.name != 'float32' or len(plan.in_types) != 1:
+        return None
+    return m['op'], m['n']
+
+
 def compile_outputs(output_list, opt_level=3):
     """Build, fuse and compile the operator graph behind ``output_list``; cached by graph structure."""
     if not isinstance(output_list, (list, tuple)):
@@ -296,6 +315,23 @@ def profile(output_list, target_language='b200', profiling_iterations=1, opt_lev
             leaves.append(torch.from_numpy(np.ascontiguousarray(x)))
     dev = 'cuda:%d' % device
     if not any(_is_torch(x) for x in dag.inputs) and profiling_iterations == 1:
+        # a host-resident long fp32 line that is scanned: chunks stream through the device, both link directions busy
+        hs = _host_scan_plan(prog)
+        if hs is not None:
+            op, n = hs
+            shape = tuple(prog.plans[0].out_types[0].shape)
+            dst = out[0] if out is not None else np.empty(shape, dtype=np.float32)
+            if dst.shape != shape or dst.dtype != np.float32 or not dst.flags['C_CONTIGUOUS']:
+                raise ValueError('out must hold one C-contiguous array of the right shape and dtype per output')
+            key = (op, device)
+            if key not in _host_scans:
+                from . import parallel
+                with torch.cuda.device(device):
+                    _host_scans[key] = parallel.HostScan(_HOST_SCAN_CHUNK, op)
+            src = np.ascontiguousarray(dag.inputs[0]).reshape(-1)
+            with torch.cuda.device(device):
+                _host_scans[key](torch.from_numpy(src), torch.from_numpy(dst.reshape(-1)))
+            return [dst], {prog.plans[0].name: np.array([np.nan])}
         # host-resident inputs: stream slabs of rows through the device when the graph allows it
         from . import streaming
         splan = streaming.plan(output_list if isinstance(output_list, (list, tuple)) else [output_list], dag, prog,

@@ -162,3 +162,23 @@ def test_config5_full_size_scan_properties_and_sharding():
             # flip a rounding in rare elements
             ref = y[r * m:(r + 1) * m].double()
             assert bool(((out.double() - ref).abs() <= 1.2e-7 * ref.abs() + 1e-6).all())
+
+
+def test_host_resident_long_line_through_evaluate():
+    """`ovl.evaluate(cumsum(numpy array))` of a long line streams chunks through the device
+    (`parallel.HostScan`); the result is the exact scan, as from device-resident data."""
+    import torch
+    ns = cases.impl()
+    n = (1 << 26) + (1 << 25) + 777            # one whole chunk and a ragged second one
+    x = np.random.RandomState(6).normal(0, 1, n).astype(np.float32)
+    got = ns.ovl.evaluate(ns.cumsum(x, axis=0))
+    assert isinstance(got, np.ndarray) and got.shape == (n,)
+    dev = ns.ovl.evaluate(ns.cumsum(torch.from_numpy(x).cuda(), axis=0)).cpu().numpy()
+    # both are fp64 accumulations rounded once; chunking changes the order of a few fp64 additions, which can move a
+    # value that sits on a rounding boundary by one unit in the last place
+    np.testing.assert_allclose(got, dev, rtol=1.3e-7, atol=0)
+    assert (got != dev).mean() < 1e-6
+    # numpy's serial fp64 sum carries its own rounding (about 1e-12 here), enough to move a value next to a zero
+    # crossing by one unit in the last place: two units allowed
+    want = np.cumsum(x.astype(np.float64)).astype(np.float32)
+    np.testing.assert_allclose(got, want, rtol=2.5e-7, atol=0)
