@@ -30,10 +30,97 @@ def _backward_program(dag, opt_level):
     return hit
 
 
+# ---------------------------------------------------------------------------------------------------------
+# The custom operators.  A compiled operator graph is registered under an integer handle; two operators of the
+# `ovl_b200` namespace run a graph forward and run its backward graph.  Both are ordinary dispatcher operators
+# (`torch.ops.ovl_b200.run`, `torch.ops.ovl_b200.run_backward`) with fake-tensor implementations, so graphs that
+# contain them can be traced and exported; autograd is attached with `register_autograd`.
+_registry = []          # handle -> (forward Program, op DAG, opt_level, output TensorTypes)
+_handles = {}
+_ops = None
+
+
+def _register(prog, dag, opt_level):
+    key = (dag.text(), opt_level >= 3)
+    if key not in _handles:
+        out_types = [prog.plans[o].out_types[k] for o, k in prog.dag.outputs]
+        _registry.append((prog, dag, opt_level, out_types))
+        _handles[key] = len(_registry) - 1
+    return _handles[key]
+
+
+def _define_ops():
+    """Create the two custom operators on first use (torch is imported lazily by this package)."""
+    global _ops
+    if _ops is not None:
+        return _ops
+    import torch
+    from typing import List
+
+    def _device_of(tensors):
+        return tensors[0].device.index if tensors else torch.cuda.current_device()
+
+    @torch.library.custom_op('ovl_b200::run', mutates_args=())
+    def run(inputs: List[torch.Tensor], handle: int) -> List[torch.Tensor]:
+        prog = _registry[handle][0]
+        device = _device_of(inputs)
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream().cuda_stream
+            outs, _ = prog.run([x.contiguous() for x in inputs], device, stream, None)
+        return list(outs)
+
+    @run.register_fake
+    def _(inputs, handle):
+        out_types = _registry[handle][3]
+        dev = inputs[0].device if inputs else 'cuda'
+        return [torch.empty(tuple(t.shape), dtype=t.dtype.as_torch(), device=dev) for t in out_types]
+
+    @torch.library.custom_op('ovl_b200::run_backward', mutates_args=())
+    def run_backward(inputs: List[torch.Tensor], grads: List[torch.Tensor], handle: int) -> List[torch.Tensor]:
+        _, dag, opt_level, _ = _registry[handle]
+        bprog, has_grad = _backward_program(dag, opt_level)
+        device = _device_of(inputs)
+        with torch.cuda.device(device):
+            stream = torch.cuda.current_stream().cuda_stream
+            outs, _ = bprog.run([x.contiguous() for x in list(inputs) + list(grads)], device, stream, None)
+        return list(outs)
+
+    @run_backward.register_fake
+    def _(inputs, grads, handle):
+        _, dag, opt_level, _ = _registry[handle]
+        _, has_grad = _backward_program(dag, opt_level)
+        return [torch.empty_like(x) for x, h in zip(inputs, has_grad) if h]
+
+    def setup_context(ctx, inputs, output):
+        tensors, handle = inputs
+        ctx.handle = handle
+        ctx.save_for_backward(*tensors)
+
+    def backward(ctx, grad_outputs):
+        handle = ctx.handle
+        _, dag, opt_level, out_types = _registry[handle]
+        bprog, has_grad = _backward_program(dag, opt_level)
+        saved = list(ctx.saved_tensors)
+        if bprog is None:
+            return [None for _ in has_grad], None
+        grads_in = []
+        for g, t, x in zip(grad_outputs, out_types, [None] * len(out_types)):
+            if g is None:
+                g = torch.zeros(tuple(t.shape), dtype=t.dtype.as_torch(), device=saved[0].device)
+            grads_in.append(g)
+        outs = iter(torch.ops.ovl_b200.run_backward(saved, grads_in, handle))
+        return [next(outs) if h else None for h in has_grad], None
+
+    run.register_autograd(backward, setup_context=setup_context)
+    _ops = (run, run_backward)
+    return _ops
+
+
 def as_torch(tensor_list, opt_level=3):
     """Evaluate operator outputs on the GPU as torch tensors, differentiable with respect to the torch leaf
     inputs that require grad.  A single requested output comes back bare, several as a list
-    (as ``as_tensorflow`` does, opveclib/operator.py:2409-2412)."""
+    (as ``as_tensorflow`` does, opveclib/operator.py:2409-2412).  The graph runs as the custom operator
+    ``torch.ops.ovl_b200.run``; its backward as ``torch.ops.ovl_b200.run_backward``."""
     import torch
     single = not isinstance(tensor_list, (list, tuple))
     outputs = [tensor_list] if single else list(tensor_list)
@@ -51,38 +138,9 @@ def as_torch(tensor_list, opt_level=3):
         else:
             leaves.append(torch.from_numpy(np.ascontiguousarray(x)))
     leaves = [x if x.is_cuda else x.to('cuda:%d' % device) for x in leaves]
-    out_types = [prog.plans[o].out_types[k] for o, k in prog.dag.outputs]
-
-    class _OvlFunction(torch.autograd.Function):
-        @staticmethod
-        def forward(ctx, *inputs):
-            with torch.cuda.device(device):
-                stream = torch.cuda.current_stream().cuda_stream
-                staged = [x.detach().contiguous() for x in inputs]
-                outs, _ = prog.run(staged, device, stream, None)
-            ctx.save_for_backward(*staged)
-            ctx.mark_non_differentiable(*[o for o, t in zip(outs, out_types) if not t.dtype.is_float])
-            return tuple(outs)
-
-        @staticmethod
-        def backward(ctx, *grad_outputs):
-            bprog, has_grad = _backward_program(dag, opt_level)
-            if bprog is None:
-                return tuple(None for _ in has_grad)
-            saved = list(ctx.saved_tensors)
-            grads_in = []
-            for g, t in zip(grad_outputs, out_types):
-                if g is None:
-                    g = torch.zeros(t.shape, dtype=t.dtype.as_torch(), device='cuda:%d' % device)
-                grads_in.append(g.contiguous())
-            with torch.cuda.device(device):
-                stream = torch.cuda.current_stream().cuda_stream
-                outs, _ = bprog.run(saved + grads_in, device, stream, None)
-            it = iter(outs)
-            return tuple(next(it) if h else None for h in has_grad)
-
-    results = _OvlFunction.apply(*leaves)
-    results = list(results)
+    _define_ops()
+    handle = _register(prog, dag, opt_level)
+    results = list(torch.ops.ovl_b200.run(leaves, handle))
     return results[0] if single or len(results) == 1 else results
 
 

@@ -90,3 +90,27 @@ def test_shared_input_contributions_are_summed_and_missing_gradients_block():
     bdag, has_grad = compose_backward(dag)
     flags = dict((id(leaf), h) for leaf, h in zip(dag.inputs, has_grad))
     assert flags[id(x)] is False
+
+
+def test_custom_operators_are_registered_with_fake_tensor_support():
+    """`as_torch` runs graphs as `torch.ops.ovl_b200.run` / `run_backward`; both can be traced without a device
+    (shapes and dtypes come from the compiled graph's signature)."""
+    import numpy as np
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    import cases
+    from opveclib_b200 import runtime, torch_bridge
+    ns = cases.impl()
+    g, c = np.zeros((6, 32), np.float32), np.zeros((6, 8), np.float32)
+    op = ns.lstm(g, c, forget_bias=0.0)
+    prog, dag = runtime.compile_outputs([op[0], op[1]])
+    torch_bridge._define_ops()
+    handle = torch_bridge._register(prog, dag, 3)
+    assert handle == torch_bridge._register(prog, dag, 3)
+    assert str(torch.ops.ovl_b200.run.default._schema).startswith('ovl_b200::run(Tensor[] inputs')
+    with FakeTensorMode():
+        a, b = torch.empty((6, 32), device='cuda'), torch.empty((6, 8), device='cuda')
+        outs = torch.ops.ovl_b200.run([a, b], handle)
+        assert [tuple(o.shape) for o in outs] == [(6, 8), (6, 8)] and outs[0].dtype == torch.float32
+        grads = torch.ops.ovl_b200.run_backward([a, b], list(outs), handle)
+        assert [tuple(x.shape) for x in grads] == [(6, 32), (6, 8)]
