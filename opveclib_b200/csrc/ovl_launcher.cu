@@ -333,11 +333,11 @@ __global__ void __launch_bounds__(ovl::kScanBlock) reduce_f32_kernel(const float
     ovl::reduce_all<float, double, Op, 4, ALIGNED>(in, n, out_total, scratch);
 }
 
-template <class Op, bool HAS_CARRY>
+template <class Op, bool HAS_CARRY, bool MULTI>
 __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
-                                                                            const double* __restrict__ carry, uint64_t n,
-                                                                            void* scratch, int withhold_block) {
-    ovl::scan_ring<float, double, Op, 4, HAS_CARRY>(in, out, carry, n, scratch, withhold_block);
+                                                                            const double* __restrict__ carry, uint64_t lines,
+                                                                            uint64_t n, void* scratch, int withhold_block) {
+    ovl::scan_ring<float, double, Op, 4, HAS_CARRY, MULTI>(in, out, carry, lines, n, scratch, withhold_block);
 }
 
 // a line of at most kTile elements is one tile; longer lines are cut into tiles of kTile elements (three-pass
@@ -450,19 +450,22 @@ cudaError_t launch_scan_pass(const float* in, float* out, uint64_t lines, uint64
     return launch_scan_mode<Op, false, false>(in, out, lines, n, carry, scratch, mode, stream);
 }
 
-// ring scan of one line: clear the aggregate words, then one cooperative launch with a block per SM
+// ring scan of long lines: clear the aggregate words, then one cooperative launch with a block per SM
 template <class Op>
-int launch_ring(const float* in, float* out, uint64_t n, const double* carry, void* scratch, cudaStream_t stream,
-                int withhold_block = -1) {
-    const uint64_t tiles = (n + kTile - 1) / kTile;
+int launch_ring(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
+                cudaStream_t stream, int withhold_block = -1) {
+    const uint64_t tiles = ((n + kTile - 1) / kTile) * lines;
     uint64_t cap = (uint64_t)sm_count_cached();
     if (cap > (uint64_t)ovl::kRingMaxGrid) cap = ovl::kRingMaxGrid;
     const uint32_t grid = (uint32_t)(tiles < cap ? tiles : cap);
     const size_t smem = (size_t)ovl::kRingSlots * kTile * sizeof(float) + ovl::kRingCtlBytes;
-    const void* kernel = carry ? (const void*)scan_ring_f32_kernel<Op, true> : (const void*)scan_ring_f32_kernel<Op, false>;
+    // (a carry is only accepted together with a single line)
+    const void* kernel = lines > 1 ? (const void*)scan_ring_f32_kernel<Op, false, true>
+                         : carry   ? (const void*)scan_ring_f32_kernel<Op, true, false>
+                                   : (const void*)scan_ring_f32_kernel<Op, false, false>;
     OVL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader) + tiles * 16, stream));
-    void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&n, (void*)&scratch, (void*)&withhold_block};
+    void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&lines, (void*)&n, (void*)&scratch, (void*)&withhold_block};
     OVL_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(ovl::kRingThreads), args, smem, stream));
     return OVL_OK;
 }
@@ -506,7 +509,7 @@ int run_scan(const float* in, float* out, uint64_t lines, uint64_t n, const doub
         cudaError_t e = launch_scan_pass<Op>(in, out, lines, n, carry, scratch, aligned, ovl::kScanOneTile, stream);
         return e == cudaSuccess ? OVL_OK : cuda_fail(e);
     }
-    if (lines == 1 && aligned && long_line_mode() == kModeRing) return launch_ring<Op>(in, out, n, carry, scratch, stream);
+    if (aligned && long_line_mode() == kModeRing) return launch_ring<Op>(in, out, lines, n, carry, scratch, stream);
     if (use_lookback()) {
         // the descriptors must start out empty
         OVL_CUDA(cudaMemsetAsync(scratch, 0, ovl_scan_f32_scratch_bytes(lines, n), stream));
@@ -538,7 +541,7 @@ extern "C" int ovl_selftest_scan_timeout(const float* in, float* out, uint64_t n
     int st = check_scan_args(0, in, 1, n, nullptr, scratch, scratch_bytes);
     if (st != OVL_OK) return st;
     if (n <= kTile || ((uintptr_t)in % 16) != 0 || ((uintptr_t)out % 16) != 0) return OVL_ERR_INVALID;
-    return launch_ring<ovl::OpAdd>(in, out, n, nullptr, scratch, (cudaStream_t)cuda_stream, /*withhold_block=*/0);
+    return launch_ring<ovl::OpAdd>(in, out, 1, n, nullptr, scratch, (cudaStream_t)cuda_stream, /*withhold_block=*/0);
 }
 
 extern "C" int ovl_scan_f32_begin(int op, const float* in, uint64_t n, double* out_total, void* scratch,

@@ -477,10 +477,10 @@ __device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uin
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Ring scan: ONE long line in a single launch; every element is read from memory once and written once
+// Ring scan: long lines in a single launch; every element is read from memory once and written once
 // (8 bytes per fp32 element) and no thread block ever waits for the block before it.
 //
-// One persistent block per SM.  Tile t belongs to block t % gridDim.x; the tiles b, b + G, b + 2G ... of block b
+// One persistent block per SM.  Tiles are numbered line by line; tile t belongs to block t % gridDim.x; the tiles b, b + G, b + 2G ... of block b
 // are its "waves" 0, 1, 2 ...  A tile travels through a ring of kRingSlots tile-sized slots in shared memory.
 // The block's warps have four roles, coupled only through shared-memory barriers (mbarrier):
 //   copy warp      one thread streams the block's tiles into free slots with bulk asynchronous copies
@@ -598,9 +598,36 @@ struct RingCursor {
     }
 };
 
-template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY>
+// Position of a role's current tile: tiles are numbered line by line (tiles_per_line per line, the last tile of a
+// line possibly ragged); a role visits tiles b, b + G, b + 2G ... and keeps (line, tile in line) without divisions.
+// With a single line (MULTI = false) the line stays 0 and nothing but an addition is left.
+template <bool MULTI>
+struct RingTile {
+    uint64_t line, q, tiles_per_line;
+    uint64_t dl, dq;
+    __device__ __forceinline__ RingTile(uint64_t tile, uint64_t tpl, uint32_t G)
+        : line(MULTI ? tile / tpl : 0), q(MULTI ? tile % tpl : tile), tiles_per_line(tpl), dl(MULTI ? G / tpl : 0),
+          dq(MULTI ? G % tpl : G) {}
+    __device__ __forceinline__ void advance() {
+        q += dq;
+        if (MULTI) {
+            line += dl;
+            if (q >= tiles_per_line) {
+                q -= tiles_per_line;
+                ++line;
+            }
+        }
+    }
+    __device__ __forceinline__ bool last_of_line() const { return q + 1 == tiles_per_line; }
+    __device__ __forceinline__ uint64_t first_element(uint64_t n, uint32_t tile_elems) const {
+        return (MULTI ? line * n : 0) + q * tile_elems;
+    }
+};
+
+template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY, bool MULTI>
 __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry_in,
-                                          const uint64_t n, void* scratch, const int withhold_block = -1) {
+                                          const uint64_t lines, const uint64_t n, void* scratch,
+                                          const int withhold_block = -1) {
     constexpr int VPT = kScanVpt;
     constexpr int SW = kRingScanWarps, RW = kRingReduceWarps;
     constexpr int CPR = SW / RW;                   // chunks (one per scan warp) handled by one reduce warp
@@ -617,10 +644,11 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
 
     ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
     uint64_t* desc = reinterpret_cast<uint64_t*>(hdr + 1);
-    const uint64_t total_tiles = (n + TILE - 1) / TILE;
+    const uint64_t tiles_per_line = (n + TILE - 1) / TILE;
+    const uint64_t total_tiles = tiles_per_line * (MULTI ? lines : 1);
     const uint32_t G = gridDim.x, b = blockIdx.x;
     const uint32_t my_tiles = (total_tiles > b) ? (uint32_t)((total_tiles - b + G - 1) / G) : 0u;
-    const uint32_t tail = (uint32_t)(n - (total_tiles - 1) * TILE);      // valid elements of the last tile
+    const uint32_t tail = (uint32_t)(n - (tiles_per_line - 1) * TILE);   // valid elements of a line's last tile
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 
     if (threadIdx.x == 0) {
@@ -642,13 +670,13 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         // warp `wid` scans chunk `wid` (32 * VPT vectors) of every tile of the block, on its own: the prefix in
         // front of the chunk is already in shared memory when the warp starts, so warps never wait for each other
         RingCursor cur;
-        uint64_t tile = b;
+        RingTile<MULTI> at(b, tiles_per_line, G);
         const uint32_t v0 = (uint32_t)wid * 32 * VPT + lane;            // this thread's vectors: v0 + 32 j
-        for (uint32_t k = 0; k < my_tiles; ++k, tile += G, cur.advance()) {
+        for (uint32_t k = 0; k < my_tiles; ++k, at.advance(), cur.advance()) {
             if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
             if (!ring_wait(&ctl->ready[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
             if (*abort_flag) break;
-            const bool whole = (tile != total_tiles - 1) || tail == TILE;
+            const bool whole = !at.last_of_line() || tail == TILE;
             const Vec<T, VEC>* sv = reinterpret_cast<const Vec<T, VEC>*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
             Acc av[VPT][VEC];                                           // the chunk's values, widened once
             if (whole) {
@@ -689,7 +717,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                 if (j + 1 < VPT) run = Op::apply(run, shfl_any(t, 31));
             }
             // sweep 2: running values, rounded to T on store
-            T* dst = out + tile * TILE;
+            T* dst = out + at.first_element(n, TILE);
 #pragma unroll
             for (int j = 0; j < VPT; ++j) {
                 const uint32_t off = (v0 + j * 32) * VEC;
@@ -718,9 +746,10 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         int parity = 0;
         const int rw = wid - SW;
         uint64_t tile = b;
-        for (uint32_t k = 0; k < my_tiles; ++k, tile += G, cur.advance(), parity ^= 1) {
+        RingTile<MULTI> at(b, tiles_per_line, G);
+        for (uint32_t k = 0; k < my_tiles; ++k, tile += G, at.advance(), cur.advance(), parity ^= 1) {
             if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
-            const bool whole = (tile != total_tiles - 1) || tail == TILE;
+            const bool whole = !at.last_of_line() || tail == TILE;
             const Vec<T, VEC>* sv = reinterpret_cast<const Vec<T, VEC>*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
             Acc part[CPR];
 #pragma unroll
@@ -770,16 +799,16 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         if (lane == 0) {
             RingCursor cur;
             uint32_t issued = 0;
-            uint64_t tile = b;
-            for (uint32_t k = 0; k < my_tiles; ++k, tile += G, cur.advance()) {
+            RingTile<MULTI> at(b, tiles_per_line, G);
+            for (uint32_t k = 0; k < my_tiles; ++k, at.advance(), cur.advance()) {
                 // second and later uses of a slot: wait until the scan of its previous tile has read it
                 if (k >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag)) {
                     ring_fail(hdr, abort_flag);
                     break;
                 }
-                const uint32_t valid = (tile == total_tiles - 1) ? tail : TILE;
+                const uint32_t valid = at.last_of_line() ? tail : TILE;
                 const uint32_t bulk = (uint32_t)(valid * sizeof(T)) & ~15u;
-                const T* src = in + tile * TILE;
+                const T* src = in + at.first_element(n, TILE);
                 T* slot_data = reinterpret_cast<T*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
                 for (uint32_t i = bulk / (uint32_t)sizeof(T); i < valid; ++i) slot_data[i] = src[i];   // ragged end
                 if (bulk) {
@@ -803,10 +832,21 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         RingCursor cur;
         Acc carry = Op::template identity<Acc>();
         if (HAS_CARRY) carry = *carry_in;
+        // With several lines, `carry` is the reduction of the tiles before the current wave that belong to the line
+        // in which the wave starts, and prefixes restart at every line start.  Which tiles of a wave belong to which
+        // line follows from the positions of the wave's first tile, of this block's tile and of the next wave's
+        // first tile inside their lines.  (With a single line all of this is constant and the masks disappear.)
         uint64_t first = 0;
-        for (uint32_t j = 0; j < my_tiles; ++j, first += G, cur.advance()) {
+        RingTile<MULTI> wave(0, tiles_per_line, G), mine(b, tiles_per_line, G);
+        for (uint32_t j = 0; j < my_tiles; ++j, first += G, cur.advance(), mine.advance()) {
             if (*abort_flag) break;
             const uint32_t gj = (uint32_t)((total_tiles - first < G) ? (total_tiles - first) : G);
+            const uint64_t line_first = wave.line;
+            wave.advance();                                                 // now the next wave's first tile
+            const bool same_line_next = !MULTI || wave.line == line_first;  // the wave lies in one line that goes on
+            const uint32_t next_lo = same_line_next ? 0u : (uint32_t)(G - wave.q);   // wave tiles from here on: next wave's line
+            const bool mine_in_first = !MULTI || mine.q >= b;               // my line began at or before the wave's start
+            const uint32_t mine_lo = mine_in_first ? 0u : (uint32_t)(b - mine.q);    // wave tiles from here to b: my line
             Acc excl = Op::template identity<Acc>(), tot = Op::template identity<Acc>();
             bool failed = false;
             for (uint32_t base_i = 0; base_i < gj; base_i += 32 * kRingGather) {
@@ -833,8 +873,8 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                             const uint64_t bits = (w0[i] & 0xffffffffull) | (w1[i] << 32);
                             Acc v;
                             memcpy(&v, &bits, sizeof(Acc));
-                            tot = Op::apply(tot, v);
-                            if (idx < b) excl = Op::apply(excl, v);
+                            if (!MULTI || idx >= next_lo) tot = Op::apply(tot, v);
+                            if (idx < b && (!MULTI || idx >= mine_lo)) excl = Op::apply(excl, v);
                         }
                     }
                 }
@@ -865,10 +905,11 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
             }
             Acc cexcl = shfl_up_any(c, 1);
             if (lane == 0) cexcl = Op::template identity<Acc>();
-            if (lane < SW) ctl->wprefix[cur.slot][lane] = Op::apply(Op::apply(carry, excl), cexcl);
+            const Acc before = mine_in_first ? Op::apply(carry, excl) : excl;
+            if (lane < SW) ctl->wprefix[cur.slot][lane] = Op::apply(before, cexcl);
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->ready[cur.slot]);
-            carry = Op::apply(carry, tot);
+            carry = same_line_next ? Op::apply(carry, tot) : tot;
         }
     }
     __syncthreads();

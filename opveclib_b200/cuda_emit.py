@@ -40,7 +40,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv22'
+TEMPLATE_VERSION = 'tv26'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -509,12 +509,13 @@ def emit_cuda(kernel, name):
                     'ull, ' + str(tpl) + 'ull, nullptr, nullptr);',
                     '}', '']
         ring = None
-        if multi and spec.lines == 1:
-            # one long line, pointers aligned: a single cooperative launch that moves every element once
+        # (bulk copies need every line to start on a 16-byte boundary)
+        if multi and can_align and (spec.lines == 1 or (spec.n * spec.dtype.itemsize) % 16 == 0):
+            # long lines, pointers aligned: a single cooperative launch that moves every element once
             src += ['extern "C" __global__ void __launch_bounds__(' + str(RING_THREADS) + ', 1) ' + name +
                     '_ring(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0, void* scratch) {',
-                    '    ovl::scan_ring<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', false>(in0, out0, nullptr, ' +
-                    str(spec.n) + 'ull, scratch);',
+                    '    ovl::scan_ring<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', false, ' + ('true' if spec.lines > 1 else 'false') +
+                    '>(in0, out0, nullptr, ' + str(spec.lines) + 'ull, ' + str(spec.n) + 'ull, scratch);',
                     '}', '']
             ring = {'symbol': name + '_ring', 'block': RING_THREADS, 'max_grid': RING_MAX_GRID,
                     'smem': RING_SLOTS * tile * spec.dtype.itemsize + RING_CTL_BYTES,

@@ -85,16 +85,16 @@ class KernelPlan(object):
             return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
         m = meta['scan']
         block, name = m['block'], m['name']
-        suffix = '' if which == 'scan' else 'u'
-        al = m['align_bytes'] if which == 'scan' else 0
         cap = sms * m['blocks_per_sm']
         scratch = m['scratch_bytes']
         passes = []
         ring = m.get('ring')
-        if ring and which == 'scan' and os.environ.get('OVL_SCAN_MODE') != 'threepass':
+        if which == 'ring':
             grid = max(1, min(m['tiles'], sms, ring['max_grid']))
-            return [self._make(device, ring['symbol'], grid, ring['block'], [0], [0], [al, al], scratch,
+            return [self._make(device, ring['symbol'], grid, ring['block'], [0], [0], [16, 16], scratch,
                                ring['zero_bytes'], ring['smem'], True)]
+        suffix = '' if which == 'scan' else 'u'
+        al = m['align_bytes'] if which == 'scan' else 0
         if m['three_pass']:
             passes.append(self._make(device, name + '_agg' + suffix, max(1, min(m['tiles'], cap)), block, [0], [], [al],
                                      scratch, m['zero_bytes']))
@@ -110,6 +110,9 @@ class KernelPlan(object):
         meta = self.meta
         if meta.get('scan'):
             al = meta['scan']['align_bytes']
+            if (meta['scan'].get('ring') and all(p % 16 == 0 for p in in_ptrs + out_ptrs)
+                    and os.environ.get('OVL_SCAN_MODE') != 'threepass'):
+                return 'ring'
             if meta['scan']['aligned_variant'] and all(p % al == 0 for p in in_ptrs + out_ptrs):
                 return 'scan'
             return 'scanu'

@@ -127,7 +127,7 @@ def test_generated_scan_of_a_long_line(dtype, fn):
     got = ns.ovl.evaluate([op])
     prog, _ = runtime.compile_outputs([op])
     plan = prog.plans[0]
-    assert plan.meta['scan']['ring'] is not None and plan.last_variant == 'scan'
+    assert plan.meta['scan']['ring'] is not None and plan.last_variant == 'ring'
     assert any(sym.endswith('_ring') for sym, _ in plan._variants)
     if dtype == 'float32':
         x64 = x.astype(np.float64)
@@ -167,3 +167,47 @@ def test_a_wait_that_nothing_satisfies_ends_with_a_status_not_a_hang():
     assert lib.ovl_status_string(status.value).decode().startswith('bounded device-side wait')
     got = _scan(dx, 0).cpu().numpy()
     np.testing.assert_allclose(got, _exact(x, 0), rtol=1.3e-7, atol=0)
+
+
+def _scan_lines(x2d, op):
+    import torch
+    lib = launcher.library()
+    stream = torch.cuda.current_stream().cuda_stream
+    lines, n = x2d.shape
+    out = torch.empty_like(x2d)
+    nbytes = int(lib.ovl_scan_f32_scratch_bytes(lines, n))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device='cuda')
+    launcher.check(lib.ovl_scan_f32(op, x2d.data_ptr(), out.data_ptr(), lines, n, None, scratch.data_ptr(), nbytes, stream),
+                   'scan')
+    status = ctypes.c_int32(-1)
+    launcher.check(lib.ovl_read_kernel_status(scratch.data_ptr(), stream, ctypes.byref(status)), 'status')
+    assert status.value == 0
+    return out
+
+
+@pytest.mark.parametrize('op', [0, 1])
+@pytest.mark.parametrize('lines,n', [(2, 2 * TILE), (3, 2 * TILE + 4), (7, 5 * TILE - 8), (40, 9 * TILE + 12),
+                                     (300, TILE + 4), (5, 148 * TILE + 2 * TILE), (2, 3 * 148 * TILE + 100)])
+def test_several_long_lines_in_one_launch(lines, n, op):
+    """Lines of several tiles each: tiles are numbered line by line, waves cross line boundaries, prefixes restart
+    at every line start (line lengths divisible by four, so every line starts on a 16-byte boundary)."""
+    import torch
+    rs = np.random.RandomState(lines * 31 + n % 97)
+    x = (rs.normal(0, 1, (lines, n)) if op == 0 else rs.uniform(0.9999, 1.0001, (lines, n))).astype(np.float32)
+    got = _scan_lines(torch.from_numpy(x).cuda(), op).cpu().numpy()
+    x64 = x.astype(np.float64)
+    want = (np.cumsum(x64, axis=1) if op == 0 else np.cumprod(x64, axis=1)).astype(np.float32)
+    np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
+
+
+def test_generated_scan_of_several_long_lines_along_the_last_axis():
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    x = np.random.RandomState(23).normal(0, 1, (3, 5, 40000)).astype(np.float32)
+    op = ns.cumsum(x, axis=2)
+    got = ns.ovl.evaluate([op])
+    prog, _ = runtime.compile_outputs([op])
+    plan = prog.plans[0]
+    assert plan.meta['scan']['ring'] is not None and plan.last_variant == 'ring'
+    want = np.cumsum(x.astype(np.float64), axis=2).astype(np.float32)
+    np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
