@@ -128,12 +128,12 @@ int ovl_read_kernel_status(const void* scratch, void* cuda_stream, int32_t* out_
 /* Inclusive scan (op: 0 = sum, 1 = product) of `lines` contiguous lines of `n` fp32 elements each, device
  * memory in and out, with the same cooperative kernels the code generator uses for recognised accumulate loops
  * (the reference's one-worker-per-line loop: opveclib/examples/test_accumulate.py:22-78).  Accumulation is in
- * fp64.  Lines of at most 8192 elements are scanned in one pass by one thread block each.  A single longer line
- * with 16-byte aligned pointers is scanned by the ring scan: one cooperative launch (a block per SM, so nothing
- * else should occupy the device's SMs meanwhile) that reads and writes every element once.  Several long lines,
- * or unaligned pointers, take three streaming passes (tile aggregates, prefixes of the aggregates, seeded tile
- * scans).  The environment variable OVL_SCAN_MODE=threepass forces the three passes, OVL_SCAN_MODE=lookback
- * selects a single pass with decoupled look-back.
+ * fp64.  Lines of at most 8192 elements are scanned in one pass by one thread block each.  Longer lines whose
+ * starts are 16-byte aligned (aligned pointers and, with several lines, n divisible by four) are scanned by the
+ * ring scan: one cooperative launch (a block per SM, so nothing else should occupy the device's SMs meanwhile)
+ * that reads and writes every element once.  Other long lines take three streaming passes (tile aggregates,
+ * prefixes of the aggregates, seeded tile scans).  The environment variable OVL_SCAN_MODE=threepass forces the
+ * three passes, OVL_SCAN_MODE=lookback selects a single pass with decoupled look-back.
  * `carry` (device pointer to one double, or NULL) is combined into every element of a single line (lines
  * must be 1 when it is given).  `scratch` must hold ovl_scan_f32_scratch_bytes(lines, n) bytes. */
 uint64_t ovl_scan_f32_scratch_bytes(uint64_t lines, uint64_t n);
