@@ -265,10 +265,21 @@ def _host_scan_plan(prog):
     return m['op'], m['n']
 
 
+def as_output_list(outputs):
+    """The outputs behind what a caller handed to ``evaluate``: a list or tuple is taken as it is; a single
+    operator stands for all of its outputs (the reference unpacks it the same way,
+    opveclib/operator.py:2256: ``_build_op_dag(*output_list)`` iterates an operator); one output is itself."""
+    from .opgraph import Operator
+    if isinstance(outputs, (list, tuple)):
+        return list(outputs)
+    if isinstance(outputs, Operator) and len(outputs) > 1:
+        return list(outputs)
+    return [outputs]
+
+
 def compile_outputs(output_list, opt_level=3):
     """Build, fuse and compile the operator graph behind ``output_list``; cached by graph structure."""
-    if not isinstance(output_list, (list, tuple)):
-        output_list = [output_list]
+    output_list = as_output_list(output_list)
     dag = build_op_dag(*output_list)
     key = (dag.text(), opt_level >= 3)
     prog = _programs.get(key)
@@ -337,7 +348,7 @@ def profile(output_list, target_language='b200', profiling_iterations=1, opt_lev
             return [dst], {prog.plans[0].name: np.array([np.nan])}
         # host-resident inputs: stream slabs of rows through the device when the graph allows it
         from . import streaming
-        splan = streaming.plan(output_list if isinstance(output_list, (list, tuple)) else [output_list], dag, prog,
+        splan = streaming.plan(as_output_list(output_list), dag, prog,
                                opt_level)
         if splan is not None:
             out_types = [prog.plans[o].out_types[k] for o, k in prog.dag.outputs]

@@ -122,8 +122,8 @@ def as_torch(tensor_list, opt_level=3):
     (as ``as_tensorflow`` does, opveclib/operator.py:2409-2412).  The graph runs as the custom operator
     ``torch.ops.ovl_b200.run``; its backward as ``torch.ops.ovl_b200.run_backward``."""
     import torch
-    single = not isinstance(tensor_list, (list, tuple))
-    outputs = [tensor_list] if single else list(tensor_list)
+    outputs = runtime.as_output_list(tensor_list)
+    single = not isinstance(tensor_list, (list, tuple)) and len(outputs) == 1
     prog, dag = runtime.compile_outputs(outputs, opt_level)
     if not torch.cuda.is_available():
         raise RuntimeError('opveclib_b200 needs a CUDA device: there is no CPU execution path')

@@ -318,3 +318,28 @@ def test_every_name_the_reference_exports_is_present():
     for n in '''neg tanh sin cos tan sigmoid split concat add sub mul div mod equal not_equal less less_equal greater
              greater_equal'''.split():
         assert hasattr(stdops, n), n
+
+
+def test_an_operator_with_several_outputs_stands_for_all_of_them():
+    """`evaluate(op)` with a multi-output operator evaluates every output, as in the reference
+    (opveclib/test/test_multiple_outputs.py:44-52)."""
+    import numpy as np
+    import opveclib_b200 as ovl
+    from opveclib_b200 import runtime
+
+    @ovl.operator()
+    def multi_op(input0, input1, input2):
+        pos = ovl.position_in(input0.shape)
+        output0, output1, output2 = ovl.output_like(input0), ovl.output_like(input0), ovl.output_like(input0)
+        d = input0[pos] + input1[pos]
+        output0[pos] = d
+        output1[pos] = d * input2[pos]
+        output2[pos] = d + input2[pos]
+        return output0, output1, output2
+
+    a, b, c = np.zeros(5), np.zeros(5), np.zeros(5)
+    op = multi_op(a, b, c)
+    assert len(runtime.as_output_list(op)) == 3
+    assert len(runtime.as_output_list(op[1])) == 1 and len(runtime.as_output_list([op[0], op[2]])) == 2
+    o0, o1, o2 = op
+    assert o1.shape == [5]
