@@ -482,16 +482,19 @@ __device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uin
 //
 // One persistent block per SM.  Tiles are numbered line by line; tile t belongs to block t % gridDim.x; the tiles b, b + G, b + 2G ... of block b
 // are its "waves" 0, 1, 2 ...  A tile travels through a ring of kRingSlots tile-sized slots in shared memory.
-// The block's warps have four roles, coupled only through shared-memory barriers (mbarrier):
+// The block's warps have five roles, coupled only through shared-memory barriers (mbarrier):
 //   copy warp      one thread streams the block's tiles into free slots with bulk asynchronous copies
 //                  (cp.async.bulk, completion counted on the slot's `full` barrier), up to a whole ring ahead;
 //   reduce warps   as soon as a tile has landed they total its sixteen chunks (`reduced` barrier) and publish the sum
 //                  of those, the tile aggregate, to global memory;
+//   chunk warp     scans the sixteen chunk totals exclusively (`chunked` barrier);
 //   prefix warp    for every wave, gathers the aggregates all blocks published for that wave and forms
 //                  carry-so-far (+) aggregates of the blocks to the left; each block keeps its own copy of the carry
 //                  over the waves, computed in the same order everywhere, so no block depends on a value another
 //                  block derived - only on the aggregates themselves.  It then leaves the prefix in front of every
-//                  chunk of the tile in shared memory (`ready` barrier);
+//                  chunk of the tile in shared memory (`ready` barrier).  Its loop is the critical path of the whole
+//                  grid - every scan waits for it - which is why the part that does not need the other blocks'
+//                  aggregates is the chunk warp's;
 //   scan warps     each scans one chunk of the tile out of its slot, seeded with the chunk's prefix, stores the
 //                  result and releases the slot (`empty` barrier); the sixteen scan warps never wait for each other.
 // Reduction runs ahead of the scan by as many tiles as the ring holds, which hides the trip of the aggregates
@@ -505,11 +508,11 @@ __device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uin
 constexpr int kRingSlots = 6;
 constexpr int kRingScanWarps = kScanBlock / 32;    // 16 warps scan a tile (VPT vectors per thread)
 constexpr int kRingReduceWarps = 8;                // 8 warps reduce a tile (2 * VPT vectors per thread)
-constexpr int kRingThreads = (kRingScanWarps + kRingReduceWarps + 2) * 32;
+constexpr int kRingThreads = (kRingScanWarps + kRingReduceWarps + 3) * 32;   // + copy, chunk and prefix warps
 constexpr int kRingMaxGrid = 256;
-constexpr int kRingGather = 8;                     // aggregates fetched per lane and round by the prefix warp
+constexpr int kRingGather = 5;                     // aggregates fetched per lane and round by the prefix warp (160 a round)
 constexpr long long kRingWaitCycles = 1ll << 32;   // bound of every wait, in SM clock cycles (about two seconds)
-constexpr uint32_t kRingCtlBytes = 2048;
+constexpr uint32_t kRingCtlBytes = 4096;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -553,6 +556,8 @@ struct RingCtl {
     uint64_t reduced[kRingSlots];                  // ctot[slot] is valid             (one arrival per reduce warp)
     uint64_t ready[kRingSlots];                    // wprefix[slot] is valid          (prefix warp)
     uint64_t empty[kRingSlots];                    // slot has been read for the scan (one arrival per scan warp)
+    Acc cexcl[kRingSlots][kRingScanWarps];         // exclusive scan of the chunk totals inside the tile
+    uint64_t chunked[kRingSlots];                  // cexcl[slot] is valid            (chunk warp)
     int abort;
     int rstop[2];                                  // abort flag as latched for the reduce warps' current step
 };
@@ -655,6 +660,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         for (int s = 0; s < R; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->reduced[s], RW);
+            mbar_init(&ctl->chunked[s], 1);
             mbar_init(&ctl->ready[s], 1);
             mbar_init(&ctl->empty[s], SW);
         }
@@ -827,6 +833,31 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                     }
             }
         }
+    } else if (wid == SW + RW + 1) {
+        // --------------------------------------------------------------------------------------- chunk warp
+        // scans the sixteen chunk totals of a tile as soon as the reduce warps have written them and leaves the
+        // exclusive values in shared memory - work that does not need the other blocks, taken off the prefix warp
+        RingCursor cur;
+        for (uint32_t k = 0; k < my_tiles; ++k, cur.advance()) {
+            // the chunk totals have been written - which also means that the slot's previous tile has been scanned, so
+            // that its prefixes (wprefix, cexcl) are no longer needed; the prefix warp relies on this
+            if (!ring_wait(&ctl->reduced[cur.slot], cur.phase, abort_flag) ||
+                (k >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag))) {
+                if (lane == 0) ring_fail(hdr, abort_flag);
+                break;
+            }
+            Acc c = (lane < SW) ? ctl->ctot[cur.slot][lane] : Op::template identity<Acc>();
+#pragma unroll
+            for (int d = 1; d < SW; d <<= 1) {
+                const Acc y = shfl_up_any(c, d);
+                if (lane >= d) c = Op::apply(y, c);
+            }
+            Acc cexcl = shfl_up_any(c, 1);
+            if (lane == 0) cexcl = Op::template identity<Acc>();
+            if (lane < SW) ctl->cexcl[cur.slot][lane] = cexcl;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->chunked[cur.slot]);
+        }
     } else {
         // -------------------------------------------------------------------------------------- prefix warp
         RingCursor cur;
@@ -851,31 +882,38 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
             bool failed = false;
             for (uint32_t base_i = 0; base_i < gj; base_i += 32 * kRingGather) {
                 uint64_t w0[kRingGather], w1[kRingGather];
+                bool missing = false;
 #pragma unroll
                 for (int i = 0; i < kRingGather; ++i) {
                     const uint32_t idx = base_i + i * 32 + lane;
-                    w0[i] = w1[i] = 0;
+                    w0[i] = w1[i] = 1ull << 32;                         // (slots past the wave's end: valid, identity)
                     if (idx < gj) ring_peek(desc, first + idx, w0[i], w1[i]);
+                }
+#pragma unroll
+                for (int i = 0; i < kRingGather; ++i) missing |= (w0[i] >> 32) == 0 || (w1[i] >> 32) == 0;
+                if (__any_sync(0xffffffffu, missing)) {
+                    // not all there yet: poll the missing ones, with a bound
+                    const long long t0 = clock64();
+#pragma unroll
+                    for (int i = 0; i < kRingGather; ++i) {
+                        const uint32_t idx = base_i + i * 32 + lane;
+                        uint32_t spins = 0;
+                        while (((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) && clock64() - t0 < kRingWaitCycles && !*abort_flag) {
+                            if (++spins > 4) __nanosleep(64);
+                            ring_peek(desc, first + idx, w0[i], w1[i]);
+                        }
+                        failed |= (w0[i] >> 32) == 0 || (w1[i] >> 32) == 0;
+                    }
                 }
 #pragma unroll
                 for (int i = 0; i < kRingGather; ++i) {
                     const uint32_t idx = base_i + i * 32 + lane;
                     if (idx < gj) {
-                        uint32_t spins = 0;
-                        const long long t0 = clock64();
-                        while (((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) && clock64() - t0 < kRingWaitCycles && !*abort_flag) {
-                            if (++spins > 4) __nanosleep(64);
-                            ring_peek(desc, first + idx, w0[i], w1[i]);
-                        }
-                        if ((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) {
-                            failed = true;
-                        } else {
-                            const uint64_t bits = (w0[i] & 0xffffffffull) | (w1[i] << 32);
-                            Acc v;
-                            memcpy(&v, &bits, sizeof(Acc));
-                            if (!MULTI || idx >= next_lo) tot = Op::apply(tot, v);
-                            if (idx < b && (!MULTI || idx >= mine_lo)) excl = Op::apply(excl, v);
-                        }
+                        const uint64_t bits = (w0[i] & 0xffffffffull) | (w1[i] << 32);
+                        Acc v;
+                        memcpy(&v, &bits, sizeof(Acc));
+                        if (!MULTI || idx >= next_lo) tot = Op::apply(tot, v);
+                        if (idx < b && (!MULTI || idx >= mine_lo)) excl = Op::apply(excl, v);
                     }
                 }
             }
@@ -883,32 +921,22 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                 if (lane == 0) ring_fail(hdr, abort_flag);
                 break;
             }
-            // lanes hold interleaved partial results; combine in a fixed butterfly so that every block derives
-            // the same carry
+            // lanes hold interleaved partial results, combined in a fixed butterfly
 #pragma unroll
-            for (int d = 16; d > 0; d >>= 1) {
-                tot = Op::apply(tot, shfl_xor_any(tot, d));
-                excl = Op::apply(excl, shfl_xor_any(excl, d));
-            }
-            // wprefix[slot] of the slot's previous tile must have been read, and this tile's chunk totals written
-            if ((j >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag)) ||
-                !ring_wait(&ctl->reduced[cur.slot], cur.phase, abort_flag)) {
+            for (int d = 16; d > 0; d >>= 1) excl = Op::apply(excl, shfl_xor_any(excl, d));
+            // this tile's chunk prefixes are ready (and with that, wprefix[slot] of the slot's previous tile was read)
+            if (!ring_wait(&ctl->chunked[cur.slot], cur.phase, abort_flag)) {
                 if (lane == 0) ring_fail(hdr, abort_flag);
                 break;
             }
-            // exclusive scan of the chunk totals, seeded with the prefix in front of the tile
-            Acc c = (lane < SW) ? ctl->ctot[cur.slot][lane] : Op::template identity<Acc>();
-#pragma unroll
-            for (int d = 1; d < SW; d <<= 1) {
-                const Acc y = shfl_up_any(c, d);
-                if (lane >= d) c = Op::apply(y, c);
-            }
-            Acc cexcl = shfl_up_any(c, 1);
-            if (lane == 0) cexcl = Op::template identity<Acc>();
             const Acc before = mine_in_first ? Op::apply(carry, excl) : excl;
-            if (lane < SW) ctl->wprefix[cur.slot][lane] = Op::apply(before, cexcl);
+            if (lane < SW) ctl->wprefix[cur.slot][lane] = Op::apply(before, ctl->cexcl[cur.slot][lane]);
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->ready[cur.slot]);
+            // the carry of the next wave, off the path of this wave's scans (the same butterfly in every block, so
+            // every block derives the same value)
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) tot = Op::apply(tot, shfl_xor_any(tot, d));
             carry = same_line_next ? Op::apply(carry, tot) : tot;
         }
     }

@@ -47,9 +47,9 @@ SCAN_BLOCK = 512
 SCAN_VPT = 4
 SCAN_HEADER_BYTES = 16
 # must match kRingThreads / kRingSlots / kRingCtlBytes / kRingMaxGrid of csrc/templates/ovl_scan.cuh
-RING_THREADS = 832
+RING_THREADS = 864
 RING_SLOTS = 6
-RING_CTL_BYTES = 2048
+RING_CTL_BYTES = 4096
 RING_MAX_GRID = 256
 # reduction loops: threads that share one worker's loop - a warp, or a whole block when there are too few workers
 # to fill the device with warps and the loop is long enough to feed a block
