@@ -140,10 +140,11 @@ uint64_t ovl_scan_f32_scratch_bytes(uint64_t lines, uint64_t n);
 int ovl_scan_f32(int op, const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch,
                  uint64_t scratch_bytes, void* cuda_stream);
 /* The same scan of ONE line split at the point where ranks of a sharded scan exchange their totals:
- * ovl_scan_f32_begin reads the shard once, keeps the per-tile aggregates in `scratch` and writes the shard's
- * total to *out_total (device memory); after the carry has been formed from the totals of the ranks before,
- * ovl_scan_f32_finish produces the result.  The pair moves 12 bytes per element, like ovl_scan_f32 on a long
- * line, so a shard costs the same whether or not a carry exchange sits in the middle. */
+ * ovl_scan_f32_begin reads the shard once and writes the shard's total to *out_total (device memory); after the
+ * carry has been formed from the totals of the ranks before, ovl_scan_f32_finish produces the result.  The pair
+ * moves 12 bytes per element (4 for the total, 8 for the scan): a shard's total is only known after all of it has
+ * been read, so every shard but the first must be read twice.  Pass the same `in`, `n` and scratch to both calls
+ * (the scratch carries state from one to the other). */
 int ovl_scan_f32_begin(int op, const float* in, uint64_t n, double* out_total, void* scratch, uint64_t scratch_bytes,
                        void* cuda_stream);
 int ovl_scan_f32_finish(int op, const float* in, float* out, uint64_t n, const double* carry, void* scratch,

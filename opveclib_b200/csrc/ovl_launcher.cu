@@ -544,6 +544,38 @@ extern "C" int ovl_selftest_scan_timeout(const float* in, float* out, uint64_t n
     return launch_ring<ovl::OpAdd>(in, out, 1, n, nullptr, scratch, (cudaStream_t)cuda_stream, /*withhold_block=*/0);
 }
 
+namespace {
+
+// total of n elements into *out_total; `scratch` holds ovl_reduce_f32_scratch_bytes(n) bytes
+int launch_reduce(int op, const float* in, uint64_t n, double* out_total, void* scratch, cudaStream_t stream) {
+    const bool aligned = ((uintptr_t)in % 16 == 0);
+    const uint64_t want = (n / 4 + ovl::kScanBlock - 1) / ovl::kScanBlock;
+    const uint64_t max_grid = (uint64_t)sm_count_cached() * 8;
+    uint32_t grid = (uint32_t)(want < max_grid ? want : max_grid);
+    if (grid == 0) grid = 1;
+    OVL_CUDA(cudaMemsetAsync(scratch, 0, 16, stream));
+    if (op == 0) {
+        if (aligned) reduce_f32_kernel<ovl::OpAdd, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
+        else reduce_f32_kernel<ovl::OpAdd, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
+    } else {
+        if (aligned) reduce_f32_kernel<ovl::OpMul, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
+        else reduce_f32_kernel<ovl::OpMul, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e);
+    return OVL_OK;
+}
+
+// The begin/finish pair of a shard: when the shard can be scanned by the ring scan, `begin` only needs the
+// shard's total (one streaming read) and `finish` is the ring scan seeded with the carry; otherwise `begin` leaves
+// per-tile aggregates in the scratch for the seeded tile scans of `finish`.  Both sides evaluate this predicate.
+bool shard_uses_ring(const float* in, uint64_t n) {
+    return long_line_mode() == kModeRing && n > kTile && ((uintptr_t)in % 16 == 0) &&
+           ovl_scan_f32_scratch_bytes(1, n) >= sizeof(ovl::ScanHeader) + ovl_reduce_f32_scratch_bytes(n);
+}
+
+}  // namespace
+
 extern "C" int ovl_scan_f32_begin(int op, const float* in, uint64_t n, double* out_total, void* scratch,
                                   uint64_t scratch_bytes, void* cuda_stream) {
     if (!out_total) return OVL_ERR_NULL;
@@ -552,6 +584,8 @@ extern "C" int ovl_scan_f32_begin(int op, const float* in, uint64_t n, double* o
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const bool aligned = ((uintptr_t)in % 16 == 0);
     OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader), stream));
+    if (shard_uses_ring(in, n))
+        return launch_reduce(op, in, n, out_total, reinterpret_cast<char*>(scratch) + sizeof(ovl::ScanHeader), stream);
     cudaError_t e = (op == 0) ? launch_tile_aggregates<ovl::OpAdd>(in, 1, n, scratch, aligned, stream)
                               : launch_tile_aggregates<ovl::OpMul>(in, 1, n, scratch, aligned, stream);
     if (e != cudaSuccess) return cuda_fail(e);
@@ -568,6 +602,12 @@ extern "C" int ovl_scan_f32_finish(int op, const float* in, float* out, uint64_t
     if (st != OVL_OK) return st;
     cudaStream_t stream = (cudaStream_t)cuda_stream;
     const bool aligned = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    if (shard_uses_ring(in, n)) {
+        // `begin` left no tile aggregates: the ring scan, or (output not aligned) the three passes from the start
+        OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader), stream));
+        if (op == 0) return run_scan<ovl::OpAdd>(in, out, 1, n, carry, scratch, aligned, stream);
+        return run_scan<ovl::OpMul>(in, out, 1, n, carry, scratch, aligned, stream);
+    }
     if (op == 0) return finish_scan<ovl::OpAdd>(in, out, 1, n, carry, scratch, aligned, stream);
     return finish_scan<ovl::OpMul>(in, out, 1, n, carry, scratch, aligned, stream);
 }
@@ -640,21 +680,5 @@ extern "C" int ovl_reduce_f32(int op, const float* in, uint64_t n, double* out_t
     if (n == 0) return OVL_ERR_INVALID;
     const uint64_t need = ovl_reduce_f32_scratch_bytes(n);
     if (!scratch || scratch_bytes < need || ((uintptr_t)scratch % 16) != 0) return OVL_ERR_SCRATCH;
-    cudaStream_t stream = (cudaStream_t)cuda_stream;
-    const bool aligned = ((uintptr_t)in % 16 == 0);
-    const uint64_t want = (n / 4 + ovl::kScanBlock - 1) / ovl::kScanBlock;
-    const uint64_t max_grid = (uint64_t)sm_count_cached() * 8;
-    uint32_t grid = (uint32_t)(want < max_grid ? want : max_grid);
-    if (grid == 0) grid = 1;
-    OVL_CUDA(cudaMemsetAsync(scratch, 0, 16, stream));
-    if (op == 0) {
-        if (aligned) reduce_f32_kernel<ovl::OpAdd, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
-        else reduce_f32_kernel<ovl::OpAdd, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
-    } else {
-        if (aligned) reduce_f32_kernel<ovl::OpMul, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
-        else reduce_f32_kernel<ovl::OpMul, false><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
-    }
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return cuda_fail(e);
-    return OVL_OK;
+    return launch_reduce(op, in, n, out_total, scratch, (cudaStream_t)cuda_stream);
 }

@@ -6,14 +6,13 @@ slab - no communication.  The one exchange this backend knows is the carry of a 
 sharded axis (the reference has no multi-GPU support at all; its rank-1 ``accumulate`` is a single worker,
 opveclib/examples/test_accumulate.py:40-41):
 
-1. every rank reads its shard once, keeping one fp64 aggregate per tile and the shard total (``ovl_scan_f32_begin``);
+1. every rank reads its shard once and forms the shard total in fp64 (``ovl_scan_f32_begin``);
 2. the totals are all-gathered (8 bytes per rank, NCCL on GPUs, gloo in CPU tests) into local memory;
-3. every rank combines the totals of the ranks before it into its carry, turns the tile aggregates into tile
-   prefixes seeded with the carry and scans its tiles (``ovl_scan_f32_finish``).
+3. every rank combines the totals of the ranks before it into its carry and scans its shard seeded with it
+   (``ovl_scan_f32_finish``: the ring scan, one launch).
 
-Per element this moves 4 bytes in step 1 and 8 in step 3 - exactly what the unsharded scan of a long line moves
-(its three passes are the same kernels without the exchange in the middle), so sharding costs one tiny
-collective and nothing else.
+Per element this moves 4 bytes in step 1 and 8 in step 3: a shard's total is only known after all of it has been
+read, so every shard but the first is read twice - 12 bytes per element against the 8 of the one-GPU scan.
 """
 import ctypes
 
@@ -93,7 +92,7 @@ class ShardedScan(object):
                                                  self.scan_scratch.data_ptr(), self.scan_bytes, stream), 'scan')
             self.launches += 1
             return out
-        # step 1: tile aggregates (kept in the scratch) and the shard total
+        # step 1: the shard total
         launcher.check(self.lib.ovl_scan_f32_begin(self.code, x.data_ptr(), self.shard_len, self.total.data_ptr(),
                                                    self.scan_scratch.data_ptr(), self.scan_bytes, stream), 'shard totals')
         # step 2: exchange, carry = combination of the totals of the ranks before this one
@@ -104,7 +103,7 @@ class ShardedScan(object):
         else:
             torch.prod(torch.where(self.before, self.totals, torch.ones_like(self.totals)), dim=0, keepdim=True,
                        out=self.carry)
-        # step 3: prefixes of the aggregates seeded with the carry, then the seeded tile scans
+        # step 3: the scan of the shard, seeded with the carry
         launcher.check(self.lib.ovl_scan_f32_finish(self.code, x.data_ptr(), out.data_ptr(), self.shard_len,
                                                     self.carry.data_ptr(), self.scan_scratch.data_ptr(),
                                                     self.scan_bytes, stream), 'shard scan')
