@@ -151,6 +151,10 @@ def build_graph(workload, rows_local=None, n_local=None):
                   'op_expm1': lambda: ns.expm1(x), 'op_mulc': lambda: u.ew_mulc(x, c=0.5), 'op_add': lambda: u.ew_add(x, x),
                   'op_where': lambda: u.where_greater(x, x)}
         return [single[workload]()], 1 << 26, 8
+    if workload == 'perf_accumulate':
+        # the reference's own timing harness: cumsum of fp64 [10000, 1000] along axis 0
+        # (opveclib/examples/test_perf_accumulate.py:35-48); 8 B read + 8 B written per element
+        return [ns.cumsum(np.zeros((10000, 1000), dtype=np.float64), axis=0)], 10000 * 1000, 16
     if workload == 'matvec':
         # reduction loop per row (documentation/programming.rst:320-344): the matrix is read once, 4 B per element
         return [cases.user_ops(ns).matvec(z(16384, 8192), z(8192))], 16384 * 8192, 4
@@ -165,7 +169,7 @@ def precompile():
         prog, dag = runtime.compile_outputs(outs)
         streaming.plan(outs, dag, prog, 3)          # the slab-shaped kernels of the end-to-end leg
     for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'light16', 'matvec', 'op_tanh', 'op_exp',
-              'op_log1p', 'op_expm1', 'op_mulc', 'op_add', 'op_where'):
+              'op_log1p', 'op_expm1', 'op_mulc', 'op_add', 'op_where', 'perf_accumulate'):
         runtime.compile_outputs(build_graph(w)[0])
 
 
@@ -176,6 +180,8 @@ def input_distribution(workload, index):
         return ('uniform', 0.99, 1.01)
     if workload in ('c1', 'c1_shift'):
         return ('uniform', -1.0, 1.0)
+    if workload == 'perf_accumulate':
+        return ('uniform', 0.0, 1.0)
     if workload == 'c3_grad' and index >= 2:
         return ('normal', 0.0, 0.1)
     return ('normal', 0.0, 1.0)
@@ -187,7 +193,7 @@ def make_device_inputs(torch, workload, types, device, seed):
     out = []
     for i, t in enumerate(types):
         kind, a, b = input_distribution(workload, i)
-        x = torch.empty(t.shape, dtype=torch.float32, device=device)
+        x = torch.empty(t.shape, dtype=t.dtype.as_torch(), device=device)
         if kind == 'uniform':
             x.uniform_(a, b, generator=gen)
         else:
@@ -221,7 +227,7 @@ def cpu_reference_run(workload, iterations):
         inputs = []
         for i, t in enumerate(types):
             kind, a, b = input_distribution(workload, i)
-            inputs.append((rs.uniform(a, b, t.shape) if kind == 'uniform' else rs.normal(a, b, t.shape)).astype(np.float32))
+            inputs.append((rs.uniform(a, b, t.shape) if kind == 'uniform' else rs.normal(a, b, t.shape)).astype(t.dtype.as_numpy()))
     if ref_runner.available(name):
         threads = ref_runner.hardware_threads()
         _, ms = ref_runner.run(name, inputs, num_threads=0, variant='opt', iterations=iterations)
@@ -260,8 +266,8 @@ def run_reference_arm(args, workload):
     line = {
         'impl': 'reference', 'metric': 'fused-op elements/s', 'value': res['value'], 'unit': 'elements/s',
         'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': res['ms_per_sample'],
-        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-        'config': workload_config(workload, args.gpus), 'cpu_baseline': res,
+        'higher_is_better': True, 'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f64' if workload == 'perf_accumulate' else 'f32',
+        'data': 'synthetic', 'config': workload_config(workload, args.gpus), 'cpu_baseline': res,
         'e2e': {'value': res['value'], 'unit': 'elements/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0, 'wall_s': time.time() - t0,
     }
@@ -281,6 +287,7 @@ def workload_config(workload, n):
         'c3_grad': 'LSTM cell gradient, gates fp32 [512, 4096], c/dc/dh [512, 1024]',
         'c5': 'cumsum along the sharded axis, fp32 [2^31] normal(0,1), contiguous shards, fp64 carry exchange',
         'matvec': 'matrix-vector product as a per-row reduction loop, fp32 [16384, 8192] x [8192] normal(0,1)',
+        'perf_accumulate': "cumsum along axis 0, fp64 [10000, 1000] uniform[0,1] (the reference's own timing harness)",
     }
     if workload.startswith('op_'):
         names[workload] = 'single operator ' + workload[3:] + ' of the 16-operator chain, fp32 [1, 2^26] uniform[-2,2]'
@@ -360,9 +367,9 @@ def main():
         outs, elements_local, bytes_per_elem = build_graph(workload, rows_local=rows_local)
         prog, dag = runtime.compile_outputs(outs)
         ins = make_device_inputs(torch, workload, dag.input_types, device, SEED + rank)
-        out_bufs = [torch.empty(prog.plans[o].out_types[k].shape, dtype=torch.float32, device=device)
-                    for o, k in prog.dag.outputs]
-        small = sum(t.size * 4 for t in dag.input_types) <= 126 * 10 ** 6     # inputs that fit in L2
+        out_bufs = [torch.empty(prog.plans[o].out_types[k].shape, dtype=prog.plans[o].out_types[k].dtype.as_torch(),
+                                device=device) for o, k in prog.dag.outputs]
+        small = sum(t.size * t.dtype.itemsize for t in dag.input_types) <= 126 * 10 ** 6     # inputs that fit in L2
         if small:
             flush = torch.empty(192 << 20, dtype=torch.uint8, device=device)
 
@@ -435,10 +442,10 @@ def main():
 
     # ---- end to end through the public API: pinned host arrays in, pinned host arrays out
     if not args.no_e2e and workload != 'c5':
-        host_in = [torch.empty(tuple(tt.shape), dtype=torch.float32, pin_memory=True) for tt in dag.input_types]
+        host_in = [torch.empty(tuple(tt.shape), dtype=tt.dtype.as_torch(), pin_memory=True) for tt in dag.input_types]
         for h, d in zip(host_in, ins):
             h.copy_(d)
-        host_out = [torch.empty(tuple(b.shape), dtype=torch.float32, pin_memory=True) for b in out_bufs]
+        host_out = [torch.empty(tuple(b.shape), dtype=b.dtype, pin_memory=True) for b in out_bufs]
         np_in = [h.numpy() for h in host_in]
         np_out = [h.numpy() for h in host_out]
         graph = rebuild_with_inputs(workload, np_in, rows_local if workload == 'c4' else None)
@@ -497,8 +504,8 @@ def main():
         line = {
             'metric': 'fused-op elements/s', 'value': value, 'unit': 'elements/s', 'n_gpus': world,
             'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': launch_ms, 'higher_is_better': True,
-            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f32', 'data': 'synthetic',
-            'config': workload_config(workload, world),
+            'scaling': 'strong', 'vs_baseline': None, 'dtype': 'f64' if workload == 'perf_accumulate' else 'f32',
+            'data': 'synthetic', 'config': workload_config(workload, world),
             'effective_hbm_gbs': achieved * world, 'pct_of_8tbs_per_gpu': 100.0 * achieved / NOMINAL_HBM_GBS,
             'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
                          'peak_kind': peak_kind + ' HBM copy bandwidth', 'algorithmic_bytes_per_element': bytes_per_elem,
@@ -537,6 +544,8 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
         return [cases.user_ops(ns).shift_cyclic(np_inputs[0])]
     if workload == 'matvec':
         return [cases.user_ops(ns).matvec(np_inputs[0], np_inputs[1])]
+    if workload == 'perf_accumulate':
+        return [ns.cumsum(np_inputs[0], axis=0)]
     if workload == 'c3':
         op = ns.lstm(np_inputs[0], np_inputs[1], forget_bias=0.0)
         return [op[0], op[1]]

@@ -51,6 +51,9 @@ RING_THREADS = 864
 RING_SLOTS = 6
 RING_CTL_BYTES = 4096
 RING_MAX_GRID = 256
+# must match kColBlock / kColRows of csrc/templates/ovl_colscan.cuh
+COL_BLOCK = 256
+COL_ROWS = 64
 # reduction loops: threads that share one worker's loop - a warp, or a whole block when there are too few workers
 # to fill the device with warps and the loop is long enough to feed a block
 REDUCE_BLOCK = 256
@@ -475,7 +478,39 @@ def emit_cuda(kernel, name):
                        'group': group, 'trips': red.n, 'op': red.op}
     # ---- cooperative scan
     spec = patterns.match_scan(kernel, info)
-    if spec is not None and spec.n >= patterns.SCAN_MIN_AXIS:
+    if spec is not None and spec.inner > 1:
+        # scan along a non-contiguous axis: warps walk down strips of columns, three streaming passes
+        if spec.n >= patterns.COLSCAN_MIN_AXIS:
+            src.insert(2, '#include "ovl_colscan.cuh"')
+            t = ctype(spec.dtype)
+            acc = 'double' if spec.dtype.is_float else t
+            acc_size = 8 if spec.dtype.is_float else spec.dtype.itemsize
+            vec = max(1, 16 // spec.dtype.itemsize)
+            op = 'ovl::OpAdd' if spec.op == 'add' else 'ovl::OpMul'
+            chunks = (spec.n + COL_ROWS - 1) // COL_ROWS
+            can_align = spec.inner % vec == 0
+            agg_ptr = '(' + acc + '*)((char*)scratch + ' + str(SCAN_HEADER_BYTES) + ')'
+            dims = str(spec.outer) + 'ull, ' + str(spec.n) + 'ull, ' + str(spec.inner) + 'ull'
+            tiles = {}
+            for suffix, v in [('u', 1)] + ([('', vec)] if can_align else []):
+                strips = (spec.inner + 32 * v - 1) // (32 * v)
+                tiles[suffix] = spec.outer * chunks * strips
+                src += ['extern "C" __global__ void __launch_bounds__(' + str(COL_BLOCK) + ') ' + name + '_cagg' + suffix +
+                        '(const ' + t + '* __restrict__ in0, void* scratch) {',
+                        '    ovl::col_tiles<' + t + ', ' + acc + ', ' + op + ', ' + str(v) + ', false>(in0, nullptr, ' + agg_ptr +
+                        ', ' + dims + ');', '}', '',
+                        'extern "C" __global__ void __launch_bounds__(' + str(COL_BLOCK) + ') ' + name + '_cscan' + suffix +
+                        '(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0, void* scratch) {',
+                        '    ovl::col_tiles<' + t + ', ' + acc + ', ' + op + ', ' + str(v) + ', true>(in0, out0, ' + agg_ptr +
+                        ', ' + dims + ');', '}', '']
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(COL_BLOCK) + ') ' + name + '_cpfx(void* scratch) {',
+                    '    ovl::col_prefixes<' + acc + ', ' + op + '>(' + agg_ptr + ', ' + dims + ');', '}', '']
+            meta['scan'] = {'name': name, 'strided': True, 'aligned_variant': bool(can_align), 'block': COL_BLOCK,
+                            'tiles': tiles, 'columns': spec.outer * spec.inner,
+                            'scratch_bytes': SCAN_HEADER_BYTES + spec.outer * chunks * spec.inner * acc_size,
+                            'zero_bytes': SCAN_HEADER_BYTES, 'align_bytes': 16, 'lines': spec.lines, 'n': spec.n,
+                            'outer': spec.outer, 'inner': spec.inner, 'op': spec.op, 'ring': None}
+    elif spec is not None and spec.n >= patterns.SCAN_MIN_AXIS:
         src.insert(2, '#include "ovl_scan.cuh"')
         t = ctype(spec.dtype)
         acc = 'double' if spec.dtype.is_float else t

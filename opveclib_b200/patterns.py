@@ -16,13 +16,21 @@ SCAN_MIN_AXIS = 1024
 
 
 class ScanSpec(object):
-    """``lines`` contiguous lines of ``n`` elements, inclusive scan with ``op`` ('add' or 'mul')."""
+    """Inclusive scan with ``op`` ('add' or 'mul') along the middle axis of a tensor seen as ``[outer, n, inner]``:
+    ``lines = outer * inner`` lines of ``n`` elements.  ``inner == 1``: the lines are contiguous."""
 
-    def __init__(self, op, lines, n, dtype):
+    def __init__(self, op, lines, n, dtype, outer=None, inner=1):
         self.op = op
         self.lines = lines
         self.n = n
         self.dtype = dtype
+        self.outer = lines if outer is None else outer
+        self.inner = inner
+
+
+#: scans along a non-contiguous axis shorter than this stay on the generic kernel (one thread per line already
+#: reads whole row segments there; the cooperative version pays off when lines are long)
+COLSCAN_MIN_AXIS = 256
 
 
 def _row_major_strides(shape):
@@ -34,8 +42,8 @@ def _row_major_strides(shape):
 
 
 def match_scan(kernel, info=None):
-    """ScanSpec if the kernel is exactly an inclusive scan along the contiguous axis of its only input into its
-    only output, else None."""
+    """ScanSpec if the kernel is exactly an inclusive scan along one axis of its only input into its only output
+    (one worker per line, workgroup = the tensor's shape without that axis), else None."""
     if len(kernel.inputs) != 1 or len(kernel.outputs) != 1:
         return None
     x, y = kernel.inputs[0], kernel.outputs[0]
@@ -75,18 +83,38 @@ def match_scan(kernel, info=None):
     if rd.tensor is not x or wr.tensor is not y or rd.form is None or wr.form is None or rd.form != wr.form:
         return None
     form = rd.form
-    if form.mod is not None or form.const != 0 or form.coef(sym) != 1:
+    if form.mod is not None or form.const != 0 or form.coef(sym) < 1:
         return None
     shape = kernel.workgroup_shape
     lines = kernel.num_workers
-    for d, s in enumerate(_row_major_strides(shape)):
-        want = s * n if shape[d] > 1 else form.coef(('p', d))
-        if form.coef(('p', d)) != want:
-            return None
     if set(form.coefs) - set([sym] + [('p', d) for d in range(len(shape))]):
         return None
     if x.size != lines * n:
         return None
+    # which axis of the tensor is scanned: its extent is n and its row-major stride the loop variable's
+    # coefficient; the workgroup's axes must then be the tensor's other axes, in order, with their strides
+    tshape = list(x.shape)
+    tstrides = _row_major_strides(tshape)
+    geometry = None
+    for axis in range(len(tshape)):
+        if tshape[axis] != n or tstrides[axis] != form.coef(sym):
+            continue
+        others = [d for d in range(len(tshape)) if d != axis]
+        if not others:
+            ok = list(shape) == [1]
+        else:
+            ok = len(others) == len(shape) and all(
+                shape[k] == tshape[d] and (tshape[d] == 1 or form.coef(('p', k)) == tstrides[d])
+                for k, d in enumerate(others))
+        if ok:
+            outer = 1
+            for d in range(axis):
+                outer *= tshape[d]
+            geometry = (outer, lines // outer)
+            break
+    if geometry is None:
+        return None
+    outer, inner = geometry
 
     # the running value
     assigns = [a for a in all_nodes if a.kind == 'assign_var']
@@ -146,7 +174,7 @@ def match_scan(kernel, info=None):
         return None
     if x.dtype.name == 'float16':
         return None
-    return ScanSpec(op, lines, n, x.dtype)
+    return ScanSpec(op, lines, n, x.dtype, outer, inner)
 
 
 #: reduction loops shorter than this stay on the generic kernel

@@ -85,6 +85,19 @@ class KernelPlan(object):
             return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
         m = meta['scan']
         block, name = m['block'], m['name']
+        if which in ('cscan', 'cscanu'):
+            suffix = '' if which == 'cscan' else 'u'
+            al = 16 if which == 'cscan' else 0
+            warps = block // 32
+            tiles = m['tiles'][suffix]
+            cap = sms * (2048 // block)
+            scratch = m['scratch_bytes']
+            return [self._make(device, name + '_cagg' + suffix, max(1, min((tiles + warps - 1) // warps, cap)), block, [0], [],
+                               [al], scratch, m['zero_bytes']),
+                    self._make(device, name + '_cpfx', max(1, min((m['columns'] + block - 1) // block, cap)), block, [], [],
+                               [], scratch, 0),
+                    self._make(device, name + '_cscan' + suffix, max(1, min((tiles + warps - 1) // warps, cap)), block, [0],
+                               [0], [al, al], scratch, 0)]
         cap = sms * m['blocks_per_sm']
         scratch = m['scratch_bytes']
         passes = []
@@ -108,6 +121,10 @@ class KernelPlan(object):
 
     def choose(self, in_ptrs, out_ptrs):
         meta = self.meta
+        if meta.get('scan') and meta['scan'].get('strided'):
+            if meta['scan']['aligned_variant'] and all(p % 16 == 0 for p in in_ptrs + out_ptrs):
+                return 'cscan'
+            return 'cscanu'
         if meta.get('scan'):
             al = meta['scan']['align_bytes']
             if (meta['scan'].get('ring') and all(p % 16 == 0 for p in in_ptrs + out_ptrs)
@@ -258,7 +275,7 @@ def _host_scan_plan(prog):
         return None
     plan = prog.plans[0]
     m = plan.meta.get('scan')
-    if not m or m['lines'] != 1 or m['n'] < _HOST_SCAN_MIN:
+    if not m or m.get('strided') or m['lines'] != 1 or m['n'] < _HOST_SCAN_MIN:
         return None
     if plan.in_types[0].dtype.name != 'float32' or len(plan.in_types) != 1:
         return None

@@ -103,3 +103,12 @@ def test_unassigned_variable_gives_the_trip_count():
     k = _kernel(u.dot(np.zeros((4, 777)), np.zeros((4, 777))))
     info = analyze(k)
     assert list(info.loop_vars.values()) == [('l', 0)] and info.ranges[('l', 0)] == (0, 776)
+
+
+def test_scans_along_any_axis_are_recognised_with_their_geometry():
+    ns = cases.impl()
+    for shape, axis, want in [((4, 2048), 1, (4, 2048, 4, 1)), ((4096, 64), 0, (64, 4096, 1, 64)),
+                              ((3, 500, 7), 1, (21, 500, 3, 7)), ((5000,), 0, (1, 5000, 1, 1)),
+                              ((2, 3, 4, 300), 2, (1800, 4, 6, 300))]:
+        spec = patterns.match_scan(_kernel(ns.cumsum(np.zeros(shape, np.float32), axis=axis)))
+        assert spec is not None and (spec.lines, spec.n, spec.outer, spec.inner) == want, (shape, axis)
