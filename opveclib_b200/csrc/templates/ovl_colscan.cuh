@@ -79,20 +79,41 @@ __device__ __forceinline__ void col_tiles(const T* __restrict__ in, T* __restric
 }
 
 // agg[o][chunk][col] becomes the reduction of the chunks before `chunk` in the same column (exclusive scan along
-// the chunks); one thread per column, neighbouring threads neighbouring columns.
+// the chunks).  One warp per column: lane L owns a contiguous run of the column's chunks, scans it locally, and the
+// lane totals are scanned across the warp, so a column costs two trips to memory whatever its length.
 template <typename Acc, class Op>
 __device__ __forceinline__ void col_prefixes(Acc* __restrict__ agg, const uint64_t outer, const uint64_t n, const uint64_t inner) {
+    constexpr int PER = 8;                      // chunks per lane and round
     const uint64_t chunks = col_chunks(n);
     const uint64_t columns = outer * inner;
-    const uint64_t stride = (uint64_t)gridDim.x * kColBlock;
-    for (uint64_t c = (uint64_t)blockIdx.x * kColBlock + threadIdx.x; c < columns; c += stride) {
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps = (uint64_t)gridDim.x * (kColBlock / 32);
+    for (uint64_t c = (uint64_t)blockIdx.x * (kColBlock / 32) + (threadIdx.x >> 5); c < columns; c += warps) {
         const uint64_t o = c / inner, col = c - o * inner;
         Acc* a = agg + o * chunks * inner + col;
-        Acc run = Op::template identity<Acc>();
-        for (uint64_t k = 0; k < chunks; ++k) {
-            const Acc t = a[k * inner];
-            a[k * inner] = run;
-            run = Op::apply(run, t);
+        Acc carry = Op::template identity<Acc>();
+        for (uint64_t k0 = 0; k0 < chunks; k0 += 32 * PER) {
+            const uint64_t mine = k0 + (uint64_t)lane * PER;
+            Acc v[PER];
+#pragma unroll
+            for (int i = 0; i < PER; ++i) v[i] = (mine + i < chunks) ? a[(mine + i) * inner] : Op::template identity<Acc>();
+            Acc t = v[0];
+#pragma unroll
+            for (int i = 1; i < PER; ++i) t = Op::apply(t, v[i]);
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const Acc y = shfl_up_any(t, d);
+                if (lane >= d) t = Op::apply(y, t);
+            }
+            Acc run = shfl_up_any(t, 1);
+            if (lane == 0) run = Op::template identity<Acc>();
+            run = Op::apply(carry, run);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) {
+                if (mine + i < chunks) a[(mine + i) * inner] = run;
+                run = Op::apply(run, v[i]);
+            }
+            carry = Op::apply(carry, shfl_any(t, 31));
         }
     }
 }

@@ -94,7 +94,7 @@ class KernelPlan(object):
             scratch = m['scratch_bytes']
             return [self._make(device, name + '_cagg' + suffix, max(1, min((tiles + warps - 1) // warps, cap)), block, [0], [],
                                [al], scratch, m['zero_bytes']),
-                    self._make(device, name + '_cpfx', max(1, min((m['columns'] + block - 1) // block, cap)), block, [], [],
+                    self._make(device, name + '_cpfx', max(1, min((m['columns'] + warps - 1) // warps, cap)), block, [], [],
                                [], scratch, 0),
                     self._make(device, name + '_cscan' + suffix, max(1, min((tiles + warps - 1) // warps, cap)), block, [0],
                                [0], [al, al], scratch, 0)]
