@@ -653,6 +653,8 @@ CASES = {name[len('case_'):]: fn for name, fn in sorted(globals().items()) if na
 TRANSCENDENTAL = {'c1_chain', 'c1_chain_odd', 'expm1_f64', 'log1p_f64', 'lstm_fwd', 'lstm_grad', 'lstm_fwd_bias_odd',
                   'chain16', 'stdops_lstm', 'stdops_binary_f32', 'unary_f32', 'unary_f64', 'binary_f32', 'binary_f64'}
 # cases that contain a re-associated scan on the GPU (compared with a scaled absolute tolerance)
-SCANS = {'cumsum_rows_f32', 'cumprod_rows_f32', 'cumsum_rank1_f32', 'cumsum_f64'}
+SCANS = {'cumsum_rows_f32', 'cumprod_rows_f32', 'cumsum_rank1_f32', 'cumsum_f64', 'cumsum_axis0_f32'}
+# axis along which those cases scan, where it is not the last one
+SCAN_AXIS = {'cumsum_axis0_f32': 0}
 # cases that contain a re-associated reduction loop on the GPU (floating point: compared with a tolerance)
 REDUCTIONS = {'dot_f64_rows', 'matvec_f32_long', 'rowprod_scaled'}

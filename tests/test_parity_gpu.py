@@ -34,7 +34,7 @@ def _check(name, got, want, source):
             assert_exact(g, w, what)
         elif name in cases.SCANS:
             w64 = w.astype(np.float64)
-            line_max = np.max(np.abs(w64), axis=-1, keepdims=True)
+            line_max = np.max(np.abs(w64), axis=cases.SCAN_AXIS.get(name, -1), keepdims=True)
             assert_close(g, w, rtol=1e-5, atol=1e-5 * line_max * np.ones_like(w64), what=what)
         elif name in cases.REDUCTIONS:
             tight = 1e-5 if g.dtype == np.float32 else 1e-12
