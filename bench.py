@@ -1,11 +1,14 @@
 """Benchmark of the hot path: fused OVL operator graphs on B200, next to the reference's CPU operator.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4|c2_cumsum|c2_cumprod|c1|c3|c5] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload c4|c5|c2_cumsum|c2_cumprod|c1|c1_shift|c3|c3_grad|light16|matvec|perf_accumulate|op_<name>]
 
 Default workload (the one the headline metric is quoted on): the 16-operator fused element-wise chain over an
 fp32 tensor [8, 2^27] drawn from uniform[-2, 2], rows sharded contiguously over N GPUs with no communication
 (total work fixed: strong scaling).  One step is one evaluation of the whole operator graph on the rank's rows.
-The other workloads exist for profiling single kernels; `c5` is the scan across shard boundaries.
+The other workloads exist for profiling single kernels: `c5` is the scan across shard boundaries, `matvec` a
+per-row reduction loop, `perf_accumulate` the reference's own timing harness (fp64 [10000, 1000] cumsum along axis 0),
+`op_<name>` one operator of the chain on its own.
 
 Prints one JSON line (rank 0).  ``value`` is elements/s with inputs resident in HBM, timed with CUDA events on
 the launching stream, maximum over ranks; ``e2e`` is the same work through ``ovl.evaluate`` from pinned host
