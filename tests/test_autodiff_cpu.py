@@ -114,3 +114,64 @@ def test_custom_operators_are_registered_with_fake_tensor_support():
         assert [tuple(o.shape) for o in outs] == [(6, 8), (6, 8)] and outs[0].dtype == torch.float32
         grads = torch.ops.ovl_b200.run_backward([a, b], list(outs), handle)
         assert [tuple(x.shape) for x in grads] == [(6, 32), (6, 8)]
+
+
+def _torch_grads(fn, arrays, grads_out):
+    leaves = [torch.tensor(a, requires_grad=True) for a in arrays]
+    outs = fn(*leaves)
+    outs = outs if isinstance(outs, (list, tuple)) else [outs]
+    total = sum((o * torch.tensor(g)).sum() for o, g in zip(outs, grads_out))
+    total.backward()
+    return [x.grad.numpy() if x.grad is not None else None for x in leaves]
+
+
+def test_stdops_binary_and_unary_gradients_match_autograd():
+    """The component-wise gradients of the operator library (the reference compares them with TensorFlow's,
+    opveclib/stdops/test_math.py:91-157)."""
+    so = cases.impl().stdops
+    rs = np.random.RandomState(11)
+    lhs = rs.random_sample(100)
+    rhs = lhs + rs.randint(-1, 2, size=100) + 0.25          # (never zero: it is also used as a divisor)
+    above = rs.random_sample(100)
+    for fcn, ref in [(so.add, torch.add), (so.sub, torch.sub), (so.mul, torch.mul), (so.div, torch.div)]:
+        for a, b in ((lhs, rhs), (rhs, lhs)):
+            dag = build_op_dag(fcn(a, b))
+            grads, has_grad, _, _ = _run_backward(dag, [above])
+            want = dict(zip((id(a), id(b)), _torch_grads(ref, [a, b], [above])))
+            assert has_grad == [True, True]
+            for leaf, got in zip(dag.inputs, grads):
+                np.testing.assert_allclose(got, want[id(leaf)], rtol=1e-13, atol=0)
+    arg = rs.random_sample(100)
+    for fcn, ref in [(so.neg, torch.neg), (so.tanh, torch.tanh), (so.sin, torch.sin), (so.cos, torch.cos),
+                     (so.tan, torch.tan), (so.sigmoid, torch.sigmoid)]:
+        dag = build_op_dag(fcn(arg))
+        grads, has_grad, _, _ = _run_backward(dag, [above])
+        np.testing.assert_allclose(grads[0], _torch_grads(ref, [arg], [above])[0], rtol=1e-12, atol=1e-15)
+
+
+def test_split_and_concat_gradients_match_autograd():
+    """Gradients through split and concat of equal parts (opveclib/stdops/test_math.py:159-268)."""
+    so = cases.impl().stdops
+    rs = np.random.RandomState(12)
+    x = rs.random_sample((3, 8, 5))
+    parts = so.split(x, split_dim=1, num_split=4)
+    outs = [so.mul(parts[0], parts[3]), so.add(parts[1], parts[2])]
+    dag = build_op_dag(*outs)
+    above = [rs.random_sample((3, 2, 5)), rs.random_sample((3, 2, 5))]
+    grads, has_grad, _, _ = _run_backward(dag, above)
+
+    def ref(t):
+        p = t.chunk(4, dim=1)
+        return [p[0] * p[3], p[1] + p[2]]
+    np.testing.assert_allclose(grads[0], _torch_grads(ref, [x], above)[0], rtol=1e-13, atol=0)
+
+    a, b, c = rs.random_sample((4, 3)), rs.random_sample((4, 3)), rs.random_sample((4, 3))
+    cat = so.concat(a, b, c, concat_dim=1)
+    dag = build_op_dag(so.mul(cat, cat))
+    above = [rs.random_sample((4, 9))]
+    grads, has_grad, _, _ = _run_backward(dag, above)
+    want = dict(zip((id(a), id(b), id(c)),
+                    _torch_grads(lambda p, q, r: torch.cat([p, q, r], dim=1) ** 2, [a, b, c], above)))
+    assert has_grad == [True, True, True]
+    for leaf, got in zip(dag.inputs, grads):
+        np.testing.assert_allclose(got, want[id(leaf)], rtol=1e-13, atol=0)

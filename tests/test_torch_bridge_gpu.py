@@ -88,3 +88,72 @@ def test_backward_kernels_compile():
         bdag, _ = compose_backward(build_op_dag(*outs))
         prog = runtime.Program(merge_op_dag(bdag))
         assert len(prog.plans) == 1
+
+
+@pytest.mark.skipif(DRYRUN, reason='needs a device')
+def test_the_reference_gradient_examples_against_torch_autograd():
+    """The two cases of opveclib/test/test_gradients.py (there against TensorFlow's gradients, exact equality):
+    z = x*x + 3*y with its hand-written gradient, and a clip operator whose gradient masks the clipped elements."""
+    import torch
+    ovl = cases.impl().ovl
+
+    @ovl.operator()
+    def func(x, y):
+        pos = ovl.position_in(x.shape)
+        z = ovl.output_like(x)
+        z[pos] = x[pos] * x[pos] + 3 * y[pos]
+        return z
+
+    @ovl.gradient(func)
+    @ovl.operator()
+    def func_grad(x, y, dz):
+        pos = ovl.position_in(x.shape)
+        dx, dy = ovl.output_like(x), ovl.output_like(y)
+        dx[pos] = 2.0 * x[pos] * dz[pos]
+        dy[pos] = 3.0 * dz[pos]
+        return dx, dy
+
+    @ovl.operator()
+    def clip(arg, threshold1=None, threshold2=None):
+        pos = ovl.position_in(arg.shape)
+        clipped = ovl.output_like(arg)
+        x = arg[pos]
+        with ovl.if_(x < threshold1):
+            clipped[pos] = threshold1
+        with ovl.elif_(x > threshold2):
+            clipped[pos] = threshold2
+        with ovl.else_():
+            clipped[pos] = x
+        return clipped
+
+    @ovl.gradient(clip)
+    @ovl.operator()
+    def clip_grad(arg, d_arg, threshold1=None, threshold2=None):
+        pos = ovl.position_in(arg.shape)
+        g = ovl.output_like(arg)
+        x = arg[pos]
+        with ovl.if_(x < threshold1):
+            g[pos] = 0
+        with ovl.elif_(x > threshold2):
+            g[pos] = 0
+        with ovl.else_():
+            g[pos] = d_arg[pos]
+        return g
+
+    rs = np.random.RandomState(5)
+    a = torch.tensor(rs.random_sample(10), device='cuda', requires_grad=True)
+    b = torch.tensor(rs.random_sample(10), device='cuda', requires_grad=True)
+    above = torch.tensor(rs.random_sample(10), device='cuda')
+    z = ovl.as_torch(func(a, b))
+    z.backward(above)
+    a2, b2 = a.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    (a2 * a2 + 3 * b2).backward(above)
+    assert torch.equal(z.detach(), (a2 * a2 + 3 * b2).detach())
+    assert torch.equal(a.grad, a2.grad) and torch.equal(b.grad, b2.grad)
+
+    c = torch.tensor(rs.random_sample(10), device='cuda', requires_grad=True)
+    scale = float(rs.random_sample(1)[0])
+    (ovl.as_torch(clip(c, threshold1=0.1, threshold2=0.9)).sum() * scale).backward()
+    c2 = c.detach().clone().requires_grad_(True)
+    (torch.clamp(c2, 0.1, 0.9).sum() * scale).backward()
+    assert torch.equal(c.grad, c2.grad)
