@@ -583,6 +583,134 @@ def case_merge_graph(ns):
     return [stack3(sum0, prod0, sum1), sum0], [in0]
 
 
+def merge_ops(ns):
+    """Operators of the reference's merge tests (opveclib/test/test_operator_merge.py:22-179): scans down the rows
+    and along the columns with zero-seeded accumulators, a loop that overwrites its variable (so it is NOT a
+    reduction), clamped padding through index variables, cropping."""
+    key = ('merge', id(ns.ovl))
+    if key in _cache:
+        return _cache[key]
+    ovl = ns.ovl
+
+    @ovl.operator()
+    def scan_down_rows(m):
+        rows, cols = m.shape
+        col = ovl.position_in(cols)
+        acc = ovl.variable(0, m.dtype)
+        out = ovl.output_like(m)
+        for row in ovl.arange(rows):
+            acc <<= acc + m[row, col]
+            out[row, col] = acc
+        return out
+
+    @ovl.operator()
+    def scan_along_cols(m):
+        rows, cols = m.shape
+        row = ovl.position_in(rows)
+        acc = ovl.variable(0, m.dtype)
+        out = ovl.output_like(m)
+        for col in ovl.arange(cols):
+            acc <<= acc + m[row, col]
+            out[row, col] = acc
+        return out
+
+    @ovl.operator()
+    def last_product(a, b):
+        # every iteration overwrites the variable: the result is the LAST product, not a sum
+        rows, cols, work = a.shape[0], b.shape[1], a.shape[1]
+        pos = ovl.position_in([rows, cols])
+        out = ovl.output([rows, cols], a.dtype)
+        acc = ovl.variable(0, dtype=a.dtype)
+        for k in ovl.arange(work):
+            acc <<= a[pos[0], k] * b[k, pos[1]]
+        out[pos[0], pos[1]] = acc
+        return out
+
+    @ovl.operator()
+    def pad_clamped(m, n=None):
+        rows_in, cols_in = m.shape
+        out = ovl.output([rows_in + 2 * n, cols_in + 2 * n], m.dtype)
+        pos = ovl.position_in([rows_in + 2 * n, cols_in + 2 * n])
+        r = ovl.variable(pos[0], dtype=pos.dtype)
+        c = ovl.variable(pos[1], dtype=pos.dtype)
+        with ovl.if_(r < n):
+            r <<= 0
+        with ovl.elif_(r >= (rows_in + n)):
+            r <<= rows_in - 1
+        with ovl.else_():
+            r <<= r - n
+        with ovl.if_(c < n):
+            c <<= 0
+        with ovl.elif_(c >= (cols_in + n)):
+            c <<= cols_in - 1
+        with ovl.else_():
+            c <<= c - n
+        out[pos[0], pos[1]] = m[r, c]
+        return out
+
+    @ovl.operator()
+    def crop(m, n=None):
+        rows, cols = m.shape[0] - 2 * n, m.shape[1] - 2 * n
+        pos = ovl.position_in([rows, cols])
+        out = ovl.output([rows, cols], m.dtype)
+        out[pos[0], pos[1]] = m[n + pos[0], n + pos[1]]
+        return out
+
+    @ovl.operator()
+    def rows_of_four(m):
+        cols = m.shape[1]
+        col = ovl.position_in(cols)
+        outs = [ovl.output(cols, m.dtype) for _ in range(4)]
+        for r in range(4):
+            outs[r][col] = m[r, col]
+        return outs
+
+    ops = types.SimpleNamespace(scan_down_rows=scan_down_rows, scan_along_cols=scan_along_cols, last_product=last_product,
+                                pad_clamped=pad_clamped, crop=crop, rows_of_four=rows_of_four)
+    _cache[key] = ops
+    return ops
+
+
+def case_merge_scan_nested(ns):
+    x = np.random.RandomState(71).random_sample([3, 5])
+    m = merge_ops(ns)
+    return [m.scan_down_rows(m.scan_down_rows(x))], [x]
+
+
+def case_merge_scan_rows_then_cols(ns):
+    x = np.random.RandomState(72).random_sample([3, 3])
+    m = merge_ops(ns)
+    return [m.scan_along_cols(m.scan_down_rows(x))], [x]
+
+
+def case_merge_product_then_scan(ns):
+    rs = np.random.RandomState(73)
+    a, b = rs.random_sample([3, 5]), rs.random_sample([5, 2])
+    m = merge_ops(ns)
+    return [m.scan_along_cols(m.last_product(a, b))], [a, b]
+
+
+def case_merge_pad_crop(ns):
+    x = np.random.RandomState(74).random_sample([3, 5])
+    m = merge_ops(ns)
+    return [m.crop(m.pad_clamped(x, n=2), n=2)], [x]
+
+
+def case_merge_add_tree(ns):
+    rs = np.random.RandomState(75)
+    in0, in1, in2, in3 = [rs.random_sample([5]) for _ in range(4)]
+    u = user_ops(ns)
+    sum0 = u.ew_add(in1, in2)
+    return [u.ew_add(in0, sum0), u.ew_add(in3, sum0)], [in0, in1, in2, in3]
+
+
+def case_merge_product_split_adds(ns):
+    x = np.random.RandomState(76).random_sample([4, 4])
+    m, u = merge_ops(ns), user_ops(ns)
+    s = m.rows_of_four(m.last_product(x, x))
+    return [u.ew_add(s[0], s[1]), u.ew_add(s[2], s[3])], [x]
+
+
 def case_dot_reference_test(ns):
     # the reference's own test: RandomState(1), uniform(-1, 1), 100 vectors of 10 elements
     rng = np.random.RandomState(1)

@@ -55,8 +55,13 @@ def main(argv):
             print('  note: reference opt_level=3 joint evaluation of %s disagrees with opt_level=0; '
                   'recording per-output evaluations' % name)
             res = [ns.ovl.evaluate([o], target_language='cpp', opt_level=3) for o in outs]
-            for a, b in zip(res, unmerged):
-                assert np.array_equal(a, b, equal_nan=True), 'reference opt_level 0 and 3 disagree for ' + name
+            if not all(np.array_equal(a, b, equal_nan=True) for a, b in zip(res, unmerged)):
+                # Seen for a scan fed by another scan of the same workgroup (the reference merges them through a
+                # temporary buffer, opveclib/test/test_operator_merge.py:227-236, and the merged operator computes
+                # something else).  The unmerged evaluation is the operators' meaning; record that.
+                print('  note: reference opt_level=3 evaluation of %s disagrees with opt_level=0 even per output; '
+                      'recording the opt_level=0 results' % name)
+                res = unmerged
         payload = {}
         for i, a in enumerate(ins):
             payload['in_%d' % i] = np.asarray(a)

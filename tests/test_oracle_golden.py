@@ -35,7 +35,9 @@ def test_oracle_reproduces_reference(name):
             assert_exact(g, w, what)
 
 
-@pytest.mark.parametrize('name', ['c1_chain', 'chain16', 'stdops_lstm', 'merge_graph', 'lstm_grad'])
+@pytest.mark.parametrize('name', ['c1_chain', 'chain16', 'stdops_lstm', 'merge_graph', 'lstm_grad', 'merge_scan_nested',
+                                  'merge_scan_rows_then_cols', 'merge_product_then_scan', 'merge_pad_crop',
+                                  'merge_add_tree', 'merge_product_split_adds'])
 def test_fused_graph_equals_unfused_on_cpu(name):
     """Fusion must not change a single bit: the fused graph run through the oracle equals the unfused one."""
     from opveclib_b200.fuse import merge_op_dag

@@ -68,7 +68,9 @@ def test_cuda_matches_reference_golden(name):
 
 
 @pytest.mark.parametrize('name', ['c1_chain', 'chain16', 'stdops_lstm', 'merge_graph', 'lstm_grad', 'cumsum_rows_f32',
-                                  'shift_1031', 'loops_locals'])
+                                  'shift_1031', 'loops_locals', 'merge_scan_nested', 'merge_scan_rows_then_cols',
+                                  'merge_product_then_scan', 'merge_pad_crop', 'merge_add_tree',
+                                  'merge_product_split_adds'])
 @pytest.mark.parametrize('opt_level', [0, 3])
 def test_cuda_matches_oracle_at_both_opt_levels(name, opt_level):
     """opt_level 0 (one kernel per operator) and 3 (fused) both agree with the oracle
