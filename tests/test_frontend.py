@@ -343,3 +343,35 @@ def test_an_operator_with_several_outputs_stands_for_all_of_them():
     assert len(runtime.as_output_list(op[1])) == 1 and len(runtime.as_output_list([op[0], op[2]])) == 2
     o0, o1, o2 = op
     assert o1.shape == [5]
+
+
+def test_index_forms_and_python_control_flow_on_expressions():
+    """Index checks of opveclib/test/test_expressions.py:293-333 and the refusal to use an expression where Python
+    needs a truth value (ibid. 516-547)."""
+    with E.tracing():
+        a = E.zeros((5, 5), float32)
+        v = E.variable(0, uint64)
+        a[0, 0]
+        a[[0, 0]]
+        a[v, 0]
+        for bad in ([1], [0, 0, 0], [v], [v, 0, 0], [v, 5], [0, 5], [-1, 0]):
+            with pytest.raises(IndexError):
+                a[bad]
+        two = E.zeros(2, float32)
+        a[two]                                           # a rank-1 tensor of the right length is an index
+        for bad in (E.zeros(1, float32), E.zeros(3, float32), E.zeros((2, 1), float32)):
+            with pytest.raises(IndexError):
+                a[bad]
+        x = E.variable(0.0, float32)
+        with pytest.raises(SyntaxError):
+            if x == 0:
+                pass
+        with pytest.raises(SyntaxError):
+            if x:
+                pass
+        with pytest.raises(SyntaxError):
+            max(x, 1)
+        with pytest.raises(SyntaxError):
+            min(x, 1)
+        with pytest.raises(TypeError):
+            E.if_(E.zeros((5, 5), float32))
