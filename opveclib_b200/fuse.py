@@ -240,9 +240,14 @@ def _merge_pair(g, h, internal, live_g_outputs):
     internal_out_nodes = {id(g.kernel.outputs[k]): k for k in var_of_output}
     internal_in_nodes = {id(h.kernel.inputs[i]): k for i, k in internal.items()}
 
+    dead_out_nodes = set(id(n) for k, n in enumerate(g.kernel.outputs)
+                         if k not in live_g_outputs and k not in var_of_output)
+
     def producer_hook(node, mapping, out_block):
         if node.kind in ('input', 'output', 'position'):
             return False
+        if node.kind == 'assign_tensor' and id(node.args[0]) in dead_out_nodes:
+            return False            # an output nothing consumes: the merged kernel does not produce it
         if node.kind == 'assign_tensor' and id(node.args[0]) in internal_out_nodes:
             k = internal_out_nodes[id(node.args[0])]
             assign = _raw(E.AssignVariable)

@@ -1,0 +1,43 @@
+"""Random operator graphs (tests/fuzz_graphs.py): fusion must not change a bit on the CPU oracle, and the CUDA path -
+generic, vectorised, fused or not - must reproduce the oracle exactly (the graphs use only exactly rounded
+arithmetic, comparisons and data movement)."""
+import numpy as np
+import pytest
+
+import cases
+import fuzz_graphs
+from helpers import DRYRUN, assert_exact
+
+SEEDS = list(range(40))
+
+
+@pytest.mark.parametrize('seed', SEEDS)
+def test_fusion_keeps_every_bit_on_the_oracle(seed):
+    from opveclib_b200.fuse import merge_op_dag
+    from opveclib_b200.opgraph import build_op_dag
+    from oracle import runner
+    outs, _ = fuzz_graphs.build(cases.impl(), seed)
+    dag = build_op_dag(*outs)
+    fused = merge_op_dag(dag)
+    assert len(fused.kernels) <= len(dag.kernels)
+    plain, _ = runner.run_dag(dag)
+    merged, _ = runner.run_dag(fused)
+    for i, (a, b) in enumerate(zip(plain, merged)):
+        assert_exact(b, a, 'seed %d output %d' % (seed, i))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('opt_level', [0, 3])
+@pytest.mark.parametrize('seed', SEEDS)
+def test_cuda_reproduces_the_oracle_exactly(seed, opt_level):
+    from oracle import runner
+    ns = cases.impl()
+    outs, _ = fuzz_graphs.build(ns, seed)
+    got = ns.ovl.evaluate(outs, opt_level=opt_level)
+    if DRYRUN:
+        return
+    want = runner.evaluate(outs)
+    if len(outs) == 1:
+        got, want = [got], [want]
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert_exact(np.asarray(g), w, 'seed %d opt %d output %d' % (seed, opt_level, i))
