@@ -30,9 +30,7 @@ __device__ __forceinline__ void col_tiles(const T* __restrict__ in, T* __restric
     const uint64_t tiles = outer * chunks * strips;
     const int lane = threadIdx.x & 31;
     const uint64_t warps = (uint64_t)gridDim.x * (kColBlock / 32);
-    for (uint64_t turn = (uint64_t)blockIdx.x * (kColBlock / 32) + (threadIdx.x >> 5); turn < tiles; turn += warps) {
-        // the writing pass walks the tiles backwards: what the totals pass read last is still in L2
-        const uint64_t tile = WRITE ? tiles - 1 - turn : turn;
+    for (uint64_t tile = (uint64_t)blockIdx.x * (kColBlock / 32) + (threadIdx.x >> 5); tile < tiles; tile += warps) {
         const uint64_t strip = tile % strips;
         const uint64_t chunk = (tile / strips) % chunks;
         const uint64_t o = tile / (strips * chunks);
