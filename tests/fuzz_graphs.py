@@ -101,7 +101,30 @@ def _ops(ovl):
         out[pos] = total - a[pos]
         return out
 
-    return dict(row_total=row_total, binary=binary, affine=affine, select=select, magnitude=magnitude, rotate_last=rotate_last,
+    @ovl.operator()
+    def gather_stride(a, k=None):
+        # a strided gather with wrap-around along the last axis
+        out = ovl.output_like(a)
+        pos = ovl.position_in(a.shape)
+        index = [pos[d] for d in range(a.rank)]
+        index[-1] = (pos[a.rank - 1] * k) % a.shape[-1]
+        out[pos] = a[index]
+        return out
+
+    @ovl.operator()
+    def neighbours(a):
+        # a three-point stencil along the last axis with clamped ends
+        out = ovl.output_like(a)
+        pos = ovl.position_in(a.shape)
+        last = a.rank - 1
+        left = [pos[d] for d in range(a.rank)]
+        right = [pos[d] for d in range(a.rank)]
+        left[last] = ovl.maximum(pos[last], 1) - 1
+        right[last] = ovl.minimum(pos[last] + 1, a.shape[-1] - 1)
+        out[pos] = a[left] - a[pos] + a[right]
+        return out
+
+    return dict(gather_stride=gather_stride, neighbours=neighbours, row_total=row_total, binary=binary, affine=affine, select=select, magnitude=magnitude, rotate_last=rotate_last,
                 mirror_first=mirror_first, stack_pair=stack_pair, unstack_pair=unstack_pair)
 
 
@@ -125,7 +148,8 @@ def build(ns, seed):
         leaves = [rs.randint(-9, 10, shape).astype(dtype) for _ in range(n_leaves)]
     values = list(leaves)
     exact_sums = not dtype.startswith('float')      # integer sums do not depend on the order of evaluation
-    kinds = ['binary', 'binary', 'binary', 'affine', 'select', 'magnitude', 'rotate', 'mirror', 'stack']
+    kinds = ['binary', 'binary', 'binary', 'affine', 'select', 'magnitude', 'rotate', 'mirror', 'stack', 'gather',
+             'neighbours']
     if exact_sums:
         # no products of products (signed overflow), but scans and reduction loops
         kinds = [k for k in kinds if k != 'magnitude'] + ['cumsum', 'row_total']
@@ -150,6 +174,10 @@ def build(ns, seed):
             new = ns.cumsum(pick(), axis=int(rs.randint(rank)))
         elif kind == 'row_total':
             new = ops['row_total'](pick())
+        elif kind == 'gather':
+            new = ops['gather_stride'](pick(), k=int(rs.randint(2, 4)))
+        elif kind == 'neighbours':
+            new = ops['neighbours'](pick())
         elif kind == 'mirror':
             new = ops['mirror_first'](pick())
         else:

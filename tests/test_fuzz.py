@@ -1,6 +1,8 @@
 """Random operator graphs (tests/fuzz_graphs.py): fusion must not change a bit on the CPU oracle, and the CUDA path -
 generic, vectorised, fused or not - must reproduce the oracle exactly (the graphs use only exactly rounded
 arithmetic, comparisons and data movement)."""
+import os
+
 import numpy as np
 import pytest
 
@@ -8,7 +10,9 @@ import cases
 import fuzz_graphs
 from helpers import DRYRUN, assert_exact
 
-SEEDS = list(range(40))
+# OVL_FUZZ_SEEDS=first:last runs another range of seeds
+_first, _last = (int(v) for v in os.environ.get('OVL_FUZZ_SEEDS', '0:40').split(':'))
+SEEDS = list(range(_first, _last))
 
 
 @pytest.mark.parametrize('seed', SEEDS)
