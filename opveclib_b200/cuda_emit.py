@@ -40,7 +40,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv26'
+TEMPLATE_VERSION = 'tv32'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -54,6 +54,8 @@ RING_MAX_GRID = 256
 # must match kColBlock / kColRows of csrc/templates/ovl_colscan.cuh
 COL_BLOCK = 256
 COL_ROWS = 64
+TILE_EDGE = 32                # staged tiles are TILE_EDGE x TILE_EDGE workers
+TILE_SMEM_LIMIT = 40 * 1024   # bytes of shared memory the staged tiles of one kernel may take
 # reduction loops: threads that share one worker's loop - a warp, or a whole block when there are too few workers
 # to fill the device with warps and the loop is long enough to feed a block
 REDUCE_BLOCK = 256
@@ -344,6 +346,45 @@ def plan_vectorisation(kernel, info=None):
     return plan
 
 
+def plan_tiling(kernel, info):
+    """Reads that walk memory along another workgroup axis than the innermost one (a transposed operand:
+    ``out[i, j] = f(a[j, i], ...)``).  Neighbouring workers of such a read are a whole stride apart, so a warp
+    touches 32 sectors for 32 values.  Returns (axis, slots) when some input reads have coefficient 1 on workgroup
+    axis ``axis`` and a larger stride on the innermost axis; slots = [(tensor node, form, [read nodes])].  These reads
+    are staged through shared memory by tiles of TILE_EDGE x TILE_EDGE workers over (axis, innermost axis)."""
+    shape = kernel.workgroup_shape
+    rank = len(shape)
+    last = rank - 1
+    if rank < 2 or shape[last] < TILE_EDGE:
+        return None
+    per_axis = {}
+    for acc in info.accesses:
+        f = acc.form
+        if acc.is_write or f is None or f.mod is not None or acc.loop_depth > 0 or acc.tensor.kind != 'input':
+            continue
+        if any(sym[0] == 'l' for sym in f.coefs):
+            continue
+        lo, hi = f.bounds(info.ranges)
+        if lo < 0 or hi >= acc.tensor.size:
+            continue            # (staging loads unconditionally: every worker's address must be valid)
+        if abs(f.coef(('p', last))) < 2:
+            continue
+        for d in range(last):
+            if shape[d] >= TILE_EDGE and f.coef(('p', d)) == 1:
+                slot = per_axis.setdefault(d, {}).setdefault((id(acc.tensor), f.key()), [acc.tensor, f, []])
+                slot[2].append(acc.node)
+    if not per_axis:
+        return None
+    axis = max(sorted(per_axis), key=lambda d: len(per_axis[d]))
+    slots, used = [], 0
+    for tensor, form, nodes in per_axis[axis].values():
+        need = TILE_EDGE * (TILE_EDGE + 1) * tensor.dtype.itemsize
+        if used + need <= TILE_SMEM_LIMIT:
+            slots.append((tensor, form, nodes))
+            used += need
+    return axis, slots
+
+
 def _address_expr(form, shape):
     """C expression (uint64) of an affine offset at the group's first worker, from ``p<d>`` position names."""
     terms = []
@@ -352,6 +393,71 @@ def _address_expr(form, shape):
     for (kind, d), c in sorted(form.coefs.items()):
         terms.append('(uint64_t)p' + str(d) + ('' if c == 1 else ' * ' + str(c) + 'ull'))
     return ' + '.join(terms) if terms else '0ull'
+
+
+def _emit_tile(kernel, info, name, params, widx_t):
+    """The ``_tile`` kernel: (source lines, metadata) or (None, None) when the kernel has no transposed reads."""
+    tiling = plan_tiling(kernel, info)
+    if tiling is None:
+        return None, None
+    shape = kernel.workgroup_shape
+    src = []
+    axis, slots = tiling
+    rank = len(shape)
+    last = rank - 1
+    edge = TILE_EDGE
+    n_t, n_l = (shape[axis] + edge - 1) // edge, (shape[last] + edge - 1) // edge
+    n_tiles = n_t * n_l
+    for d in range(rank):
+        if d not in (axis, last):
+            n_tiles *= shape[d]
+    read_subst = {}
+    decls, stage = [], []
+    for si, (tensor, form, nodes) in enumerate(slots):
+        decls.append('    __shared__ ' + ctype(tensor.dtype) + ' ovl_tile' + str(si) + '[' + str(edge) + '][' + str(edge + 1) + '];')
+        stage.append('ovl_tile' + str(si) + '[ovl_ty + ovl_r][ovl_tx] = in' + str(tensor.attr['io_index']) + '[' +
+                     _address_expr(form, shape) + '];')
+        for n in nodes:
+            read_subst[id(n)] = 'ovl_tile' + str(si) + '[ovl_tx][ovl_ty + ovl_r]'
+    decode = ['uint64_t ovl_rem = ovl_t;',
+              'const uint32_t ovl_l0 = (uint32_t)(ovl_rem % ' + str(n_l) + 'ull) * ' + str(edge) + 'u; ovl_rem /= ' + str(n_l) + 'ull;',
+              'const uint32_t ovl_t0 = (uint32_t)(ovl_rem % ' + str(n_t) + 'ull) * ' + str(edge) + 'u; ovl_rem /= ' + str(n_t) + 'ull;']
+    for d in range(rank - 1, -1, -1):
+        if d not in (axis, last):
+            decode.append('const uint32_t ovl_q' + str(d) + ' = (uint32_t)(ovl_rem % ' + str(shape[d]) + 'ull); ovl_rem /= ' +
+                          str(shape[d]) + 'ull;')
+
+    def coords(t_expr, l_expr, prefix):
+        out = []
+        for d in range(rank):
+            v = t_expr if d == axis else (l_expr if d == last else 'ovl_q' + str(d))
+            out.append('const uint32_t ' + prefix + str(d) + ' = ' + v + ';')
+        return out
+    strides = _strides(shape)
+    widx = ' + '.join('(' + widx_t + ')w' + str(d) + ' * ' + str(strides[d]) + 'u' for d in range(rank))
+    pos_text = 'const uint32_t position[' + str(rank) + '] = {' + ', '.join('w' + str(d) for d in range(rank)) + '};'
+    em = BodyEmitter(kernel, 4, read_subst, position_text=pos_text)
+    em.block(kernel.body)
+    i2, i3, i4 = '        ', '            ', '                '
+    src += ['extern "C" __global__ void __launch_bounds__(' + str(BLOCK_THREADS) + ') ' + name + '_tile(' + params + ') {'] + \
+        decls + \
+        ['    const uint32_t ovl_tx = threadIdx.x & 31u, ovl_ty = threadIdx.x >> 5;',
+         '    for (uint64_t ovl_t = blockIdx.x; ovl_t < ' + str(n_tiles) + 'ull; ovl_t += gridDim.x) {'] + \
+        [i2 + l for l in decode] + \
+        [i2 + '// stage: consecutive threads walk the axis along which the operand is contiguous',
+         i2 + '#pragma unroll',
+         i2 + 'for (uint32_t ovl_r = 0; ovl_r < ' + str(edge) + 'u; ovl_r += ' + str(BLOCK_THREADS // 32) + 'u) {'] + \
+        [i3 + l for l in coords('ovl_t0 + ovl_tx', 'ovl_l0 + ovl_ty + ovl_r', 'p')] + \
+        [i3 + 'if (p' + str(axis) + ' < ' + str(shape[axis]) + 'u && p' + str(last) + ' < ' + str(shape[last]) + 'u) {'] + \
+        [i4 + l for l in stage] + [i3 + '}', i2 + '}', i2 + '__syncthreads();',
+         i2 + '// compute: consecutive threads are consecutive workers of the innermost axis',
+         i2 + '#pragma unroll',
+         i2 + 'for (uint32_t ovl_r = 0; ovl_r < ' + str(edge) + 'u; ovl_r += ' + str(BLOCK_THREADS // 32) + 'u) {'] + \
+        [i3 + l for l in coords('ovl_t0 + ovl_ty + ovl_r', 'ovl_l0 + ovl_tx', 'w')] + \
+        [i3 + 'if (w' + str(axis) + ' < ' + str(shape[axis]) + 'u && w' + str(last) + ' < ' + str(shape[last]) + 'u) {',
+         i4 + 'const ' + widx_t + ' worker_index = ' + widx + '; (void)worker_index;'] + \
+        em.lines + [i3 + '}', i2 + '}', i2 + '__syncthreads();', '    }', '}', '']
+    return src, {'symbol': name + '_tile', 'block': BLOCK_THREADS, 'tiles': n_tiles, 'axis': axis, 'staged': len(slots)}
 
 
 def emit_cuda(kernel, name):
@@ -378,7 +484,8 @@ def emit_cuda(kernel, name):
             '    for (' + widx_t + ' worker_index = (' + widx_t + ')blockIdx.x * ' + str(BLOCK_THREADS) +
             'u + threadIdx.x; worker_index < ' + str(W) + 'ull; worker_index += ovl_stride) {'] + em.lines + \
            ['    }', '}', '']
-    meta = {'gen': {'symbol': name + '_gen', 'block': BLOCK_THREADS, 'items': W}, 'vec': None, 'scan': None, 'red': None}
+    meta = {'gen': {'symbol': name + '_gen', 'block': BLOCK_THREADS, 'items': W}, 'vec': None, 'scan': None, 'red': None,
+            'tile': None}
 
     # ---- vectorised kernel
     plan = plan_vectorisation(kernel, info)
@@ -434,6 +541,11 @@ def emit_cuda(kernel, name):
             em.lines + [ind + '}'] + [ind + l for l in post] + ['    }', '}', '']
         meta['vec'] = {'symbol': name + '_vec', 'block': BLOCK_THREADS, 'items': groups, 'lanes': L,
                        'aligned': sorted(aligned_tensors)}
+    # ---- transposed reads staged through shared memory
+    tile_src, tile_meta = _emit_tile(kernel, info, name, params, widx_t)
+    if tile_src is not None:
+        src += tile_src
+        meta['tile'] = tile_meta
     # ---- cooperative reduction loop
     red = patterns.match_reduce(kernel, info)
     if red is not None:

@@ -78,6 +78,10 @@ class KernelPlan(object):
                 for kind, idx in m['aligned']:
                     aligns[idx if kind == 'in' else n_in + idx] = 16
             return [self._make(device, m['symbol'], grid, block, all_in, all_out, aligns)]
+        if which == 'tile':
+            m = meta['tile']
+            grid = max(1, min(m['tiles'], sms * (2048 // m['block'])))
+            return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
         if which == 'red':
             m = meta['red']
             blocks = (m['items'] + m['workers_per_block'] - 1) // m['workers_per_block']
@@ -135,6 +139,8 @@ class KernelPlan(object):
             return 'scanu'
         if meta.get('red'):
             return 'red'
+        if meta.get('tile') and os.environ.get('OVL_TILE_MODE') != 'off':
+            return 'tile'
         if meta.get('vec'):
             ok = True
             for kind, idx in meta['vec']['aligned']:

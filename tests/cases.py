@@ -147,7 +147,24 @@ def user_ops(ns):
         out[pos] = accum * scale[pos[1]]
         return out
 
-    ops = types.SimpleNamespace(shift_cyclic=shift_cyclic, absolute=absolute, halfplus=halfplus, ew_exp=ew_exp,
+    @ovl.operator()
+    def transpose(a):
+        # the operand is read along the workgroup's first axis: neighbouring workers are a row apart in memory
+        out = ovl.output([a.shape[1], a.shape[0]], a.dtype)
+        pos = ovl.position_in(out.shape)
+        out[pos] = a[pos[1], pos[0]]
+        return out
+
+    @ovl.operator()
+    def transpose_axpy(a, b, alpha=None):
+        # b and the output share the layout; a comes in transposed
+        out = ovl.output_like(b)
+        pos = ovl.position_in(b.shape)
+        out[pos] = a[pos[1], pos[0]] * alpha + b[pos]
+        return out
+
+    ops = types.SimpleNamespace(transpose=transpose, transpose_axpy=transpose_axpy,
+                                shift_cyclic=shift_cyclic, absolute=absolute, halfplus=halfplus, ew_exp=ew_exp,
                                 dot=dot, matvec=matvec, rowprod_scaled=rowprod_scaled,
                                 ew_tanh=ew_tanh, ew_add=ew_add, ew_mul=ew_mul, ew_addc=ew_addc, ew_mulc=ew_mulc,
                                 where_greater=where_greater)

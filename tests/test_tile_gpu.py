@@ -1,0 +1,114 @@
+"""Operands read along another axis than the innermost one of the workgroup (transposes and their fusions):
+the `_tile` kernel stages them through shared memory, 32 x 32 workers at a time.  Results must equal the oracle's
+bit for bit (data movement and exactly rounded arithmetic only)."""
+import numpy as np
+import pytest
+
+import cases
+from helpers import DRYRUN, assert_exact
+
+pytestmark = pytest.mark.gpu
+
+
+def _ops(ovl):
+    @ovl.operator()
+    def batched_transpose(a):
+        out = ovl.output([a.shape[0], a.shape[2], a.shape[1]], a.dtype)
+        pos = ovl.position_in(out.shape)
+        out[pos] = a[pos[0], pos[2], pos[1]]
+        return out
+
+    @ovl.operator()
+    def symmetrise(a):
+        # the same operand both ways, and a branch on the transposed value
+        out = ovl.output_like(a)
+        pos = ovl.position_in(a.shape)
+        mirrored = a[pos[1], pos[0]]
+        with ovl.if_(mirrored > a[pos]):
+            out[pos] = mirrored
+        with ovl.else_():
+            out[pos] = a[pos] - mirrored
+        return out
+
+    @ovl.operator()
+    def outer_to_inner(a):
+        # [n, rows, cols] -> [rows, cols, n]: the operand is contiguous along the output's middle axis
+        out = ovl.output([a.shape[1], a.shape[2], a.shape[0]], a.dtype)
+        pos = ovl.position_in(out.shape)
+        out[pos] = a[pos[2], pos[0], pos[1]]
+        return out
+
+    return batched_transpose, symmetrise, outer_to_inner
+
+
+_cache = {}
+
+
+def ops(ns):
+    if id(ns.ovl) not in _cache:
+        _cache[id(ns.ovl)] = _ops(ns.ovl)
+    return _cache[id(ns.ovl)]
+
+
+def _check(ns, outs, expect_tile=True):
+    from opveclib_b200 import runtime
+    from oracle import runner
+    got = ns.ovl.evaluate(outs)
+    prog, _ = runtime.compile_outputs(outs)
+    tiled = [p for p in prog.plans if p.meta.get('tile')]
+    assert bool(tiled) == expect_tile
+    if DRYRUN:
+        return
+    assert all(p.last_variant == 'tile' for p in tiled)
+    want = runner.evaluate(outs)
+    if len(outs) == 1:
+        got, want = [got], [want]
+    for g, w in zip(got, want):
+        assert_exact(np.asarray(g), w, 'tile kernel')
+
+
+@pytest.mark.parametrize('shape,dtype', [((64, 96), 'float32'), ((100, 37), 'float32'), ((33, 1000), 'float64'),
+                                         ((257, 129), 'int16'), ((1024, 2048), 'float32'), ((32, 32), 'uint8')])
+def test_transpose(shape, dtype):
+    ns = cases.impl()
+    transpose = cases.user_ops(ns).transpose
+    rs = np.random.RandomState(shape[0])
+    x = (rs.uniform(-4, 4, shape) if dtype.startswith('float') else rs.randint(0, 100, shape)).astype(dtype)
+    out = transpose(x)
+    _check(ns, [out])
+    if not DRYRUN:
+        assert_exact(np.asarray(ns.ovl.evaluate([out])), np.ascontiguousarray(x.T), 'against numpy')
+
+
+def test_transposed_operand_fused_with_a_straight_one():
+    ns = cases.impl()
+    _, symmetrise, _ = ops(ns)
+    transpose_axpy = cases.user_ops(ns).transpose_axpy
+    rs = np.random.RandomState(5)
+    a = rs.uniform(-1, 1, (300, 200)).astype(np.float32)
+    b = rs.uniform(-1, 1, (200, 300)).astype(np.float32)
+    _check(ns, [transpose_axpy(a, b, alpha=0.5)])
+    sq = rs.uniform(-1, 1, (150, 150)).astype(np.float32)
+    _check(ns, [symmetrise(sq)])
+    # the staged kernel after fusion with element-wise neighbours
+    u = cases.user_ops(ns)
+    _check(ns, [u.ew_mulc(transpose_axpy(u.ew_addc(a, c=1.0), b, alpha=2.0), c=0.25)])
+
+
+def test_rank_three_tiles_over_the_right_axes():
+    ns = cases.impl()
+    batched_transpose, _, outer_to_inner = ops(ns)
+    rs = np.random.RandomState(6)
+    x = rs.uniform(-1, 1, (3, 70, 45)).astype(np.float32)
+    _check(ns, [batched_transpose(x)])
+    y = rs.randint(-50, 50, (40, 5, 64)).astype(np.int32)
+    _check(ns, [outer_to_inner(y)])
+
+
+def test_small_or_straight_kernels_are_left_alone():
+    ns = cases.impl()
+    transpose = cases.user_ops(ns).transpose
+    x = np.arange(6 * 8, dtype=np.float32).reshape(6, 8)
+    _check(ns, [transpose(x)], expect_tile=False)        # narrower than a tile
+    u = cases.user_ops(ns)
+    _check(ns, [u.ew_mulc(np.ones((64, 64), np.float32), c=2.0)], expect_tile=False)
