@@ -21,6 +21,7 @@ Two entry points are generated per kernel:
 Scans recognised by :mod:`opveclib_b200.patterns` use the cooperative scan template instead.
 """
 import math
+import os
 
 from . import expr as E
 from .access import analyze
@@ -40,7 +41,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv32'
+TEMPLATE_VERSION = 'tv36'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -54,7 +55,8 @@ RING_MAX_GRID = 256
 # must match kColBlock / kColRows of csrc/templates/ovl_colscan.cuh
 COL_BLOCK = 256
 COL_ROWS = 64
-TILE_EDGE = 32                # staged tiles are TILE_EDGE x TILE_EDGE workers
+TILE_EDGE = 32                # smallest extent of the two tiled axes for which accesses are staged
+TILE_WIDE = 64                # tile edge along an axis that is at least this long (32 otherwise)
 TILE_SMEM_LIMIT = 40 * 1024   # bytes of shared memory the staged tiles of one kernel may take
 # reduction loops: threads that share one worker's loop - a warp, or a whole block when there are too few workers
 # to fill the device with warps and the loop is long enough to feed a block
@@ -346,43 +348,75 @@ def plan_vectorisation(kernel, info=None):
     return plan
 
 
+def _tile_edges(shape, axis):
+    """Tile extents along the staged axis and along the innermost axis."""
+    return (TILE_WIDE if shape[axis] >= TILE_WIDE else TILE_EDGE,
+            TILE_WIDE if shape[-1] >= TILE_WIDE else TILE_EDGE)
+
+
 def plan_tiling(kernel, info):
-    """Reads that walk memory along another workgroup axis than the innermost one (a transposed operand:
-    ``out[i, j] = f(a[j, i], ...)``).  Neighbouring workers of such a read are a whole stride apart, so a warp
-    touches 32 sectors for 32 values.  Returns (axis, slots) when some input reads have coefficient 1 on workgroup
-    axis ``axis`` and a larger stride on the innermost axis; slots = [(tensor node, form, [read nodes])].  These reads
-    are staged through shared memory by tiles of TILE_EDGE x TILE_EDGE workers over (axis, innermost axis)."""
+    """Accesses that walk memory along another workgroup axis than the innermost one (a transposed operand,
+    ``out[i, j] = f(a[j, i], ...)``, or a transposed result, ``out[j, i] = f(a[i, j], ...)``).  Neighbouring
+    workers of such an access are a whole stride apart, so a warp touches 32 sectors for 32 values.  Returns
+    (axis, read slots, write slots) when some accesses have coefficient 1 on workgroup axis ``axis`` and a
+    larger stride on the innermost axis; read slots = [(tensor node, form, [read nodes])], write slots =
+    [(tensor node, form, assign node)].  These accesses are staged through shared memory by tiles of
+    up to TILE_WIDE x TILE_WIDE workers over (axis, innermost axis).  Only unconditional accesses outside loops whose
+    address is provably inside the tensor for every worker qualify; a staged write must be the only statement
+    that writes its tensor."""
     shape = kernel.workgroup_shape
     rank = len(shape)
     last = rank - 1
     if rank < 2 or shape[last] < TILE_EDGE:
         return None
-    per_axis = {}
+    writers = {}
+    for acc in info.accesses:
+        if acc.is_write:
+            writers[id(acc.tensor)] = writers.get(id(acc.tensor), 0) + 1
+    reads, writes = {}, {}
     for acc in info.accesses:
         f = acc.form
-        if acc.is_write or f is None or f.mod is not None or acc.loop_depth > 0 or acc.tensor.kind != 'input':
+        if f is None or f.mod is not None or acc.loop_depth > 0:
             continue
         if any(sym[0] == 'l' for sym in f.coefs):
             continue
         lo, hi = f.bounds(info.ranges)
         if lo < 0 or hi >= acc.tensor.size:
-            continue            # (staging loads unconditionally: every worker's address must be valid)
+            continue            # (staging moves whole tiles: every worker's address must be valid)
         if abs(f.coef(('p', last))) < 2:
+            continue
+        if acc.is_write:
+            if acc.tensor.kind != 'output' or acc.cond_depth > 0 or writers[id(acc.tensor)] != 1:
+                continue
+            if not _is_injective(f, info.ranges):
+                continue
+        elif acc.tensor.kind != 'input':
             continue
         for d in range(last):
             if shape[d] >= TILE_EDGE and f.coef(('p', d)) == 1:
-                slot = per_axis.setdefault(d, {}).setdefault((id(acc.tensor), f.key()), [acc.tensor, f, []])
-                slot[2].append(acc.node)
-    if not per_axis:
+                if acc.is_write:
+                    writes.setdefault(d, []).append((acc.tensor, f, acc.node))
+                else:
+                    slot = reads.setdefault(d, {}).setdefault((id(acc.tensor), f.key()), [acc.tensor, f, []])
+                    slot[2].append(acc.node)
+    if not reads and not writes:
         return None
-    axis = max(sorted(per_axis), key=lambda d: len(per_axis[d]))
-    slots, used = [], 0
-    for tensor, form, nodes in per_axis[axis].values():
-        need = TILE_EDGE * (TILE_EDGE + 1) * tensor.dtype.itemsize
+    axis = max(sorted(set(reads) | set(writes)), key=lambda d: len(reads.get(d, {})) + len(writes.get(d, [])))
+    read_slots, write_slots, used = [], [], 0
+    tile_t, tile_l = _tile_edges(shape, axis)
+    for tensor, form, node in writes.get(axis, []):
+        need = tile_l * (tile_t + 1) * tensor.dtype.itemsize
         if used + need <= TILE_SMEM_LIMIT:
-            slots.append((tensor, form, nodes))
+            write_slots.append((tensor, form, node))
             used += need
-    return axis, slots
+    for tensor, form, nodes in reads.get(axis, {}).values():
+        need = tile_l * (tile_t + 1) * tensor.dtype.itemsize
+        if used + need <= TILE_SMEM_LIMIT:
+            read_slots.append((tensor, form, nodes))
+            used += need
+    if not read_slots and not write_slots:
+        return None
+    return axis, read_slots, write_slots
 
 
 def _address_expr(form, shape):
@@ -396,68 +430,91 @@ def _address_expr(form, shape):
 
 
 def _emit_tile(kernel, info, name, params, widx_t):
-    """The ``_tile`` kernel: (source lines, metadata) or (None, None) when the kernel has no transposed reads."""
+    """The ``_tile`` kernel: (source lines, metadata) or (None, None) when the kernel has no transposed accesses.
+
+    Per tile of up to 64 x 64 workers over (axis, innermost axis): threads that walk the axis along which the
+    operand is contiguous bring the staged operands into shared memory; the body runs with consecutive threads on
+    consecutive workers of the innermost axis and takes the staged values from shared memory (transposed, rows
+    padded by one element against bank conflicts); staged results go through shared memory the other way round."""
     tiling = plan_tiling(kernel, info)
     if tiling is None:
         return None, None
     shape = kernel.workgroup_shape
-    src = []
-    axis, slots = tiling
+    axis, slots, wslots = tiling
     rank = len(shape)
     last = rank - 1
-    edge = TILE_EDGE
-    n_t, n_l = (shape[axis] + edge - 1) // edge, (shape[last] + edge - 1) // edge
+    tt, tl = _tile_edges(shape, axis)
+    n_t, n_l = (shape[axis] + tt - 1) // tt, (shape[last] + tl - 1) // tl
     n_tiles = n_t * n_l
     for d in range(rank):
         if d not in (axis, last):
             n_tiles *= shape[d]
-    read_subst = {}
-    decls, stage = [], []
+    pitch = '[' + str(tl) + '][' + str(tt + 1) + ']'
+    l_rows, t_rows = BLOCK_THREADS // tt, BLOCK_THREADS // tl      # rows covered at once when moving / computing
+    read_subst, write_subst = {}, {}
+    decls, stage, unstage = [], [], []
     for si, (tensor, form, nodes) in enumerate(slots):
-        decls.append('    __shared__ ' + ctype(tensor.dtype) + ' ovl_tile' + str(si) + '[' + str(edge) + '][' + str(edge + 1) + '];')
-        stage.append('ovl_tile' + str(si) + '[ovl_ty + ovl_r][ovl_tx] = in' + str(tensor.attr['io_index']) + '[' +
+        decls.append('    __shared__ ' + ctype(tensor.dtype) + ' ovl_tile' + str(si) + pitch + ';')
+        stage.append('ovl_tile' + str(si) + '[ovl_ml + ovl_r][ovl_mt] = in' + str(tensor.attr['io_index']) + '[' +
                      _address_expr(form, shape) + '];')
         for n in nodes:
-            read_subst[id(n)] = 'ovl_tile' + str(si) + '[ovl_tx][ovl_ty + ovl_r]'
+            read_subst[id(n)] = 'ovl_tile' + str(si) + '[ovl_cl][ovl_ct + ovl_r]'
+    for si, (tensor, form, node) in enumerate(wslots):
+        decls.append('    __shared__ ' + ctype(tensor.dtype) + ' ovl_wtile' + str(si) + pitch + ';')
+        write_subst[id(node)] = 'ovl_wtile' + str(si) + '[ovl_cl][ovl_ct + ovl_r] = %s;'
+        unstage.append('out' + str(tensor.attr['io_index']) + '[' + _address_expr(form, shape) + '] = ovl_wtile' + str(si) +
+                       '[ovl_ml + ovl_r][ovl_mt];')
     decode = ['uint64_t ovl_rem = ovl_t;',
-              'const uint32_t ovl_l0 = (uint32_t)(ovl_rem % ' + str(n_l) + 'ull) * ' + str(edge) + 'u; ovl_rem /= ' + str(n_l) + 'ull;',
-              'const uint32_t ovl_t0 = (uint32_t)(ovl_rem % ' + str(n_t) + 'ull) * ' + str(edge) + 'u; ovl_rem /= ' + str(n_t) + 'ull;']
+              'const uint32_t ovl_l0 = (uint32_t)(ovl_rem % ' + str(n_l) + 'ull) * ' + str(tl) + 'u; ovl_rem /= ' + str(n_l) + 'ull;',
+              'const uint32_t ovl_t0 = (uint32_t)(ovl_rem % ' + str(n_t) + 'ull) * ' + str(tt) + 'u; ovl_rem /= ' + str(n_t) + 'ull;']
     for d in range(rank - 1, -1, -1):
         if d not in (axis, last):
             decode.append('const uint32_t ovl_q' + str(d) + ' = (uint32_t)(ovl_rem % ' + str(shape[d]) + 'ull); ovl_rem /= ' +
                           str(shape[d]) + 'ull;')
 
-    def coords(t_expr, l_expr, prefix):
+    def coords(t_expr, l_expr, var):
         out = []
         for d in range(rank):
             v = t_expr if d == axis else (l_expr if d == last else 'ovl_q' + str(d))
-            out.append('const uint32_t ' + prefix + str(d) + ' = ' + v + ';')
+            out.append('const uint32_t ' + var + str(d) + ' = ' + v + ';')
         return out
+
+    def inside(var):
+        return var + str(axis) + ' < ' + str(shape[axis]) + 'u && ' + var + str(last) + ' < ' + str(shape[last]) + 'u'
+
+    def moving(statements, comment):
+        # consecutive threads walk the staged axis: whole contiguous segments of the tensor per row of the tile
+        return [i2 + comment, i2 + '#pragma unroll',
+                i2 + 'for (uint32_t ovl_r = 0; ovl_r < ' + str(tl) + 'u; ovl_r += ' + str(l_rows) + 'u) {'] + \
+            [i3 + l for l in coords('ovl_t0 + ovl_mt', 'ovl_l0 + ovl_ml + ovl_r', 'p')] + \
+            [i3 + 'if (' + inside('p') + ') {'] + [i4 + l for l in statements] + [i3 + '}', i2 + '}', i2 + '__syncthreads();']
+
     strides = _strides(shape)
     widx = ' + '.join('(' + widx_t + ')w' + str(d) + ' * ' + str(strides[d]) + 'u' for d in range(rank))
     pos_text = 'const uint32_t position[' + str(rank) + '] = {' + ', '.join('w' + str(d) for d in range(rank)) + '};'
-    em = BodyEmitter(kernel, 4, read_subst, position_text=pos_text)
+    em = BodyEmitter(kernel, 4, read_subst, write_subst, position_text=pos_text)
     em.block(kernel.body)
-    i2, i3, i4 = '        ', '            ', '                '
-    src += ['extern "C" __global__ void __launch_bounds__(' + str(BLOCK_THREADS) + ') ' + name + '_tile(' + params + ') {'] + \
+    i1, i2, i3, i4 = '    ', '        ', '            ', '                '
+    src = ['extern "C" __global__ void __launch_bounds__(' + str(BLOCK_THREADS) + ') ' + name + '_tile(' + params + ') {'] + \
         decls + \
-        ['    const uint32_t ovl_tx = threadIdx.x & 31u, ovl_ty = threadIdx.x >> 5;',
-         '    for (uint64_t ovl_t = blockIdx.x; ovl_t < ' + str(n_tiles) + 'ull; ovl_t += gridDim.x) {'] + \
-        [i2 + l for l in decode] + \
-        [i2 + '// stage: consecutive threads walk the axis along which the operand is contiguous',
-         i2 + '#pragma unroll',
-         i2 + 'for (uint32_t ovl_r = 0; ovl_r < ' + str(edge) + 'u; ovl_r += ' + str(BLOCK_THREADS // 32) + 'u) {'] + \
-        [i3 + l for l in coords('ovl_t0 + ovl_tx', 'ovl_l0 + ovl_ty + ovl_r', 'p')] + \
-        [i3 + 'if (p' + str(axis) + ' < ' + str(shape[axis]) + 'u && p' + str(last) + ' < ' + str(shape[last]) + 'u) {'] + \
-        [i4 + l for l in stage] + [i3 + '}', i2 + '}', i2 + '__syncthreads();',
-         i2 + '// compute: consecutive threads are consecutive workers of the innermost axis',
-         i2 + '#pragma unroll',
-         i2 + 'for (uint32_t ovl_r = 0; ovl_r < ' + str(edge) + 'u; ovl_r += ' + str(BLOCK_THREADS // 32) + 'u) {'] + \
-        [i3 + l for l in coords('ovl_t0 + ovl_ty + ovl_r', 'ovl_l0 + ovl_tx', 'w')] + \
-        [i3 + 'if (w' + str(axis) + ' < ' + str(shape[axis]) + 'u && w' + str(last) + ' < ' + str(shape[last]) + 'u) {',
+        [i1 + '// thread coordinates inside a tile when moving data (mt fastest) and when computing (cl fastest)',
+         i1 + 'const uint32_t ovl_mt = threadIdx.x % ' + str(tt) + 'u, ovl_ml = threadIdx.x / ' + str(tt) + 'u;',
+         i1 + 'const uint32_t ovl_cl = threadIdx.x % ' + str(tl) + 'u, ovl_ct = threadIdx.x / ' + str(tl) + 'u;',
+         i1 + 'for (uint64_t ovl_t = blockIdx.x; ovl_t < ' + str(n_tiles) + 'ull; ovl_t += gridDim.x) {'] + \
+        [i2 + l for l in decode]
+    if slots:
+        src += moving(stage, '// stage the operands read along axis ' + str(axis))
+    src += [i2 + '#pragma unroll',
+            i2 + 'for (uint32_t ovl_r = 0; ovl_r < ' + str(tt) + 'u; ovl_r += ' + str(t_rows) + 'u) {'] + \
+        [i3 + l for l in coords('ovl_t0 + ovl_ct + ovl_r', 'ovl_l0 + ovl_cl', 'w')] + \
+        [i3 + 'if (' + inside('w') + ') {',
          i4 + 'const ' + widx_t + ' worker_index = ' + widx + '; (void)worker_index;'] + \
-        em.lines + [i3 + '}', i2 + '}', i2 + '__syncthreads();', '    }', '}', '']
-    return src, {'symbol': name + '_tile', 'block': BLOCK_THREADS, 'tiles': n_tiles, 'axis': axis, 'staged': len(slots)}
+        em.lines + [i3 + '}', i2 + '}', i2 + '__syncthreads();']
+    if wslots:
+        src += moving(unstage, '// write the results that are contiguous along axis ' + str(axis))
+    src += [i1 + '}', '}', '']
+    return src, {'symbol': name + '_tile', 'block': BLOCK_THREADS, 'tiles': n_tiles, 'axis': axis, 'staged': len(slots),
+                 'staged_writes': len(wslots)}
 
 
 def emit_cuda(kernel, name):

@@ -38,7 +38,26 @@ def _ops(ovl):
         out[pos] = a[pos[2], pos[0], pos[1]]
         return out
 
-    return batched_transpose, symmetrise, outer_to_inner
+    @ovl.operator()
+    def scatter_transpose(a, scale=None):
+        # the workgroup follows the operand; the result is written transposed
+        out = ovl.output([a.shape[1], a.shape[0]], a.dtype)
+        pos = ovl.position_in(a.shape)
+        out[pos[1], pos[0]] = a[pos] * scale
+        return out
+
+    @ovl.operator()
+    def both_ways(a, b):
+        # b is read and the first result written along the workgroup's first axis; the second result goes straight
+        flipped = ovl.output([a.shape[1], a.shape[0]], a.dtype)
+        straight = ovl.output_like(a)
+        pos = ovl.position_in(a.shape)
+        total = a[pos] + b[pos[1], pos[0]]
+        flipped[pos[1], pos[0]] = total
+        straight[pos] = total - a[pos]
+        return flipped, straight
+
+    return batched_transpose, symmetrise, outer_to_inner, scatter_transpose, both_ways
 
 
 _cache = {}
@@ -82,7 +101,7 @@ def test_transpose(shape, dtype):
 
 def test_transposed_operand_fused_with_a_straight_one():
     ns = cases.impl()
-    _, symmetrise, _ = ops(ns)
+    _, symmetrise, _, _, _ = ops(ns)
     transpose_axpy = cases.user_ops(ns).transpose_axpy
     rs = np.random.RandomState(5)
     a = rs.uniform(-1, 1, (300, 200)).astype(np.float32)
@@ -97,12 +116,27 @@ def test_transposed_operand_fused_with_a_straight_one():
 
 def test_rank_three_tiles_over_the_right_axes():
     ns = cases.impl()
-    batched_transpose, _, outer_to_inner = ops(ns)
+    batched_transpose, _, outer_to_inner, _, _ = ops(ns)
     rs = np.random.RandomState(6)
     x = rs.uniform(-1, 1, (3, 70, 45)).astype(np.float32)
     _check(ns, [batched_transpose(x)])
     y = rs.randint(-50, 50, (40, 5, 64)).astype(np.int32)
     _check(ns, [outer_to_inner(y)])
+
+
+def test_results_written_along_another_axis():
+    ns = cases.impl()
+    _, _, _, scatter_transpose, both_ways = ops(ns)
+    rs = np.random.RandomState(7)
+    for shape in ((64, 64), (130, 75), (40, 1000)):
+        a = rs.uniform(-1, 1, shape).astype(np.float32)
+        _check(ns, [scatter_transpose(a, scale=2.0)])
+        if not DRYRUN:
+            assert_exact(np.asarray(ns.ovl.evaluate([scatter_transpose(a, scale=2.0)])), np.ascontiguousarray(a.T * 2), 'numpy')
+    a = rs.randint(-9, 9, (96, 200)).astype(np.int32)
+    b = rs.randint(-9, 9, (200, 96)).astype(np.int32)
+    op = both_ways(a, b)
+    _check(ns, [op[0], op[1]])
 
 
 def test_small_or_straight_kernels_are_left_alone():
