@@ -13,6 +13,9 @@ opveclib/examples/test_accumulate.py:40-41):
 
 Per element this moves 4 bytes in step 1 and 8 in step 3: a shard's total is only known after all of it has been
 read, so every shard but the first is read twice - 12 bytes per element against the 8 of the one-GPU scan.
+
+A reduction along the sharded axis exchanges partial results the same way (``ShardedReduce``): every rank reduces
+its shard, the partials are all-gathered into local memory and combined in rank order on every rank.
 """
 import ctypes
 
@@ -118,6 +121,70 @@ class ShardedScan(object):
                        'reading scan status')
         if status.value != 0:
             raise launcher.OvlError(status.value, 'sharded scan')
+
+
+def combine_partials(partials, op='add'):
+    """Combine per-rank partial results (first axis = rank) in rank order.  Works on numpy arrays and torch tensors;
+    every rank calls it on the same gathered data and therefore gets bit-identical results."""
+    if op not in ('add', 'mul'):
+        raise ValueError("op must be 'add' or 'mul'")
+    acc = partials[0]
+    for r in range(1, len(partials)):
+        acc = acc + partials[r] if op == 'add' else acc * partials[r]
+    return acc
+
+
+class ShardedReduce(object):
+    """A reduction whose reduced axis is split over the ranks of ``group``: every rank reduces its own shard, the
+    partial results are all-gathered into local memory and combined in rank order (the "partial exchange"; the
+    reference has no multi-GPU support).  Two forms:
+
+    ``total(x)``        sum / product of all elements of a contiguous fp32 tensor shard in fp64
+                        (``ovl_reduce_f32``: one streaming read, fixed combination order), then the exchange;
+    ``combine(partial)`` the exchange alone, for a partial result of any shape that an operator graph produced
+                        from the rank's shard (a dot product over a sharded vector, column sums over sharded rows).
+    Both return the same tensor on every rank."""
+
+    def __init__(self, op='add', group=None, device=None):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist = torch, dist
+        self.op = op
+        self.code = _op_code(op)
+        self.group = group
+        self.distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+        self.device = torch.device('cuda', torch.cuda.current_device()) if device is None else torch.device(device)
+        self.lib = launcher.library() if self.device.type == 'cuda' else None
+        self._scratch = None
+        self.partial = torch.zeros(1, dtype=torch.float64, device=self.device)
+        self.launches = 0
+
+    def combine(self, partial):
+        """All-gather ``partial`` (same shape and dtype on every rank) and combine the copies in rank order."""
+        if self.world == 1:
+            return partial
+        torch = self.torch
+        flat = partial.contiguous().view(-1)
+        gathered = torch.empty(self.world * flat.numel(), dtype=partial.dtype, device=partial.device)
+        self.dist.all_gather_into_tensor(gathered, flat, group=self.group)
+        return combine_partials(gathered.view((self.world,) + tuple(partial.shape)), self.op)
+
+    def total(self, x):
+        """fp64 sum / product over all ranks' shards of a contiguous float32 CUDA tensor; a [1] float64 tensor."""
+        torch = self.torch
+        if x.dtype != torch.float32 or not x.is_contiguous() or not x.is_cuda:
+            raise ValueError('expected a contiguous float32 CUDA tensor')
+        n = x.numel()
+        need = int(self.lib.ovl_reduce_f32_scratch_bytes(n))
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, dtype=torch.uint8, device=self.device)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        launcher.check(self.lib.ovl_reduce_f32(self.code, x.data_ptr(), n, self.partial.data_ptr(),
+                                               self._scratch.data_ptr(), self._scratch.numel(), stream), 'shard total')
+        self.launches += 1
+        return self.combine(self.partial)
 
 
 class HostScan(object):

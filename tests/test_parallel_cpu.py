@@ -87,3 +87,60 @@ def test_carry_exchange_with_two_gloo_ranks(op):
     want = (np.cumsum(x64) if op == 'add' else np.cumprod(x64)).astype(np.float32)
     got = np.concatenate([parts[r] for r in range(world)])
     np.testing.assert_allclose(got, want, rtol=2e-7, atol=0)
+
+
+def _gloo_reduce_rank(rank, world, port, queue):
+    import torch
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        rs = np.random.RandomState(9)
+        a, b = rs.normal(0, 1, 5001), rs.normal(0, 1, 5001)
+        mine_a, mine_b = (parallel.shard_leading_axis(v, rank, world) for v in (a, b))
+        red = parallel.ShardedReduce('add', device='cpu')
+        # a dot product over a sharded vector: the rank's partial, then the exchange
+        dot = red.combine(torch.tensor([np.dot(mine_a, mine_b)], dtype=torch.float64))
+        # column sums over sharded rows, and a product
+        m = rs.uniform(0.9, 1.1, (40, 6))
+        cols = red.combine(torch.tensor(parallel.shard_leading_axis(m, rank, world).sum(axis=0)))
+        prod = parallel.ShardedReduce('mul', device='cpu').combine(
+            torch.tensor(parallel.shard_leading_axis(m, rank, world).prod(axis=0)))
+        queue.put((rank, dot.numpy(), cols.numpy(), prod.numpy()))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_partial_exchange_of_a_sharded_reduction_with_two_gloo_ranks():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    world, port = 2, _free_port()
+    procs = [ctx.Process(target=_gloo_reduce_rank, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict((r, rest) for r, *rest in (queue.get(timeout=120) for _ in range(world)))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    rs = np.random.RandomState(9)
+    a, b = rs.normal(0, 1, 5001), rs.normal(0, 1, 5001)
+    m = rs.uniform(0.9, 1.1, (40, 6))
+    for r in range(world):
+        dot, cols, prod = got[r]
+        np.testing.assert_allclose(dot, [np.dot(a, b)], rtol=1e-12)
+        np.testing.assert_allclose(cols, m.sum(axis=0), rtol=1e-13)
+        np.testing.assert_allclose(prod, m.prod(axis=0), rtol=1e-12)
+    # every rank holds the same bits
+    for x, y in zip(got[0], got[1]):
+        assert np.array_equal(x, y)
+
+
+def test_combine_partials_is_rank_ordered():
+    parts = np.array([[1e16, 1.0], [1.0, 2.0], [-1e16, 3.0]])
+    assert parallel.combine_partials(parts, 'add').tolist() == [(1e16 + 1.0) - 1e16, 6.0]
+    assert parallel.combine_partials(parts[:, 1:], 'mul').tolist() == [6.0]
+    with pytest.raises(ValueError):
+        parallel.combine_partials(parts, 'max')
