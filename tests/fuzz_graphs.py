@@ -1,5 +1,6 @@
 """Random operator graphs for the fuzz tests: element-wise arithmetic with exact results (no libm), comparisons,
-branches, broadcast-free binary operators, cyclic and affine index shifts, stacking and unstacking along a new
+branches, broadcast-free binary operators, cyclic and affine index shifts, axis swaps on the reading and on the writing
+side, strided gathers, clamped stencils, integer scans and reduction loops, stacking and unstacking along a new
 axis.  Every graph is a pure function of its seed."""
 import numpy as np
 
@@ -124,7 +125,27 @@ def _ops(ovl):
         out[pos] = a[left] - a[pos] + a[right]
         return out
 
-    return dict(gather_stride=gather_stride, neighbours=neighbours, row_total=row_total, binary=binary, affine=affine, select=select, magnitude=magnitude, rotate_last=rotate_last,
+    @ovl.operator()
+    def swap_last_two(a):
+        # reads its operand with the last two axes exchanged (square trailing axes keep the shape)
+        out = ovl.output_like(a)
+        pos = ovl.position_in(a.shape)
+        index = [pos[d] for d in range(a.rank)]
+        index[-1], index[-2] = pos[a.rank - 2], pos[a.rank - 1]
+        out[pos] = a[index]
+        return out
+
+    @ovl.operator()
+    def scatter_last_two(a):
+        # writes its result with the last two axes exchanged
+        out = ovl.output_like(a)
+        pos = ovl.position_in(a.shape)
+        index = [pos[d] for d in range(a.rank)]
+        index[-1], index[-2] = pos[a.rank - 2], pos[a.rank - 1]
+        out[index] = a[pos] + a[pos]
+        return out
+
+    return dict(swap_last_two=swap_last_two, scatter_last_two=scatter_last_two, gather_stride=gather_stride, neighbours=neighbours, row_total=row_total, binary=binary, affine=affine, select=select, magnitude=magnitude, rotate_last=rotate_last,
                 mirror_first=mirror_first, stack_pair=stack_pair, unstack_pair=unstack_pair)
 
 
@@ -140,6 +161,9 @@ def build(ns, seed):
     rs = np.random.RandomState(seed)
     rank = rs.randint(1, 4)
     shape = [int(rs.choice([1, 2, 3, 4, 5, 7, 8, 12, 16, 31, 33, 64, 100])) for _ in range(rank)]
+    square = rank >= 2 and rs.rand() < 0.5
+    if square:
+        shape[-2] = shape[-1]
     dtype = rs.choice(['float32', 'float32', 'int32', 'float64', 'int16'])
     n_leaves = rs.randint(1, 4)
     if dtype.startswith('float'):
@@ -150,6 +174,8 @@ def build(ns, seed):
     exact_sums = not dtype.startswith('float')      # integer sums do not depend on the order of evaluation
     kinds = ['binary', 'binary', 'binary', 'affine', 'select', 'magnitude', 'rotate', 'mirror', 'stack', 'gather',
              'neighbours']
+    if square:
+        kinds += ['swap', 'swap', 'scatter']
     if exact_sums:
         # no products of products (signed overflow), but scans and reduction loops
         kinds = [k for k in kinds if k != 'magnitude'] + ['cumsum', 'row_total']
@@ -174,6 +200,10 @@ def build(ns, seed):
             new = ns.cumsum(pick(), axis=int(rs.randint(rank)))
         elif kind == 'row_total':
             new = ops['row_total'](pick())
+        elif kind == 'swap':
+            new = ops['swap_last_two'](pick())
+        elif kind == 'scatter':
+            new = ops['scatter_last_two'](pick())
         elif kind == 'gather':
             new = ops['gather_stride'](pick(), k=int(rs.randint(2, 4)))
         elif kind == 'neighbours':
