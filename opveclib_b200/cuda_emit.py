@@ -41,7 +41,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv36'
+TEMPLATE_VERSION = 'tv37'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -348,8 +348,10 @@ def plan_vectorisation(kernel, info=None):
     return plan
 
 
-def _tile_edges(shape, axis):
+def _tile_edges(shape, axis, wide):
     """Tile extents along the staged axis and along the innermost axis."""
+    if not wide:
+        return TILE_EDGE, TILE_EDGE
     return (TILE_WIDE if shape[axis] >= TILE_WIDE else TILE_EDGE,
             TILE_WIDE if shape[-1] >= TILE_WIDE else TILE_EDGE)
 
@@ -358,7 +360,7 @@ def plan_tiling(kernel, info):
     """Accesses that walk memory along another workgroup axis than the innermost one (a transposed operand,
     ``out[i, j] = f(a[j, i], ...)``, or a transposed result, ``out[j, i] = f(a[i, j], ...)``).  Neighbouring
     workers of such an access are a whole stride apart, so a warp touches 32 sectors for 32 values.  Returns
-    (axis, read slots, write slots) when some accesses have coefficient 1 on workgroup axis ``axis`` and a
+    (axis, read slots, write slots, tile extents) when some accesses have coefficient 1 on workgroup axis ``axis`` and a
     larger stride on the innermost axis; read slots = [(tensor node, form, [read nodes])], write slots =
     [(tensor node, form, assign node)].  These accesses are staged through shared memory by tiles of
     up to TILE_WIDE x TILE_WIDE workers over (axis, innermost axis).  Only unconditional accesses outside loops whose
@@ -402,21 +404,27 @@ def plan_tiling(kernel, info):
     if not reads and not writes:
         return None
     axis = max(sorted(set(reads) | set(writes)), key=lambda d: len(reads.get(d, {})) + len(writes.get(d, [])))
-    read_slots, write_slots, used = [], [], 0
-    tile_t, tile_l = _tile_edges(shape, axis)
-    for tensor, form, node in writes.get(axis, []):
-        need = tile_l * (tile_t + 1) * tensor.dtype.itemsize
-        if used + need <= TILE_SMEM_LIMIT:
-            write_slots.append((tensor, form, node))
-            used += need
-    for tensor, form, nodes in reads.get(axis, {}).values():
-        need = tile_l * (tile_t + 1) * tensor.dtype.itemsize
-        if used + need <= TILE_SMEM_LIMIT:
-            read_slots.append((tensor, form, nodes))
-            used += need
+    wanted_writes = writes.get(axis, [])
+    wanted_reads = list(reads.get(axis, {}).values())
+    # the widest tiles whose staging buffers fit; narrower tiles rather than fewer staged accesses
+    for wide in (True, False):
+        tile_t, tile_l = _tile_edges(shape, axis, wide)
+        read_slots, write_slots, used = [], [], 0
+        for tensor, form, node in wanted_writes:
+            need = tile_l * (tile_t + 1) * tensor.dtype.itemsize
+            if used + need <= TILE_SMEM_LIMIT:
+                write_slots.append((tensor, form, node))
+                used += need
+        for tensor, form, nodes in wanted_reads:
+            need = tile_l * (tile_t + 1) * tensor.dtype.itemsize
+            if used + need <= TILE_SMEM_LIMIT:
+                read_slots.append((tensor, form, nodes))
+                used += need
+        if len(read_slots) + len(write_slots) == len(wanted_reads) + len(wanted_writes):
+            break
     if not read_slots and not write_slots:
         return None
-    return axis, read_slots, write_slots
+    return axis, read_slots, write_slots, tile_t, tile_l
 
 
 def _address_expr(form, shape):
@@ -440,10 +448,9 @@ def _emit_tile(kernel, info, name, params, widx_t):
     if tiling is None:
         return None, None
     shape = kernel.workgroup_shape
-    axis, slots, wslots = tiling
+    axis, slots, wslots, tt, tl = tiling
     rank = len(shape)
     last = rank - 1
-    tt, tl = _tile_edges(shape, axis)
     n_t, n_l = (shape[axis] + tt - 1) // tt, (shape[last] + tl - 1) // tl
     n_tiles = n_t * n_l
     for d in range(rank):

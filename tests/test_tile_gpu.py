@@ -139,6 +139,27 @@ def test_results_written_along_another_axis():
     _check(ns, [op[0], op[1]])
 
 
+def test_many_wide_operands_fall_back_to_narrower_tiles():
+    """Three transposed fp64 operands do not fit in shared memory as 64 x 64 tiles; all three are still staged."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    ovl = ns.ovl
+
+    @ovl.operator()
+    def three_transposed(a, b, c):
+        out = ovl.output([a.shape[1], a.shape[0]], a.dtype)
+        pos = ovl.position_in(out.shape)
+        out[pos] = a[pos[1], pos[0]] * b[pos[1], pos[0]] - c[pos[1], pos[0]]
+        return out
+
+    rs = np.random.RandomState(8)
+    a, b, c = (rs.uniform(-1, 1, (130, 200)) for _ in range(3))
+    op = three_transposed(a, b, c)
+    prog, _ = runtime.compile_outputs([op])
+    assert prog.plans[0].meta['tile']['staged'] == 3
+    _check(ns, [op])
+
+
 def test_small_or_straight_kernels_are_left_alone():
     ns = cases.impl()
     transpose = cases.user_ops(ns).transpose
