@@ -8,12 +8,14 @@ fp32 tensor [8, 2^27] drawn from uniform[-2, 2], rows sharded contiguously over 
 (total work fixed: strong scaling).  One step is one evaluation of the whole operator graph on the rank's rows.
 The other workloads exist for profiling single kernels: `c5` is the scan across shard boundaries, `matvec` a
 per-row reduction loop, `perf_accumulate` the reference's own timing harness (fp64 [10000, 1000] cumsum along axis 0),
-`op_<name>` one operator of the chain on its own.
+`colscan` a column scan far larger than L2, `transpose` / `transpose_axpy` an operand read along the workgroup's
+first axis, `op_<name>` one operator of the chain on its own.
 
 Prints one JSON line (rank 0).  ``value`` is elements/s with inputs resident in HBM, timed with CUDA events on
 the launching stream, maximum over ranks; ``e2e`` is the same work through ``ovl.evaluate`` from pinned host
 arrays and back (host<->device copies inside the timed region); ``roofline`` relates the dominant kernel's
-algorithmic bytes per launch to the measured HBM copy bandwidth; ``cpu_baseline`` times the reference's own
+algorithmic bytes per launch to the measured HBM copy bandwidth (and, as ``same_size_copy_ms``, to a plain device copy
+of the same number of bytes timed the same way - what that peak becomes at the workload's own size); ``cpu_baseline`` times the reference's own
 generated C++ operators (oracle/_ref, else the oracle port) on this machine's host cores over a bounded sample.
 ``--impl reference`` runs only that CPU arm and prints it in the same format.
 """
@@ -449,6 +451,43 @@ def main():
                   'note': 'back-to-back launches without the L2 flush: inputs are L2-resident'}
     clocks = sampler.stop() if rank == 0 else None
     finish()
+    # a plain streaming kernel (torch: dst = 2 * src) that moves the same number of bytes, timed the same way: what the measured peak (a
+    # 2 GiB copy) becomes at this problem's size, where launch and ramp-up are a visible share of the time
+    same_size_copy_ms = None
+    copy_bytes = elements_local * bytes_per_elem // 2
+    if world == 1 and copy_bytes <= (2 << 30):
+        # (an element-wise kernel, not a memcpy node: inside a CUDA graph those may run on a copy engine)
+        src = torch.empty(copy_bytes // 4, dtype=torch.float32, device=device).fill_(1)
+        dst = torch.empty_like(src)
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            torch.mul(src, 2.0, out=dst)
+        side.synchronize()
+        copy_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(copy_graph, stream=side):
+            torch.mul(src, 2.0, out=dst)
+        for _ in range(3):
+            copy_graph.replay()
+        torch.cuda.synchronize()
+        if flush is None:
+            start.record()
+            for _ in range(args.steps):
+                copy_graph.replay()
+            stop.record()
+            stop.synchronize()
+            total = start.elapsed_time(stop)
+        else:
+            total = 0.0
+            for _ in range(args.steps):
+                flush.fill_(1)
+                start.record()
+                copy_graph.replay()
+                stop.record()
+                stop.synchronize()
+                total += start.elapsed_time(stop)
+        same_size_copy_ms = total / args.steps
+        del src, dst
     t = torch.tensor([elapsed_ms], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -525,7 +564,10 @@ def main():
             'effective_hbm_gbs': achieved * world, 'pct_of_8tbs_per_gpu': 100.0 * achieved / NOMINAL_HBM_GBS,
             'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
                          'peak_kind': peak_kind + ' HBM copy bandwidth', 'algorithmic_bytes_per_element': bytes_per_elem,
-                         'traffic': profiled_traffic(workload, elements_local)},
+                         'traffic': profiled_traffic(workload, elements_local),
+                         'same_size_copy_ms': same_size_copy_ms,
+                         'frac_of_same_size_copy': (same_size_copy_ms / (elapsed_ms / args.steps)
+                                                    if same_size_copy_ms else None)},
             'clocks': clocks, 'e2e': e2e, 'gpu_launches': kernels_per_step * args.steps,
         }
         if steady is not None:

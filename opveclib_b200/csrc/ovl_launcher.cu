@@ -340,6 +340,15 @@ __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_f32_kernel(con
     ovl::scan_ring<float, double, Op, 4, HAS_CARRY, MULTI>(in, out, carry, lines, n, scratch, withhold_block);
 }
 
+template <class Op>
+__global__ void __launch_bounds__(ovl::kWarpScanBlock) scan_warp_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                                          uint64_t lines, uint64_t n) {
+    ovl::scan_lines_warp<float, double, Op, 4>(in, out, lines, n);
+}
+
+// from this many lines on (all starting on 16-byte boundaries) a warp scans a whole line by itself
+constexpr uint64_t kWarpScanMinLines = 2048;
+
 // a line of at most kTile elements is one tile; longer lines are cut into tiles of kTile elements (three-pass
 // scan) or kTileLookback elements (single-pass look-back scan)
 constexpr uint64_t kTile = (uint64_t)ovl::kScanBlock * ovl::kScanVpt * 4;
@@ -505,6 +514,14 @@ int finish_scan(const float* in, float* out, uint64_t lines, uint64_t n, const d
 template <class Op>
 int run_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, bool aligned,
              cudaStream_t stream) {
+    if (aligned && !carry && lines >= kWarpScanMinLines && n % 4 == 0 && long_line_mode() == kModeRing) {
+        const uint64_t per_block = ovl::kWarpScanBlock / 32;
+        const uint64_t want = (lines + per_block - 1) / per_block;
+        const uint64_t cap = (uint64_t)sm_count_cached() * (1024 / ovl::kWarpScanBlock);
+        scan_warp_f32_kernel<Op><<<(uint32_t)(want < cap ? want : cap), ovl::kWarpScanBlock, 0, stream>>>(in, out, lines, n);
+        cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? OVL_OK : cuda_fail(e);
+    }
     if (n <= kTile) {
         cudaError_t e = launch_scan_pass<Op>(in, out, lines, n, carry, scratch, aligned, ovl::kScanOneTile, stream);
         return e == cudaSuccess ? OVL_OK : cuda_fail(e);

@@ -476,6 +476,84 @@ __device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uin
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Many lines: one WARP per line, no cooperation between warps at all.
+//
+// When there are thousands of lines, a warp can walk down its line alone: chunks of 32 lanes x kWarpScanVecs vectors
+// (warp-striped, every access a coalesced 128-bit vector), the running prefix of the line carried in a register, the
+// next chunk already requested while the current one is scanned.  No shared memory, no barrier, nothing published:
+// the only waits are a warp's own loads, and the other warps of the SM cover them.  Lines of any length (vectors
+// must not straddle line ends: n % VEC == 0 and 16-byte aligned bases for VEC > 1).
+constexpr int kWarpScanBlock = 256;
+constexpr int kWarpScanVecs = 4;
+
+template <typename T, typename Acc, class Op, int VEC>
+__device__ __forceinline__ void scan_lines_warp(const T* __restrict__ in, T* __restrict__ out, const uint64_t lines,
+                                                const uint64_t n) {
+    constexpr int U = kWarpScanVecs;
+    constexpr uint64_t CHUNK = 32ull * VEC * U;
+    const int lane = threadIdx.x & 31;
+    const uint64_t warps = (uint64_t)gridDim.x * (kWarpScanBlock / 32);
+    for (uint64_t line = (uint64_t)blockIdx.x * (kWarpScanBlock / 32) + (threadIdx.x >> 5); line < lines; line += warps) {
+        const T* src = in + line * n;
+        T* dst = out + line * n;
+        Acc carry = Op::template identity<Acc>();
+        // one chunk ahead: the loads of chunk k + 1 are in flight while chunk k is scanned
+        Vec<T, VEC> nxt[U];
+        auto fetch = [&](const uint64_t from) {
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                const uint64_t at = from + ((uint64_t)j * 32 + lane) * VEC;
+                if (at < n) {
+                    nxt[j] = load_vec<T, VEC>(src + at);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) nxt[j].v[e] = Op::template identity<T>();
+                }
+            }
+        };
+        fetch(0);
+        for (uint64_t base = 0; base < n; base += CHUNK) {
+            Vec<T, VEC> cur[U];
+#pragma unroll
+            for (int j = 0; j < U; ++j) cur[j] = nxt[j];
+            if (base + CHUNK < n) fetch(base + CHUNK);
+            // running values inside each of the lane's vectors (every element is widened once), then U independent
+            // inclusive scans of the vector totals across the lanes
+            Acc part[U][VEC], inc[U];
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                part[j][0] = (Acc)cur[j].v[0];
+#pragma unroll
+                for (int e = 1; e < VEC; ++e) part[j][e] = Op::apply(part[j][e - 1], (Acc)cur[j].v[e]);
+                inc[j] = part[j][VEC - 1];
+            }
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    const Acc y = shfl_up_any(inc[j], d);
+                    if (lane >= d) inc[j] = Op::apply(y, inc[j]);
+                }
+            }
+            // vector j covers elements [j * 32 * VEC, (j + 1) * 32 * VEC) of the chunk
+#pragma unroll
+            for (int j = 0; j < U; ++j) {
+                Acc before = shfl_up_any(inc[j], 1);
+                if (lane == 0) before = Op::template identity<Acc>();
+                const Acc lead = Op::apply(carry, before);
+                Vec<T, VEC> w;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) w.v[e] = (T)Op::apply(lead, part[j][e]);
+                const uint64_t at = base + ((uint64_t)j * 32 + lane) * VEC;
+                if (at < n) store_vec<T, VEC>(dst + at, w);
+                carry = Op::apply(carry, shfl_any(inc[j], 31));
+            }
+        }
+    }
+}
+
+
 // ---------------------------------------------------------------------------------------------------------
 // Ring scan: long lines in a single launch; every element is read from memory once and written once
 // (8 bytes per fp32 element) and no thread block ever waits for the block before it.

@@ -41,7 +41,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv37'
+TEMPLATE_VERSION = 'tv39'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -55,6 +55,9 @@ RING_MAX_GRID = 256
 # must match kColBlock / kColRows of csrc/templates/ovl_colscan.cuh
 COL_BLOCK = 256
 COL_ROWS = 64
+WARP_SCAN_BLOCK = 256
+WARP_SCAN_MIN_LINES = 2048     # from this many lines on, a warp scans a whole line by itself
+WARP_SCAN_MIN_AXIS = 64        # ... if the line is at least this long
 TILE_EDGE = 32                # smallest extent of the two tiled axes for which accesses are staged
 TILE_WIDE = 64                # tile edge along an axis that is at least this long (32 otherwise)
 TILE_SMEM_LIMIT = 40 * 1024   # bytes of shared memory the staged tiles of one kernel may take
@@ -686,7 +689,9 @@ def emit_cuda(kernel, name):
                             'scratch_bytes': SCAN_HEADER_BYTES + spec.outer * chunks * spec.inner * acc_size,
                             'zero_bytes': SCAN_HEADER_BYTES, 'align_bytes': 16, 'lines': spec.lines, 'n': spec.n,
                             'outer': spec.outer, 'inner': spec.inner, 'op': spec.op, 'ring': None}
-    elif spec is not None and spec.n >= patterns.SCAN_MIN_AXIS:
+    elif spec is not None and (spec.n >= patterns.SCAN_MIN_AXIS or
+                               (spec.lines >= WARP_SCAN_MIN_LINES and spec.n >= WARP_SCAN_MIN_AXIS and
+                                (spec.n * spec.dtype.itemsize) % 16 == 0)):
         src.insert(2, '#include "ovl_scan.cuh"')
         t = ctype(spec.dtype)
         acc = 'double' if spec.dtype.is_float else t
@@ -719,6 +724,15 @@ def emit_cuda(kernel, name):
                     '    ovl::scan_aggregates<' + acc + ', ' + op + ', false, true>(' + agg_ptr + ', ' + str(spec.lines) +
                     'ull, ' + str(tpl) + 'ull, nullptr, nullptr);',
                     '}', '']
+        warp = None
+        if spec.lines >= WARP_SCAN_MIN_LINES and (spec.n * spec.dtype.itemsize) % 16 == 0:
+            # thousands of lines: a warp per line, nothing shared between warps
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(WARP_SCAN_BLOCK) + ') ' + name +
+                    '_wscan(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0) {',
+                    '    ovl::scan_lines_warp<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + '>(in0, out0, ' +
+                    str(spec.lines) + 'ull, ' + str(spec.n) + 'ull);',
+                    '}', '']
+            warp = {'symbol': name + '_wscan', 'block': WARP_SCAN_BLOCK}
         ring = None
         # (bulk copies need every line to start on a 16-byte boundary)
         if multi and can_align and (spec.lines == 1 or (spec.n * spec.dtype.itemsize) % 16 == 0):
@@ -732,6 +746,7 @@ def emit_cuda(kernel, name):
                     'smem': RING_SLOTS * tile * spec.dtype.itemsize + RING_CTL_BYTES,
                     'zero_bytes': SCAN_HEADER_BYTES + tiles * 16}
         meta['scan'] = {'name': name, 'aligned_variant': bool(can_align), 'three_pass': bool(multi), 'ring': ring,
+                        'warp': warp, 'short': spec.n < patterns.SCAN_MIN_AXIS,
                         'block': SCAN_BLOCK, 'tiles': tiles, 'scratch_bytes': scratch, 'zero_bytes': SCAN_HEADER_BYTES,
                         'blocks_per_sm': 2, 'align_bytes': vec * spec.dtype.itemsize, 'lines': spec.lines, 'n': spec.n,
                         'op': spec.op}

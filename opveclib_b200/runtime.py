@@ -102,6 +102,11 @@ class KernelPlan(object):
                                [], scratch, 0),
                     self._make(device, name + '_cscan' + suffix, max(1, min((tiles + warps - 1) // warps, cap)), block, [0],
                                [0], [al, al], scratch, 0)]
+        if which == 'wscan':
+            w = m['warp']
+            per_block = w['block'] // 32
+            grid = max(1, min((m['lines'] + per_block - 1) // per_block, sms * (1024 // w['block'])))
+            return [self._make(device, w['symbol'], grid, w['block'], [0], [0], [16, 16])]
         cap = sms * m['blocks_per_sm']
         scratch = m['scratch_bytes']
         passes = []
@@ -130,13 +135,18 @@ class KernelPlan(object):
                 return 'cscan'
             return 'cscanu'
         if meta.get('scan'):
+            if (meta['scan'].get('warp') and all(p % 16 == 0 for p in in_ptrs + out_ptrs)
+                    and os.environ.get('OVL_SCAN_MODE') not in ('threepass', 'block')):
+                return 'wscan'
             al = meta['scan']['align_bytes']
             if (meta['scan'].get('ring') and all(p % 16 == 0 for p in in_ptrs + out_ptrs)
                     and os.environ.get('OVL_SCAN_MODE') != 'threepass'):
                 return 'ring'
-            if meta['scan']['aligned_variant'] and all(p % al == 0 for p in in_ptrs + out_ptrs):
-                return 'scan'
-            return 'scanu'
+            # (lines too short for a block each are only scanned cooperatively by the warp kernel)
+            if not meta['scan'].get('short'):
+                if meta['scan']['aligned_variant'] and all(p % al == 0 for p in in_ptrs + out_ptrs):
+                    return 'scan'
+                return 'scanu'
         if meta.get('red'):
             return 'red'
         if meta.get('tile') and os.environ.get('OVL_TILE_MODE') != 'off':
