@@ -515,10 +515,8 @@ template <class Op>
 int run_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, bool aligned,
              cudaStream_t stream) {
     if (aligned && !carry && lines >= kWarpScanMinLines && n % 4 == 0 && long_line_mode() == kModeRing) {
-        const uint64_t per_block = ovl::kWarpScanBlock / 32;
-        const uint64_t want = (lines + per_block - 1) / per_block;
-        const uint64_t cap = (uint64_t)sm_count_cached() * (1024 / ovl::kWarpScanBlock);
-        scan_warp_f32_kernel<Op><<<(uint32_t)(want < cap ? want : cap), ovl::kWarpScanBlock, 0, stream>>>(in, out, lines, n);
+        const ovl::WarpScanShape shape = ovl::warp_scan_shape(lines, (uint32_t)sm_count_cached());
+        scan_warp_f32_kernel<Op><<<shape.grid, shape.block, 0, stream>>>(in, out, lines, n);
         cudaError_t e = cudaGetLastError();
         return e == cudaSuccess ? OVL_OK : cuda_fail(e);
     }

@@ -487,14 +487,43 @@ __device__ __forceinline__ void scan_aggregates(Acc* __restrict__ agg, const uin
 constexpr int kWarpScanBlock = 256;
 constexpr int kWarpScanVecs = 4;
 
+// Launch shape for `lines` lines on `sms` SMs: every warp walks whole lines one after the other, so the kernel takes
+// as long as the warp with the most lines.  Among 12 to 21 resident warps per SM (two to four blocks of four to eight
+// warps; the kernel's registers allow no more) take the shape that leaves the fewest warp slots idle in the last
+// round, and among equals the one with the most warps.
+struct WarpScanShape {
+    uint32_t grid, block;
+};
+__host__ __device__ inline WarpScanShape warp_scan_shape(uint64_t lines, uint32_t sms) {
+    const uint32_t shapes[][2] = {{3, 7}, {4, 5}, {3, 6}, {2, 8}, {2, 7}, {3, 5}, {2, 6}, {3, 4}};   // {blocks per SM, warps}
+    double best = -1.0;
+    WarpScanShape pick = {1, 32};
+    for (int i = 0; i < 8; ++i) {
+        const uint64_t slots = (uint64_t)sms * shapes[i][0] * shapes[i][1];
+        const uint64_t rounds = (lines + slots - 1) / slots;
+        const double used = (double)lines / (double)(rounds * slots);
+        if (used > best + 0.02) {
+            best = used;
+            const uint64_t blocks = (lines + shapes[i][1] - 1) / shapes[i][1];
+            const uint64_t cap = (uint64_t)sms * shapes[i][0];
+            pick.grid = (uint32_t)(blocks < cap ? blocks : cap);
+            pick.block = shapes[i][1] * 32;
+        }
+    }
+    return pick;
+}
+
 template <typename T, typename Acc, class Op, int VEC>
 __device__ __forceinline__ void scan_lines_warp(const T* __restrict__ in, T* __restrict__ out, const uint64_t lines,
                                                 const uint64_t n) {
     constexpr int U = kWarpScanVecs;
     constexpr uint64_t CHUNK = 32ull * VEC * U;
     const int lane = threadIdx.x & 31;
-    const uint64_t warps = (uint64_t)gridDim.x * (kWarpScanBlock / 32);
-    for (uint64_t line = (uint64_t)blockIdx.x * (kWarpScanBlock / 32) + (threadIdx.x >> 5); line < lines; line += warps) {
+    // (the block may be launched with fewer warps than kWarpScanBlock / 32: the host sizes blocks and grid so that
+    // the lines divide evenly among the resident warps)
+    const uint64_t per_block = blockDim.x >> 5;
+    const uint64_t warps = (uint64_t)gridDim.x * per_block;
+    for (uint64_t line = (uint64_t)blockIdx.x * per_block + (threadIdx.x >> 5); line < lines; line += warps) {
         const T* src = in + line * n;
         T* dst = out + line * n;
         Acc carry = Op::template identity<Acc>();

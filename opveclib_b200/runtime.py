@@ -25,6 +25,22 @@ def _torch():
     return torch
 
 
+def warp_scan_shape(lines, sms):
+    """(grid, block) of the warp-per-line scan (the same rule as ``ovl::warp_scan_shape`` of the templates): every
+    warp walks whole lines one after the other, so among the residencies the kernel's registers allow - 12 to 21
+    warps per SM as two to four blocks of four to eight warps - take the one that leaves the fewest warp slots idle
+    in the last round, and among equals (within 2 %) the one with the most warps."""
+    best, pick = -1.0, (1, 32)
+    for per_sm, warps in ((3, 7), (4, 5), (3, 6), (2, 8), (2, 7), (3, 5), (2, 6), (3, 4)):
+        slots = sms * per_sm * warps
+        rounds = (lines + slots - 1) // slots
+        used = lines / float(rounds * slots)
+        if used > best + 0.02:
+            best = used
+            pick = (max(1, min((lines + warps - 1) // warps, sms * per_sm)), warps * 32)
+    return pick
+
+
 class KernelPlan(object):
     """A compiled kernel with its launchable variants (generic / vectorised / scan / reduction), created on first
     use."""
@@ -103,10 +119,8 @@ class KernelPlan(object):
                     self._make(device, name + '_cscan' + suffix, max(1, min((tiles + warps - 1) // warps, cap)), block, [0],
                                [0], [al, al], scratch, 0)]
         if which == 'wscan':
-            w = m['warp']
-            per_block = w['block'] // 32
-            grid = max(1, min((m['lines'] + per_block - 1) // per_block, sms * (1024 // w['block'])))
-            return [self._make(device, w['symbol'], grid, w['block'], [0], [0], [16, 16])]
+            grid, block = warp_scan_shape(m['lines'], sms)
+            return [self._make(device, m['warp']['symbol'], grid, block, [0], [0], [16, 16])]
         cap = sms * m['blocks_per_sm']
         scratch = m['scratch_bytes']
         passes = []
