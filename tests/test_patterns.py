@@ -112,3 +112,78 @@ def test_scans_along_any_axis_are_recognised_with_their_geometry():
                               ((2, 3, 4, 300), 2, (1800, 4, 6, 300))]:
         spec = patterns.match_scan(_kernel(ns.cumsum(np.zeros(shape, np.float32), axis=axis)))
         assert spec is not None and (spec.lines, spec.n, spec.outer, spec.inner) == want, (shape, axis)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# accesses staged through shared memory (cuda_emit.plan_tiling) and the launch shape of the warp-per-line scan
+
+def _tiling(op):
+    from opveclib_b200 import cuda_emit
+    from opveclib_b200.access import analyze
+    k = _kernel(op)
+    return cuda_emit.plan_tiling(k, analyze(k))
+
+
+def test_transposed_operands_and_results_are_staged():
+    ns = cases.impl()
+    u = cases.user_ops(ns)
+    axis, reads, writes, tile_t, tile_l = _tiling(u.transpose(np.zeros((200, 300), np.float32)))
+    assert axis == 0 and len(reads) == 1 and not writes and (tile_t, tile_l) == (64, 64)
+    axis, reads, writes, tile_t, tile_l = _tiling(u.transpose_axpy(np.zeros((40, 100), np.float32),
+                                                                  np.zeros((100, 40), np.float32), alpha=1.0))
+    assert axis == 0 and len(reads) == 1 and (tile_t, tile_l) == (64, 32)
+    ovl = ns.ovl
+
+    @ovl.operator()
+    def scatter(a):
+        out = ovl.output([a.shape[1], a.shape[0]], a.dtype)
+        pos = ovl.position_in(a.shape)
+        out[pos[1], pos[0]] = a[pos]
+        return out
+
+    axis, reads, writes, _, _ = _tiling(scatter(np.zeros((64, 96), np.float64)))
+    assert axis == 0 and not reads and len(writes) == 1
+
+
+def test_what_is_not_staged():
+    ns = cases.impl()
+    u = cases.user_ops(ns)
+    ovl = ns.ovl
+    assert _tiling(u.transpose(np.zeros((8, 300), np.float32))) is None        # the result is only 8 wide
+    assert _tiling(u.ew_mulc(np.zeros((64, 64), np.float32), c=2.0)) is None    # nothing strided
+    assert _tiling(u.shift_cyclic(np.zeros(4096, np.float32))) is None          # rank 1
+
+    @ovl.operator()
+    def guarded(a):
+        # the transposed read sits behind a condition on a straight read: staged (the address is valid for every
+        # worker); the conditional transposed write is not
+        out = ovl.output_like(a)
+        pos = ovl.position_in(a.shape)
+        with ovl.if_(a[pos] > 0):
+            out[pos[1], pos[0]] = a[pos[1], pos[0]]
+        return out
+
+    axis, reads, writes, _, _ = _tiling(guarded(np.zeros((64, 64), np.float32)))
+    assert len(reads) == 1 and not writes
+
+    @ovl.operator()
+    def strided_gather(a):
+        # stride 2 along the innermost axis, no axis along which the operand is contiguous
+        out = ovl.output([a.shape[0], a.shape[1] // 2], a.dtype)
+        pos = ovl.position_in(out.shape)
+        out[pos] = a[pos[0], pos[1] * 2]
+        return out
+
+    assert _tiling(strided_gather(np.zeros((64, 128), np.float32))) is None
+
+
+def test_warp_scan_shape_divides_the_lines_evenly():
+    from opveclib_b200 import runtime
+    for lines in (2048, 4096, 5000, 10 ** 5, 2 ** 17):
+        grid, block = runtime.warp_scan_shape(lines, 148)
+        warps = block // 32
+        assert 4 <= warps <= 8 and block % 32 == 0 and 1 <= grid <= 148 * 4
+        slots = grid * warps
+        rounds = -(-lines // slots)
+        assert lines / float(rounds * slots) > 0.85
+    assert runtime.warp_scan_shape(4096, 148) == (296, 224)      # two even rounds of 2072 warps
