@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import cases
-from helpers import assert_exact
+from helpers import DRYRUN, assert_exact
 from opveclib_b200.autodiff import compose_backward
 from opveclib_b200.fuse import merge_op_dag
 from opveclib_b200.opgraph import build_op_dag
@@ -17,12 +17,15 @@ UNARY = ['neg', 'tanh', 'sigmoid', 'sin', 'cos']
 BINARY = ['add', 'sub', 'mul', 'div']
 
 
-def _random_graph(so, seed):
-    """The same random function twice: on operator-library values and on torch tensors."""
+def _random_graph(so, seed, wrap=None):
+    """The same random function twice: on operator-library values and on torch tensors.  ``wrap`` turns the numpy
+    leaves into what the operator library sees (device tensors in the GPU test)."""
     rs = np.random.RandomState(seed)
     rows, cols = int(rs.choice([1, 3, 4, 7])), int(rs.choice([2, 4, 6, 12]))
     leaves = [rs.uniform(0.5, 1.5, (rows, cols)) for _ in range(rs.randint(1, 4))]
     tleaves = [torch.tensor(x, requires_grad=True) for x in leaves]
+    if wrap is not None:
+        leaves = [wrap(x) for x in leaves]
     values = [(x, t) for x, t in zip(leaves, tleaves)]          # all of shape [rows, cols]
     for _ in range(rs.randint(3, 10)):
         kind = rs.choice(['unary', 'binary', 'binary', 'splitcat'])
@@ -82,3 +85,38 @@ def test_composed_gradients_match_autograd_and_survive_fusion(seed):
         expect = want[id(leaf)]
         expect = np.zeros_like(leaf) if expect is None else expect.numpy()
         np.testing.assert_allclose(got, expect, rtol=1e-9, atol=1e-11, err_msg='seed %d' % seed)
+
+
+GPU_SEEDS = range(12)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('seed', GPU_SEEDS)
+def test_gradients_through_as_torch_match_autograd(seed):
+    """The same graphs on the device: forward through `as_torch`, backward through `torch.autograd` into the fused
+    backward kernel, against torch's own autograd of the same function on the CPU."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    so = ns.stdops
+    if DRYRUN:
+        # cache warming without a device: trace, compose, fuse, compile
+        _, _, outs, _, _ = _random_graph(so, seed)
+        runtime.compile_outputs(outs)
+        bdag, has_grad = compose_backward(build_op_dag(*outs))
+        if any(has_grad):
+            runtime.Program(merge_op_dag(bdag))
+        return
+    wrap = lambda x: torch.tensor(x, device='cuda', requires_grad=True)     # noqa: E731
+    leaves, tleaves, outs, touts, above = _random_graph(so, seed, wrap)
+    results = ns.ovl.as_torch(outs)
+    results = results if isinstance(results, (list, tuple)) else [results]
+    for got, want in zip(results, touts):
+        np.testing.assert_allclose(got.detach().cpu().numpy(), want.detach().numpy(), rtol=1e-11, atol=1e-12)
+    sum((r * torch.tensor(g, device='cuda')).sum() for r, g in zip(results, above)).backward()
+    sum((t * torch.tensor(g)).sum() for t, g in zip(touts, above)).backward()
+    for leaf, ref in zip(leaves, tleaves):
+        if ref.grad is None:
+            assert leaf.grad is None or not leaf.grad.abs().sum().item()
+            continue
+        np.testing.assert_allclose(leaf.grad.cpu().numpy(), ref.grad.numpy(), rtol=1e-9, atol=1e-11,
+                                   err_msg='seed %d' % seed)

@@ -160,6 +160,26 @@ def test_many_wide_operands_fall_back_to_narrower_tiles():
     _check(ns, [op])
 
 
+@pytest.mark.skipif(DRYRUN, reason='needs a device')
+def test_staged_and_unstaged_kernels_agree(monkeypatch):
+    """OVL_TILE_MODE=off runs the same graph through the vectorised kernel (operand read in place)."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    u = cases.user_ops(ns)
+    rs = np.random.RandomState(12)
+    a = rs.uniform(-1, 1, (500, 333)).astype(np.float32)
+    b = rs.uniform(-1, 1, (333, 500)).astype(np.float32)
+    op = u.transpose_axpy(a, b, alpha=0.75)
+    staged = np.asarray(ns.ovl.evaluate([op]))
+    prog, _ = runtime.compile_outputs([op])
+    assert prog.plans[0].last_variant == 'tile'
+    monkeypatch.setenv('OVL_TILE_MODE', 'off')
+    plain = np.asarray(ns.ovl.evaluate([op]))
+    assert prog.plans[0].last_variant in ('vec', 'gen')
+    assert_exact(staged, plain, 'staged against unstaged')
+    assert_exact(staged, (a.T * np.float32(0.75) + b).astype(np.float32), 'against numpy')
+
+
 def test_small_or_straight_kernels_are_left_alone():
     ns = cases.impl()
     transpose = cases.user_ops(ns).transpose
