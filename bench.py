@@ -1,7 +1,7 @@
 """Benchmark of the hot path: fused OVL operator graphs on B200, next to the reference's CPU operator.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-                    [--workload c4|c5|c2_cumsum|c2_cumprod|c1|c1_shift|c3|c3_grad|light16|matvec|perf_accumulate|colscan|rows_short|transpose|transpose_axpy|op_<name>]
+                    [--workload c4|c5|c2_cumsum|c2_cumprod|c1|c1_shift|c3|c3_grad|light16|matvec|perf_accumulate|colscan|colsum|rows_short|transpose|transpose_axpy|op_<name>]
 
 Default workload (the one the headline metric is quoted on): the 16-operator fused element-wise chain over an
 fp32 tensor [8, 2^27] drawn from uniform[-2, 2], rows sharded contiguously over N GPUs with no communication
@@ -163,6 +163,9 @@ def build_graph(workload, rows_local=None, n_local=None):
     if workload == 'colscan':
         # a column scan far larger than L2: cumsum of fp32 [32768, 8192] along axis 0 (1 GiB in, 1 GiB out)
         return [ns.cumsum(z(32768, 8192), axis=0)], 32768 * 8192, 8
+    if workload == 'colsum':
+        # column sums as a per-column reduction loop over the rows of fp32 [16384, 8192]: the matrix is read once
+        return [cases.user_ops(ns).colsum(z(16384, 8192))], 16384 * 8192, 4
     if workload == 'rows_short':
         # many short lines: cumsum along axis 1 of fp32 [131072, 512] (256 MiB in, 256 MiB out), a warp per line
         return [ns.cumsum(z(131072, 512), axis=1)], 131072 * 512, 8
@@ -187,7 +190,7 @@ def precompile():
         streaming.plan(outs, dag, prog, 3)          # the slab-shaped kernels of the end-to-end leg
     for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'light16', 'matvec', 'op_tanh', 'op_exp',
               'op_log1p', 'op_expm1', 'op_mulc', 'op_add', 'op_where', 'perf_accumulate', 'colscan', 'transpose',
-              'transpose_axpy', 'rows_short'):
+              'transpose_axpy', 'rows_short', 'colsum'):
         runtime.compile_outputs(build_graph(w)[0])
 
 
@@ -308,6 +311,7 @@ def workload_config(workload, n):
         'perf_accumulate': "cumsum along axis 0, fp64 [10000, 1000] uniform[0,1] (the reference's own timing harness)",
         'colscan': 'cumsum along axis 0, fp32 [32768, 8192] normal(0,1)',
         'rows_short': 'cumsum along axis 1, fp32 [131072, 512] normal(0,1)',
+        'colsum': 'column sums as a per-column reduction loop, fp32 [16384, 8192] normal(0,1)',
         'transpose': 'transpose of fp32 [16384, 16384] normal(0,1) written as an operator that reads its operand transposed',
         'transpose_axpy': 'a^T * 0.5 + b, fp32 [16384, 16384] normal(0,1)',
     }
@@ -318,7 +322,7 @@ def workload_config(workload, n):
     if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
         names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
-            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec', 'colscan', 'rows_short', 'transpose', 'transpose_axpy')
+            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec', 'colscan', 'colsum', 'rows_short', 'transpose', 'transpose_axpy')
                                                       or workload.startswith('op_'))
             else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
 
@@ -606,6 +610,8 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
         return [cases.user_ops(ns).shift_cyclic(np_inputs[0])]
     if workload == 'matvec':
         return [cases.user_ops(ns).matvec(np_inputs[0], np_inputs[1])]
+    if workload == 'colsum':
+        return [cases.user_ops(ns).colsum(np_inputs[0])]
     if workload == 'rows_short':
         return [ns.cumsum(np_inputs[0], axis=1)]
     if workload == 'transpose':

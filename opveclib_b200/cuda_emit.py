@@ -41,7 +41,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv39'
+TEMPLATE_VERSION = 'tv43'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -527,6 +527,31 @@ def _emit_tile(kernel, info, name, params, widx_t):
                  'staged_writes': len(wslots)}
 
 
+def _reduce_across_workers(kernel, info, red):
+    """Should the threads of a warp be neighbouring WORKERS of a reduction loop rather than neighbouring trips of one
+    worker's loop?  Yes when the loop's reads are strided along the loop variable but contiguous along the innermost
+    workgroup axis (column sums: ``acc += a[i, col]``): then neighbouring workers' reads coalesce and neighbouring
+    trips' do not."""
+    shape = kernel.workgroup_shape
+    last = ('p', len(shape) - 1)
+    sym = info.loop_vars.get(id(red.loop.args[0]))
+    if sym is None or shape[-1] < 32:
+        return False
+    in_loop = set(id(n) for n in iter_nodes(red.loop.body))
+    along = across = False
+    for acc in info.accesses:
+        if id(acc.node) not in in_loop or acc.is_write or acc.tensor.kind != 'input':
+            continue
+        if acc.form is None or acc.form.mod is not None:
+            return False
+        step = abs(acc.form.coef(sym))
+        if step == 1:
+            along = True
+        elif step > 1 and acc.form.coef(last) == 1:
+            across = True
+    return across and not along
+
+
 def emit_cuda(kernel, name):
     """Full ``.cu`` text for one kernel plus its launch metadata.
 
@@ -617,7 +642,10 @@ def emit_cuda(kernel, name):
     red = patterns.match_reduce(kernel, info)
     if red is not None:
         src.insert(2, '#include "ovl_reduce.cuh"')
+        across = _reduce_across_workers(kernel, info, red) and os.environ.get('OVL_RED_LAYOUT') != 'along'
         group = REDUCE_BLOCK if (red.n >= REDUCE_BLOCK_TRIPS and W < REDUCE_FEW_WORKERS) else 32
+        if across:
+            group = REDUCE_BLOCK // 32          # 32 neighbouring workers per block, the loop cut into 8 slices
         per_block = REDUCE_BLOCK // group
         top = kernel.body.nodes
         at = [i for i, x in enumerate(top) if x is red.loop][0]
@@ -628,7 +656,7 @@ def emit_cuda(kernel, name):
         opname = 'ovl::OpAdd' if red.op == 'add' else 'ovl::OpMul'
         ivar = em.name(red.loop.args[0])
         em.put(acc_t + ' ovl_partial = ' + opname + '::identity<' + acc_t + '>();')
-        em.put('#pragma unroll 4')
+        em.put('#pragma unroll ' + ('8' if across else '4'))
         em.put('for(' + ivar + ' = ovl_member; ' + ivar + ' < ' + str(red.n) + '; ' + ivar + ' += ' + str(group) + '){')
         em.depth += 1
         for node in red.loop.body.nodes:
@@ -638,6 +666,38 @@ def emit_cuda(kernel, name):
                 em.node(node)
         em.depth -= 1
         em.put('}')
+        if across:
+            em.put('ovl_red_cols[ovl_member][ovl_tx] = ovl_partial;')
+            em.put('__syncthreads();')
+            em.put('if (ovl_member == 0) {')
+            em.depth += 1
+            em.put(acc_t + ' ovl_all = ovl_red_cols[0][ovl_tx];')
+            em.put('#pragma unroll')
+            em.put('for (int ovl_s = 1; ovl_s < ' + str(group) + '; ++ovl_s) ovl_all = ' + opname + '::apply<' + acc_t +
+                   '>(ovl_all, ovl_red_cols[ovl_s][ovl_tx]);')
+            em.put(em.name(red.acc) + ' = ' + opname + '::apply<' + acc_t + '>(' + em.name(red.acc) + ', ovl_all);')
+            em.put('if (ovl_live) {')
+            em.depth += 1
+            for node in top[at + 1:]:
+                em.node(node)
+            em.depth -= 1
+            em.put('}')
+            em.depth -= 1
+            em.put('}')
+            em.put('__syncthreads();')
+            # neighbouring threads are neighbouring workers (their reads coalesce); the warps of a block share the loop
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(REDUCE_BLOCK) + ') ' + name + '_red(' + params + ') {',
+                    '    __shared__ ' + acc_t + ' ovl_red_cols[' + str(group) + '][32];',
+                    '    const uint32_t ovl_tx = threadIdx.x & 31u, ovl_member = threadIdx.x >> 5;',
+                    '    for (' + widx_t + ' ovl_base = (' + widx_t + ')blockIdx.x * 32u; ovl_base < ' + str(W) +
+                    'ull; ovl_base += (' + widx_t + ')gridDim.x * 32u) {',
+                    '        const bool ovl_live = ovl_base + ovl_tx < ' + str(W) + 'ull;',
+                    '        // (threads past the last worker repeat it, so that every thread reaches the barriers)',
+                    '        const ' + widx_t + ' worker_index = ovl_live ? ovl_base + ovl_tx : (' + widx_t + ')' + str(W - 1) +
+                    'ull;'] + em.lines + ['    }', '}', '']
+            meta['red'] = {'symbol': name + '_red', 'block': REDUCE_BLOCK, 'workers_per_block': 32, 'items': W,
+                           'group': group, 'trips': red.n, 'op': red.op, 'layout': 'across'}
+    if red is not None and not across:
         em.put(em.name(red.acc) + ' = ' + opname + '::apply<' + acc_t + '>(' + em.name(red.acc) + ', ovl::group_reduce<' +
                acc_t + ', ' + opname + ', ' + str(group) + '>(ovl_partial, ovl_red_smem));')
         em.put('if (ovl_member == 0) {')
@@ -654,7 +714,7 @@ def emit_cuda(kernel, name):
                 str(group) + 'u; worker_index < ' + str(W) + 'ull; worker_index += ovl_stride) {'] + em.lines + \
                ['    }', '}', '']
         meta['red'] = {'symbol': name + '_red', 'block': REDUCE_BLOCK, 'workers_per_block': per_block, 'items': W,
-                       'group': group, 'trips': red.n, 'op': red.op}
+                       'group': group, 'trips': red.n, 'op': red.op, 'layout': 'along'}
     # ---- cooperative scan
     spec = patterns.match_scan(kernel, info)
     if spec is not None and spec.inner > 1:

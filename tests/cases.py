@@ -163,7 +163,18 @@ def user_ops(ns):
         out[pos] = a[pos[1], pos[0]] * alpha + b[pos]
         return out
 
-    ops = types.SimpleNamespace(transpose=transpose, transpose_axpy=transpose_axpy,
+    @ovl.operator()
+    def colsum(a):
+        # one worker per column folds the rows: strided along the loop, contiguous across workers
+        out = ovl.output([a.shape[1]], a.dtype)
+        col = ovl.position_in([a.shape[1]])[0]
+        accum = ovl.variable(0, a.dtype)
+        for i in ovl.arange(a.shape[0]):
+            accum <<= accum + a[i, col]
+        out[col] = accum
+        return out
+
+    ops = types.SimpleNamespace(transpose=transpose, transpose_axpy=transpose_axpy, colsum=colsum,
                                 shift_cyclic=shift_cyclic, absolute=absolute, halfplus=halfplus, ew_exp=ew_exp,
                                 dot=dot, matvec=matvec, rowprod_scaled=rowprod_scaled,
                                 ew_tanh=ew_tanh, ew_add=ew_add, ew_mul=ew_mul, ew_addc=ew_addc, ew_mulc=ew_mulc,

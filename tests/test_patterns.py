@@ -187,3 +187,16 @@ def test_warp_scan_shape_divides_the_lines_evenly():
         rounds = -(-lines // slots)
         assert lines / float(rounds * slots) > 0.85
     assert runtime.warp_scan_shape(4096, 148) == (296, 224)      # two even rounds of 2072 warps
+
+
+def test_reduction_layout_follows_the_contiguous_direction():
+    """Column sums put neighbouring workers, not neighbouring trips, on the threads of a warp."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    u = cases.user_ops(ns)
+    prog, _ = runtime.compile_outputs([u.colsum(np.zeros((300, 512), np.float32))])
+    assert prog.plans[0].meta['red']['layout'] == 'across' and prog.plans[0].meta['red']['workers_per_block'] == 32
+    prog, _ = runtime.compile_outputs([u.matvec(np.zeros((64, 300), np.float32), np.zeros(300, np.float32))])
+    assert prog.plans[0].meta['red']['layout'] == 'along'
+    prog, _ = runtime.compile_outputs([u.colsum(np.zeros((300, 16), np.float32))])      # too few columns for a warp
+    assert prog.plans[0].meta['red']['layout'] == 'along'

@@ -180,6 +180,29 @@ def test_staged_and_unstaged_kernels_agree(monkeypatch):
     assert_exact(staged, (a.T * np.float32(0.75) + b).astype(np.float32), 'against numpy')
 
 
+@pytest.mark.parametrize('shape,dtype', [((4096, 512), 'float32'), ((1000, 100), 'float64'), ((777, 45), 'int32'),
+                                         ((130, 8192), 'float32')])
+def test_column_sums_walk_the_rows_with_neighbouring_workers_on_a_warp(shape, dtype):
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    rs = np.random.RandomState(shape[1])
+    x = (rs.normal(0, 1, shape) if dtype.startswith('float') else rs.randint(-5, 6, shape)).astype(dtype)
+    op = cases.user_ops(ns).colsum(x)
+    got = np.asarray(ns.ovl.evaluate([op]))
+    prog, _ = runtime.compile_outputs([op])
+    assert prog.plans[0].meta['red']['layout'] == 'across'
+    if DRYRUN:
+        return
+    assert prog.plans[0].last_variant == 'red'
+    if dtype == 'int32':
+        np.testing.assert_array_equal(got, x.sum(axis=0, dtype=np.int32))
+    else:
+        wide = x.astype(np.float64).sum(axis=0)
+        scale = np.abs(x.astype(np.float64)).sum(axis=0)
+        tol = 1e-5 if dtype == 'float32' else 1e-12
+        assert np.all(np.abs(got - wide) <= tol * scale)
+
+
 def test_small_or_straight_kernels_are_left_alone():
     ns = cases.impl()
     transpose = cases.user_ops(ns).transpose
