@@ -6,7 +6,9 @@
 // (neighbouring members touch neighbouring elements, so row-major reads coalesce), keeps a private partial result
 // and group_reduce combines the partials in a fixed order.  Partials are kept in the accumulator's own type:
 // integer results are exactly those of the serial loop; floating-point results differ from it only by the order
-// of the additions.
+// of the additions.  Loops whose reads are strided along the loop variable but contiguous across workers (column
+// sums) get the other layout, written out by the code generator: a warp is 32 neighbouring workers, the block's warps
+// take slices of the loop and the slices meet in shared memory.
 #pragma once
 #include "ovl_scan.cuh"
 

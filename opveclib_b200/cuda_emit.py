@@ -41,7 +41,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv43'
+TEMPLATE_VERSION = 'tv44'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -66,6 +66,7 @@ TILE_SMEM_LIMIT = 40 * 1024   # bytes of shared memory the staged tiles of one k
 REDUCE_BLOCK = 256
 REDUCE_BLOCK_TRIPS = 2048
 REDUCE_FEW_WORKERS = 2048
+REDUCE_ACROSS_WIDE_BELOW = 1184      # blocks of 32 workers: fewer than eight per SM get 1024 threads each
 
 
 def ctype(dtype):
@@ -644,9 +645,14 @@ def emit_cuda(kernel, name):
         src.insert(2, '#include "ovl_reduce.cuh"')
         across = _reduce_across_workers(kernel, info, red) and os.environ.get('OVL_RED_LAYOUT') != 'along'
         group = REDUCE_BLOCK if (red.n >= REDUCE_BLOCK_TRIPS and W < REDUCE_FEW_WORKERS) else 32
+        red_block = REDUCE_BLOCK
         if across:
-            group = REDUCE_BLOCK // 32          # 32 neighbouring workers per block, the loop cut into 8 slices
-        per_block = REDUCE_BLOCK // group
+            # 32 neighbouring workers per block, the loop cut into as many slices as the block has warps: 8, or 32
+            # when there are too few workers to fill the device with 256-thread blocks
+            if (W + 31) // 32 < REDUCE_ACROSS_WIDE_BELOW and red.n >= 1024:
+                red_block = 1024
+            group = red_block // 32
+        per_block = red_block // group
         top = kernel.body.nodes
         at = [i for i, x in enumerate(top) if x is red.loop][0]
         em = BodyEmitter(kernel, 2, position_text=pos_text)
@@ -686,7 +692,7 @@ def emit_cuda(kernel, name):
             em.put('}')
             em.put('__syncthreads();')
             # neighbouring threads are neighbouring workers (their reads coalesce); the warps of a block share the loop
-            src += ['extern "C" __global__ void __launch_bounds__(' + str(REDUCE_BLOCK) + ') ' + name + '_red(' + params + ') {',
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(red_block) + ') ' + name + '_red(' + params + ') {',
                     '    __shared__ ' + acc_t + ' ovl_red_cols[' + str(group) + '][32];',
                     '    const uint32_t ovl_tx = threadIdx.x & 31u, ovl_member = threadIdx.x >> 5;',
                     '    for (' + widx_t + ' ovl_base = (' + widx_t + ')blockIdx.x * 32u; ovl_base < ' + str(W) +
@@ -695,7 +701,7 @@ def emit_cuda(kernel, name):
                     '        // (threads past the last worker repeat it, so that every thread reaches the barriers)',
                     '        const ' + widx_t + ' worker_index = ovl_live ? ovl_base + ovl_tx : (' + widx_t + ')' + str(W - 1) +
                     'ull;'] + em.lines + ['    }', '}', '']
-            meta['red'] = {'symbol': name + '_red', 'block': REDUCE_BLOCK, 'workers_per_block': 32, 'items': W,
+            meta['red'] = {'symbol': name + '_red', 'block': red_block, 'workers_per_block': 32, 'items': W,
                            'group': group, 'trips': red.n, 'op': red.op, 'layout': 'across'}
     if red is not None and not across:
         em.put(em.name(red.acc) + ' = ' + opname + '::apply<' + acc_t + '>(' + em.name(red.acc) + ', ovl::group_reduce<' +
