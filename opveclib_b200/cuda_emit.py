@@ -41,7 +41,7 @@ _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_M
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
 
-TEMPLATE_VERSION = 'tv44'
+TEMPLATE_VERSION = 'tv45'
 BLOCK_THREADS = 256
 # must match kScanBlock / kScanVpt of csrc/templates/ovl_scan.cuh
 SCAN_BLOCK = 512
@@ -546,8 +546,9 @@ def _reduce_across_workers(kernel, info, red):
         if acc.form is None or acc.form.mod is not None:
             return False
         step = abs(acc.form.coef(sym))
-        if step == 1:
-            along = True
+        per_worker = any(k[0] == 'p' and c != 0 for k, c in acc.form.coefs.items())
+        if step == 1 and per_worker:
+            along = True                # (a read every worker shares, `w[i]`, is a broadcast in either layout)
         elif step > 1 and acc.form.coef(last) == 1:
             across = True
     return across and not along

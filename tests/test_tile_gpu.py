@@ -203,6 +203,33 @@ def test_column_sums_walk_the_rows_with_neighbouring_workers_on_a_warp(shape, dt
         assert np.all(np.abs(got - wide) <= tol * scale)
 
 
+def test_weighted_column_sums_share_the_weights_across_the_warp():
+    """`acc += a[i, col] * w[i]`: the weight is the same for every worker, the matrix decides the layout."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    ovl = ns.ovl
+
+    @ovl.operator()
+    def weighted_colsum(a, w):
+        out = ovl.output([a.shape[1]], a.dtype)
+        col = ovl.position_in([a.shape[1]])[0]
+        accum = ovl.variable(0, a.dtype)
+        for i in ovl.arange(a.shape[0]):
+            accum <<= accum + a[i, col] * w[i]
+        out[col] = accum
+        return out
+
+    rs = np.random.RandomState(21)
+    a, w = rs.normal(0, 1, (2000, 300)), rs.normal(0, 1, 2000)
+    op = weighted_colsum(a, w)
+    got = np.asarray(ns.ovl.evaluate([op]))
+    prog, _ = runtime.compile_outputs([op])
+    assert prog.plans[0].meta['red']['layout'] == 'across'
+    if DRYRUN:
+        return
+    np.testing.assert_allclose(got, (a * w[:, None]).sum(axis=0), rtol=1e-11, atol=1e-11)
+
+
 def test_small_or_straight_kernels_are_left_alone():
     ns = cases.impl()
     transpose = cases.user_ops(ns).transpose
