@@ -21,3 +21,4 @@ from .runtime import evaluate, profile
 from .torch_bridge import as_torch, as_tensorflow
 # local runtime environment
 from .local import version, logger, cuda_enabled, cache_directory, clear_op_cache
+from .local import math_mode, set_math_mode, get_math_mode

@@ -36,12 +36,14 @@ def _template_stamp():
 _STAMP = None
 
 
-def kernel_name(kernel):
-    """'f' + sha224 of (kernel text, version, templates) - stable across processes."""
+def kernel_name(kernel, math='exact'):
+    """'f' + sha224 of (kernel text, version, templates, math lowering) - stable across processes."""
     global _STAMP
     if _STAMP is None:
         _STAMP = _template_stamp()
     key = kernel.text() + '|' + version + '|' + cuda_emit.TEMPLATE_VERSION + '|' + _STAMP
+    if math != 'exact':
+        key += '|math=' + math
     return 'f' + hashlib.sha224(key.encode('utf-8')).hexdigest()[:48]
 
 
@@ -53,18 +55,19 @@ def _run(cmd):
         raise RuntimeError('nvcc failed:\n' + exc.output)
 
 
-def compile_kernel(kernel):
+def compile_kernel(kernel, math='exact'):
     """Generate and compile one kernel (or fetch it from the cache).  Returns (cubin path, metadata)."""
-    name = kernel_name(kernel)
+    name = kernel_name(kernel, math)
     cubin = os.path.join(cache_directory, name + '.cubin')
     meta_path = os.path.join(cache_directory, name + '.json')
     if os.path.exists(cubin) and os.path.exists(meta_path):
         with open(meta_path) as f:
             return cubin, json.load(f)
     logger.debug('Compiling CUDA for kernel ' + kernel.name + ' as ' + name)
-    source, meta = cuda_emit.emit_cuda(kernel, name)
+    source, meta = cuda_emit.emit_cuda(kernel, name, math)
     meta['name'] = name
     meta['kernel'] = kernel.name
+    meta['math'] = math
     src_path = os.path.join(cache_directory, name + '.cu')
     with open(src_path, 'w') as f:
         f.write(source)
@@ -78,17 +81,34 @@ def compile_kernel(kernel):
     return cubin, meta
 
 
+def _launcher_stamp(deps):
+    h = hashlib.sha224()
+    for d in sorted(deps):
+        if os.path.exists(d):
+            with open(d, 'rb') as f:
+                h.update(f.read())
+    h.update(' '.join(gpu_arch_flags + NVCC_FLAGS).encode('utf-8'))
+    return h.hexdigest()
+
+
 def build_launcher(force=False):
-    """Compile csrc/ovl_launcher.cu into lib/libovl_b200.so for sm_100a (no GPU needed)."""
+    """Compile csrc/ovl_launcher.cu into lib/libovl_b200.so for sm_100a (no GPU needed).  The library is rebuilt
+    when the content of its sources differs from what it was built from (a digest kept beside it - file times do
+    not survive a copy of the tree)."""
     with _lock:
         os.makedirs(LIB_DIR, exist_ok=True)
         deps = [LAUNCHER_SRC, os.path.join(_PKG, '..', 'include', 'ovl_b200.h')] + \
             [os.path.join(TEMPLATE_DIR, fn) for fn in os.listdir(TEMPLATE_DIR)]
-        if not force and os.path.exists(LIB_PATH):
-            newest = max(os.path.getmtime(d) for d in deps if os.path.exists(d))
-            if os.path.getmtime(LIB_PATH) >= newest:
-                return LIB_PATH
+        stamp = _launcher_stamp(deps)
+        stamp_path = LIB_PATH + '.stamp'
+        if not force and os.path.exists(LIB_PATH) and os.path.exists(stamp_path):
+            with open(stamp_path) as f:
+                if f.read().strip() == stamp:
+                    return LIB_PATH
         tmp = LIB_PATH + '.%d.tmp' % os.getpid()
         _run([nvcc_path] + gpu_arch_flags + NVCC_FLAGS + ['-shared', '-Xcompiler', '-fPIC', '-o', tmp, LAUNCHER_SRC])
         os.replace(tmp, LIB_PATH)
+        with open(stamp_path + '.%d.tmp' % os.getpid(), 'w') as f:
+            f.write(stamp)
+        os.replace(stamp_path + '.%d.tmp' % os.getpid(), stamp_path)
         return LIB_PATH

@@ -11,6 +11,7 @@
 #include <string.h>
 #include <mutex>
 #include <string>
+#include <atomic>
 #include <vector>
 
 #include "../../include/ovl_b200.h"
@@ -360,17 +361,18 @@ inline uint64_t tiles_per_line(uint64_t n, bool lookback) {
     return (n + t - 1) / t;
 }
 
+// SM count of the current device (looked up once per device)
 int sm_count_cached() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
-            sms = v;
-        else
-            return 148;
+    constexpr int kMaxDevices = 64;
+    static std::atomic<int> sms[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    int v = sms[dev].load(std::memory_order_relaxed);
+    if (v == 0) {
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+        sms[dev].store(v, std::memory_order_relaxed);
     }
-    return sms;
+    return v;
 }
 
 // How a single line of several tiles is scanned.  Default: the ring scan (one launch, 8 bytes per element).

@@ -619,6 +619,7 @@ constexpr int kRingThreads = (kRingScanWarps + kRingReduceWarps + 3) * 32;   // 
 constexpr int kRingMaxGrid = 256;
 constexpr int kRingGather = 5;                     // aggregates fetched per lane and round by the prefix warp (160 a round)
 constexpr long long kRingWaitCycles = 1ll << 32;   // bound of every wait, in SM clock cycles (about two seconds)
+constexpr long long kRingSelfTestWaitCycles = 1ll << 27;   // the same bound in the expiry self-test (about 70 ms)
 constexpr uint32_t kRingCtlBytes = 4096;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -670,10 +671,10 @@ struct RingCtl {
 };
 
 // bounded wait on a shared-memory barrier; gives up at once when the block is aborting
-__device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool ring_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, const long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
-    while (clock64() - t0 < kRingWaitCycles) {
+    while (clock64() - t0 < limit) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
     }
@@ -753,6 +754,8 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
     extern __shared__ __align__(128) unsigned char ring_smem[];
     RingCtl<Acc>* ctl = reinterpret_cast<RingCtl<Acc>*>(ring_smem + (size_t)R * TILE_BYTES);
     volatile int* abort_flag = &ctl->abort;
+    // (the self-test that withholds one block's aggregates lets every wait run out: it uses a short bound)
+    const long long wait_limit = withhold_block >= 0 ? kRingSelfTestWaitCycles : kRingWaitCycles;
 
     ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
     uint64_t* desc = reinterpret_cast<uint64_t*>(hdr + 1);
@@ -786,8 +789,8 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         RingTile<MULTI> at(b, tiles_per_line, G);
         const uint32_t v0 = (uint32_t)wid * 32 * VPT + lane;            // this thread's vectors: v0 + 32 j
         for (uint32_t k = 0; k < my_tiles; ++k, at.advance(), cur.advance()) {
-            if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
-            if (!ring_wait(&ctl->ready[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
+            if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag, wait_limit)) ring_fail(hdr, abort_flag);
+            if (!ring_wait(&ctl->ready[cur.slot], cur.phase, abort_flag, wait_limit)) ring_fail(hdr, abort_flag);
             if (*abort_flag) break;
             const bool whole = !at.last_of_line() || tail == TILE;
             const Vec<T, VEC>* sv = reinterpret_cast<const Vec<T, VEC>*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
@@ -861,7 +864,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         uint64_t tile = b;
         RingTile<MULTI> at(b, tiles_per_line, G);
         for (uint32_t k = 0; k < my_tiles; ++k, tile += G, at.advance(), cur.advance(), parity ^= 1) {
-            if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag)) ring_fail(hdr, abort_flag);
+            if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag, wait_limit)) ring_fail(hdr, abort_flag);
             const bool whole = !at.last_of_line() || tail == TILE;
             const Vec<T, VEC>* sv = reinterpret_cast<const Vec<T, VEC>*>(ring_smem + (size_t)cur.slot * TILE_BYTES);
             Acc part[CPR];
@@ -915,7 +918,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
             RingTile<MULTI> at(b, tiles_per_line, G);
             for (uint32_t k = 0; k < my_tiles; ++k, at.advance(), cur.advance()) {
                 // second and later uses of a slot: wait until the scan of its previous tile has read it
-                if (k >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag)) {
+                if (k >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag, wait_limit)) {
                     ring_fail(hdr, abort_flag);
                     break;
                 }
@@ -936,7 +939,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                 // let the copies that may still be in flight land before the block gives up its shared memory
                 const long long t0 = clock64();
                 for (uint32_t k = (issued > (uint32_t)R) ? issued - R : 0; k < issued; ++k)
-                    while (!mbar_try_wait(&ctl->full[k % R], (k / R) & 1u) && clock64() - t0 < kRingWaitCycles) {
+                    while (!mbar_try_wait(&ctl->full[k % R], (k / R) & 1u) && clock64() - t0 < wait_limit) {
                     }
             }
         }
@@ -948,8 +951,8 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         for (uint32_t k = 0; k < my_tiles; ++k, cur.advance()) {
             // the chunk totals have been written - which also means that the slot's previous tile has been scanned, so
             // that its prefixes (wprefix, cexcl) are no longer needed; the prefix warp relies on this
-            if (!ring_wait(&ctl->reduced[cur.slot], cur.phase, abort_flag) ||
-                (k >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag))) {
+            if (!ring_wait(&ctl->reduced[cur.slot], cur.phase, abort_flag, wait_limit) ||
+                (k >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag, wait_limit))) {
                 if (lane == 0) ring_fail(hdr, abort_flag);
                 break;
             }
@@ -1005,7 +1008,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                     for (int i = 0; i < kRingGather; ++i) {
                         const uint32_t idx = base_i + i * 32 + lane;
                         uint32_t spins = 0;
-                        while (((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) && clock64() - t0 < kRingWaitCycles && !*abort_flag) {
+                        while (((w0[i] >> 32) == 0 || (w1[i] >> 32) == 0) && clock64() - t0 < wait_limit && !*abort_flag) {
                             if (++spins > 4) __nanosleep(64);
                             ring_peek(desc, first + idx, w0[i], w1[i]);
                         }
@@ -1032,7 +1035,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) excl = Op::apply(excl, shfl_xor_any(excl, d));
             // this tile's chunk prefixes are ready (and with that, wprefix[slot] of the slot's previous tile was read)
-            if (!ring_wait(&ctl->chunked[cur.slot], cur.phase, abort_flag)) {
+            if (!ring_wait(&ctl->chunked[cur.slot], cur.phase, abort_flag, wait_limit)) {
                 if (lane == 0) ring_fail(hdr, abort_flag);
                 break;
             }

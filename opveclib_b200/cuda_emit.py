@@ -26,6 +26,7 @@ import os
 from . import expr as E
 from .access import analyze
 from .kernel import iter_nodes
+from . import cuda_pack
 from . import patterns
 
 _UNARY_F32 = {'acos': 'acosf', 'asin': 'asinf', 'atan': 'atanf', 'cos': 'cosf', 'cosh': 'coshf', 'sin': 'sinf',
@@ -37,6 +38,9 @@ _UNARY_F64 = {'acos': 'acos', 'asin': 'asin', 'atan': 'atan', 'cos': 'cos', 'cos
 _ABS_INT = {'int8': 'ovl::abs_8', 'int16': 'ovl::abs_16', 'int32': 'abs', 'int64': 'llabs'}
 _INFIX = {'add': '+', 'sub': '-', 'mul': '*', 'div': '/', 'mod': '%', 'eq': '==', 'ne': '!=', 'lt': '<',
           'le': '<=', 'gt': '>', 'ge': '>=', 'and': '&&', 'or': '||'}
+# math='tolerance': fp32 division and these fp32 functions go to csrc/templates/ovl_fastmath.cuh
+_TOLERANCE_F32 = {'exp': 'ovl::tol::fexp', 'log': 'ovl::tol::flog', 'tanh': 'ovl::tol::ftanh'}
+MATH_MODES = ('exact', 'tolerance')
 _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_MIN',
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',
            ('epsilon', 'float32'): 'FLT_EPSILON', ('epsilon', 'float64'): 'DBL_EPSILON'}
@@ -94,8 +98,9 @@ class BodyEmitter(object):
     """Emits the statements of a kernel body.  ``read_subst`` / ``write_subst`` map id(node) of hoisted accesses
     to the C text that replaces the memory access (a register expression / an assignment template)."""
 
-    def __init__(self, kernel, indent, read_subst=None, write_subst=None, position_text=None):
+    def __init__(self, kernel, indent, read_subst=None, write_subst=None, position_text=None, math='exact'):
         self.kernel = kernel
+        self.math = math
         self.names = {}
         self.lines = []
         self.depth = indent
@@ -169,6 +174,8 @@ class BodyEmitter(object):
                 rhs = '(' + fn + '(' + x + ') ? 1 : 0)'
             elif fn == 'abs' and t in _ABS_INT:
                 rhs = _ABS_INT[t] + '(' + x + ')'
+            elif self.math == 'tolerance' and t == 'float32' and fn in _TOLERANCE_F32:
+                rhs = _TOLERANCE_F32[fn] + '(' + x + ')'
             else:
                 rhs = (_UNARY_F32 if t == 'float32' else _UNARY_F64)[fn] + '(' + x + ')'
             n = self.fresh(node)
@@ -188,6 +195,8 @@ class BodyEmitter(object):
                 rhs = 'fmodf(' + x + ',' + y + ')'
             elif fn == 'mod' and t == 'float64':
                 rhs = 'fmod(' + x + ',' + y + ')'
+            elif fn == 'div' and t == 'float32' and self.math == 'tolerance':
+                rhs = 'ovl::tol::fdiv(' + x + ', ' + y + ')'
             else:
                 rhs = '(' + x + ' ' + _INFIX[fn] + ' ' + y + ')'
             n = self.fresh(node)
@@ -441,7 +450,7 @@ def _address_expr(form, shape):
     return ' + '.join(terms) if terms else '0ull'
 
 
-def _emit_tile(kernel, info, name, params, widx_t):
+def _emit_tile(kernel, info, name, params, widx_t, math='exact'):
     """The ``_tile`` kernel: (source lines, metadata) or (None, None) when the kernel has no transposed accesses.
 
     Per tile of up to 64 x 64 workers over (axis, innermost axis): threads that walk the axis along which the
@@ -503,7 +512,7 @@ def _emit_tile(kernel, info, name, params, widx_t):
     strides = _strides(shape)
     widx = ' + '.join('(' + widx_t + ')w' + str(d) + ' * ' + str(strides[d]) + 'u' for d in range(rank))
     pos_text = 'const uint32_t position[' + str(rank) + '] = {' + ', '.join('w' + str(d) for d in range(rank)) + '};'
-    em = BodyEmitter(kernel, 4, read_subst, write_subst, position_text=pos_text)
+    em = BodyEmitter(kernel, 4, read_subst, write_subst, position_text=pos_text, math=math)
     em.block(kernel.body)
     i1, i2, i3, i4 = '    ', '        ', '            ', '                '
     src = ['extern "C" __global__ void __launch_bounds__(' + str(BLOCK_THREADS) + ') ' + name + '_tile(' + params + ') {'] + \
@@ -554,23 +563,33 @@ def _reduce_across_workers(kernel, info, red):
     return across and not along
 
 
-def emit_cuda(kernel, name):
+def emit_cuda(kernel, name, math='exact', pack=True):
     """Full ``.cu`` text for one kernel plus its launch metadata.
 
     Returns (source, meta) with meta = {'gen': {...}, 'vec': {...} or None}; each entry has the symbol name, the
-    block size and the number of loop iterations the grid should cover."""
+    block size and the number of loop iterations the grid should cover.
+
+    ``math``: 'exact' - CUDA's libm and IEEE division, results within an ulp or two of the reference's C++
+    operator; 'tolerance' - fp32 division, exp, log and tanh from csrc/templates/ovl_fastmath.cuh (results within
+    rtol 1e-5, division within 2 ulp), and vectorised bodies of pure fp32 arithmetic evaluated two workers at a
+    time with packed instructions (:mod:`opveclib_b200.cuda_pack`).  Integer work, data movement, fp64 and
+    scans are the same in both."""
+    if math not in MATH_MODES:
+        raise ValueError('math must be one of ' + ', '.join(MATH_MODES))
     info = analyze(kernel)
     shape = kernel.workgroup_shape
     W = kernel.num_workers
     widx_t = 'uint32_t' if W < 2 ** 31 else 'uint64_t'
     params = ', '.join(_params(kernel))
-    src = ['// generated by opveclib_b200 (' + TEMPLATE_VERSION + ') for kernel ' + kernel.name,
+    src = ['// generated by opveclib_b200 (' + TEMPLATE_VERSION + ', math=' + math + ') for kernel ' + kernel.name,
            '#include "ovl_common.cuh"', '']
+    if math == 'tolerance':
+        src.insert(2, '#include "ovl_fastmath.cuh"')
 
     # ---- generic kernel
     pos_text = 'const uint32_t position[' + str(len(shape)) + '] = {' + \
         ', '.join(_position_values(shape, 'worker_index')) + '};'
-    em = BodyEmitter(kernel, 2, position_text=pos_text)
+    em = BodyEmitter(kernel, 2, position_text=pos_text, math=math)
     em.block(kernel.body)
     src += ['extern "C" __global__ void __launch_bounds__(' + str(BLOCK_THREADS) + ') ' + name + '_gen(' + params +
             ') {',
@@ -618,25 +637,43 @@ def emit_cuda(kernel, name):
             aligned_tensors.add(('out', tensor.attr['io_index']))
         pvals = _position_values(shape, 'ovl_w0')
         pos_decl = ['const uint32_t p' + str(d) + ' = ' + v + ';' for d, v in enumerate(pvals)]
-        lane_pos = 'const uint32_t position[' + str(len(shape)) + '] = {' + ', '.join(
-            ['p' + str(d) for d in range(last)] + ['p' + str(last) + ' + (uint32_t)ovl_lane']) + '};'
-        em = BodyEmitter(kernel, 3, read_subst, write_subst, position_text=lane_pos)
-        em.block(kernel.body)
         ind = '        '
+        pairs = cuda_pack.plan_pairs(kernel, plan) if (math == 'tolerance' and pack) else None
+        if pairs is not None:
+            # two workers per expression: packed fp32 arithmetic, branches as masks
+            read_text, write_name, open_pair, close_pair = {}, {}, [], []
+            for si, (tensor, form, mode, nodes) in enumerate(plan.read_slots):
+                for n in nodes:
+                    read_text[id(n)] = ('ovl::tol::make2(rv%d.v[2 * ovl_pair], rv%d.v[2 * ovl_pair + 1])' % (si, si)
+                                        if mode == 'vec' else 'ovl::tol::splat(ru%d)' % si)
+            for si, (tensor, form, nodes, conditional) in enumerate(plan.write_slots):
+                open_pair.append('ovl::tol::f2 wp%d = ovl::tol::splat(0.0f);' % si)
+                close_pair.append('wv%d.v[2 * ovl_pair] = wp%d.x; wv%d.v[2 * ovl_pair + 1] = wp%d.y;' % (si, si, si, si))
+                for n in nodes:
+                    write_name[id(n)] = 'wp%d' % si
+            em = cuda_pack.PairEmitter(kernel, 3, pairs, read_text, write_name, literal, _LIMITS)
+            em.block(kernel.body)
+            loop = [ind + '#pragma unroll', ind + 'for (int ovl_pair = 0; ovl_pair < ' + str(L // 2) + '; ++ovl_pair) {'] + \
+                [ind + '    ' + l for l in open_pair] + em.lines + [ind + '    ' + l for l in close_pair] + [ind + '}']
+        else:
+            lane_pos = 'const uint32_t position[' + str(len(shape)) + '] = {' + ', '.join(
+                ['p' + str(d) for d in range(last)] + ['p' + str(last) + ' + (uint32_t)ovl_lane']) + '};'
+            em = BodyEmitter(kernel, 3, read_subst, write_subst, position_text=lane_pos, math=math)
+            em.block(kernel.body)
+            loop = [ind + '#pragma unroll', ind + 'for (int ovl_lane = 0; ovl_lane < ' + str(L) + '; ++ovl_lane) {',
+                    ind + '    const ' + widx_t + ' worker_index = ovl_w0 + ovl_lane; (void)worker_index;'] + \
+                em.lines + [ind + '}']
         src += ['extern "C" __global__ void __launch_bounds__(' + str(BLOCK_THREADS) + ') ' + name + '_vec(' +
                 params + ') {',
                 '    const ' + widx_t + ' ovl_stride = (' + widx_t + ')gridDim.x * ' + str(BLOCK_THREADS) + 'u;',
                 '    for (' + widx_t + ' ovl_g = (' + widx_t + ')blockIdx.x * ' + str(BLOCK_THREADS) +
                 'u + threadIdx.x; ovl_g < ' + str(groups) + 'ull; ovl_g += ovl_stride) {',
                 ind + 'const ' + widx_t + ' ovl_w0 = ovl_g * ' + str(L) + 'u;'] + \
-            [ind + l for l in pos_decl] + [ind + l for l in pre] + \
-            [ind + '#pragma unroll', ind + 'for (int ovl_lane = 0; ovl_lane < ' + str(L) + '; ++ovl_lane) {',
-             ind + '    const ' + widx_t + ' worker_index = ovl_w0 + ovl_lane; (void)worker_index;'] + \
-            em.lines + [ind + '}'] + [ind + l for l in post] + ['    }', '}', '']
+            [ind + l for l in pos_decl] + [ind + l for l in pre] + loop + [ind + l for l in post] + ['    }', '}', '']
         meta['vec'] = {'symbol': name + '_vec', 'block': BLOCK_THREADS, 'items': groups, 'lanes': L,
-                       'aligned': sorted(aligned_tensors)}
+                       'aligned': sorted(aligned_tensors), 'paired': pairs is not None}
     # ---- transposed reads staged through shared memory
-    tile_src, tile_meta = _emit_tile(kernel, info, name, params, widx_t)
+    tile_src, tile_meta = _emit_tile(kernel, info, name, params, widx_t, math)
     if tile_src is not None:
         src += tile_src
         meta['tile'] = tile_meta
@@ -656,7 +693,7 @@ def emit_cuda(kernel, name):
         per_block = red_block // group
         top = kernel.body.nodes
         at = [i for i, x in enumerate(top) if x is red.loop][0]
-        em = BodyEmitter(kernel, 2, position_text=pos_text)
+        em = BodyEmitter(kernel, 2, position_text=pos_text, math=math)
         for node in top[:at]:
             em.node(node)
         acc_t = ctype(red.acc.dtype)

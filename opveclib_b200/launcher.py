@@ -47,8 +47,11 @@ def library():
     if _lib is not None:
         return _lib
     path = compiler.LIB_PATH
-    if not os.path.exists(path) or os.environ.get('OVL_B200_REBUILD'):
-        path = compiler.build_launcher()
+    if os.path.exists(compiler.nvcc_path):
+        # (returns at once when the library is newer than its sources)
+        path = compiler.build_launcher(force=bool(os.environ.get('OVL_B200_REBUILD')))
+    elif not os.path.exists(path):
+        raise RuntimeError('libovl_b200.so is missing and there is no nvcc to build it: ' + path)
     lib = ctypes.CDLL(path)
     vp, u64, u32, i32 = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_int32
     tp = ctypes.POINTER(OvlTensor)

@@ -16,94 +16,60 @@ from .kernel import trace_function
 from .local import logger
 
 
+# Infix operators of lazy operator results: python method name -> (key of the operator library entry, whether the
+# lazy value is the right-hand operand).  The library (stdops) registers its element-wise operators under these
+# keys; the methods are attached to both classes below.
+_INFIX = {
+    '__add__': ('add', False), '__radd__': ('add', True), '__sub__': ('sub', False), '__rsub__': ('sub', True),
+    '__mul__': ('mul', False), '__rmul__': ('mul', True), '__truediv__': ('div', False),
+    '__rtruediv__': ('div', True), '__div__': ('div', False), '__rdiv__': ('div', True),
+    '__mod__': ('mod', False), '__rmod__': ('mod', True), '__eq__': ('eq', False), '__ne__': ('ne', False),
+    '__lt__': ('lt', False), '__le__': ('le', False), '__gt__': ('gt', False), '__ge__': ('ge', False),
+}
+_infix_library = {}
+
+
+def _attach_infix(cls, unwrap):
+    """Give ``cls`` the infix methods; ``unwrap(self)`` yields the OperatorOutput that takes part."""
+    def binary(key, reflected):
+        def method(self, other):
+            mine = unwrap(self)
+            fn = _infix_library[key]
+            return fn(other, mine) if reflected else fn(mine, other)
+        return method
+
+    for method_name, (key, reflected) in _INFIX.items():
+        setattr(cls, method_name, binary(key, reflected))
+    cls.__neg__ = lambda self: _infix_library['neg'](unwrap(self))
+    cls.__hash__ = object.__hash__
+
+
 class OperatorOutput(object):
-    """An un-evaluated output tensor of an :class:`Operator`.  Infix arithmetic and comparisons between
-    outputs dispatch to the standard operator library registered with :meth:`register_magic_method`."""
+    """One un-evaluated output tensor of an :class:`Operator` (opveclib/operator.py:134-160).  Arithmetic and
+    comparisons between outputs build further operators from the standard operator library."""
     __array_priority__ = 1
-    _builtin_ops = {}
 
     @staticmethod
     def register_magic_method(key, value):
-        OperatorOutput._builtin_ops[key] = value
+        """Install the library operator behind an infix key ('add', 'lt', 'neg', ...)."""
+        _infix_library[key] = value
 
     def __init__(self, parent, index):
-        if not isinstance(parent, Operator):
-            raise TypeError('parent must be an Operator')
-        if not isinstance(index, int):
-            raise TypeError('index must be an int')
-        self.parent = parent
-        self.index = index
-        self.tensor_type = parent.output_types[index]
-        self.shape = self.tensor_type.shape
-        self.dtype = self.tensor_type.dtype
-        self.size = self.tensor_type.size
-        self.rank = self.tensor_type.rank
+        if not isinstance(parent, Operator) or not isinstance(index, int):
+            raise TypeError('an OperatorOutput is (Operator, int output index)')
+        self.parent, self.index = parent, index
+        t = self.tensor_type = parent.output_types[index]
+        self.shape, self.dtype, self.size, self.rank = t.shape, t.dtype, t.size, t.rank
 
     @property
     def from_gradient(self):
         return self.parent.from_gradient
 
-    def _call(self, key, *args):
-        return OperatorOutput._builtin_ops[key](*args)
-
-    def __add__(self, other):
-        return self._call('add', self, other)
-
-    def __radd__(self, other):
-        return self._call('add', other, self)
-
-    def __sub__(self, other):
-        return self._call('sub', self, other)
-
-    def __rsub__(self, other):
-        return self._call('sub', other, self)
-
-    def __mul__(self, other):
-        return self._call('mul', self, other)
-
-    def __rmul__(self, other):
-        return self._call('mul', other, self)
-
-    def __truediv__(self, other):
-        return self._call('div', self, other)
-
-    def __rtruediv__(self, other):
-        return self._call('div', other, self)
-
-    __div__ = __truediv__
-    __rdiv__ = __rtruediv__
-
-    def __mod__(self, other):
-        return self._call('mod', self, other)
-
-    def __rmod__(self, other):
-        return self._call('mod', other, self)
-
-    def __eq__(self, other):
-        return self._call('eq', self, other)
-
-    def __ne__(self, other):
-        return self._call('ne', self, other)
-
-    def __lt__(self, other):
-        return self._call('lt', self, other)
-
-    def __le__(self, other):
-        return self._call('le', self, other)
-
-    def __gt__(self, other):
-        return self._call('gt', self, other)
-
-    def __ge__(self, other):
-        return self._call('ge', self, other)
-
-    def __neg__(self):
-        return self._call('neg', self)
-
     def __bool__(self):
-        raise SyntaxError('Cannot resolve operator values at interpretation time.')
+        raise SyntaxError('The value of an operator output is not known while the graph is being built.')
 
-    __hash__ = object.__hash__
+
+_attach_infix(OperatorOutput, lambda out: out)
 
 
 class GradientPlaceholder(object):
@@ -118,7 +84,9 @@ class GradientPlaceholder(object):
 
 
 class Operator(object):
-    """A lazily evaluated operator application: a traced kernel plus where its inputs come from."""
+    """A lazily evaluated operator application: a traced kernel plus where its inputs come from.  Where a tensor
+    is expected (infix arithmetic, ``shape``, ``dtype``) an operator with exactly one output stands for that
+    output; one with several must be indexed (SyntaxError otherwise, as in opveclib/operator.py:210-216)."""
     __array_priority__ = 1
 
     def __init__(self, kernel, inputs, grad_dag, from_gradient, name, generator=None, constants=None):
@@ -139,96 +107,24 @@ class Operator(object):
         return len(self.output_types)
 
     def __iter__(self):
-        for i in range(len(self.output_types)):
-            yield OperatorOutput(self, i)
+        return (OperatorOutput(self, i) for i in range(len(self.output_types)))
 
-    def check_binary(self):
+    def only_output(self):
         if len(self.output_types) != 1:
-            raise SyntaxError('Cannot use binary infix operators on multi-output operators. '
-                              'Explicitly index an output.')
+            raise SyntaxError(str(self.name) + ' has ' + str(len(self.output_types)) + ' outputs: index the one '
+                              'that is meant before using it as a tensor.')
+        return self[0]
 
     @property
     def shape(self):
-        self.check_binary()
-        return self.output_types[0].shape
+        return self.only_output().shape
 
     @property
     def dtype(self):
-        self.check_binary()
-        return self.output_types[0].dtype
+        return self.only_output().dtype
 
-    def __add__(self, other):
-        self.check_binary()
-        return self[0] + other
 
-    def __radd__(self, other):
-        self.check_binary()
-        return other + self[0]
-
-    def __sub__(self, other):
-        self.check_binary()
-        return self[0] - other
-
-    def __rsub__(self, other):
-        self.check_binary()
-        return other - self[0]
-
-    def __mul__(self, other):
-        self.check_binary()
-        return self[0] * other
-
-    def __rmul__(self, other):
-        self.check_binary()
-        return other * self[0]
-
-    def __truediv__(self, other):
-        self.check_binary()
-        return self[0] / other
-
-    def __rtruediv__(self, other):
-        self.check_binary()
-        return other / self[0]
-
-    __div__ = __truediv__
-    __rdiv__ = __rtruediv__
-
-    def __mod__(self, other):
-        self.check_binary()
-        return self[0] % other
-
-    def __rmod__(self, other):
-        self.check_binary()
-        return other % self[0]
-
-    def __eq__(self, other):
-        self.check_binary()
-        return self[0] == other
-
-    def __ne__(self, other):
-        self.check_binary()
-        return self[0] != other
-
-    def __lt__(self, other):
-        self.check_binary()
-        return self[0] < other
-
-    def __le__(self, other):
-        self.check_binary()
-        return self[0] <= other
-
-    def __gt__(self, other):
-        self.check_binary()
-        return self[0] > other
-
-    def __ge__(self, other):
-        self.check_binary()
-        return self[0] >= other
-
-    def __neg__(self):
-        self.check_binary()
-        return -self[0]
-
-    __hash__ = object.__hash__
+_attach_infix(Operator, Operator.only_output)
 
 
 def _resolve_output(x):
@@ -257,83 +153,83 @@ class OpGenerator(object):
     def __str__(self):
         return self.op_function.__name__
 
-    def __call__(self, *inputs, **defined_constants):
-        from_gradient = False
-        for inp in inputs:
-            if getattr(inp, 'from_gradient', False) or isinstance(inp, GradientPlaceholder):
-                from_gradient = True
+    def _parameters(self):
+        """(names of the tensor parameters, {constant name: default}, accepts *args)."""
+        tensors, constants, variadic = [], {}, False
+        for p in inspect.signature(self.op_function).parameters.values():
+            if p.kind == p.VAR_POSITIONAL:
+                variadic = True
+            elif p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD):
+                if p.default is p.empty:
+                    tensors.append(p.name)
+                else:
+                    constants[p.name] = p.default
+            elif p.kind == p.KEYWORD_ONLY and p.default is not p.empty:
+                constants[p.name] = p.default
+        return tensors, constants, variadic
 
-        spec = inspect.getfullargspec(self.op_function)
-        func_args, func_varargs, func_defaults = spec.args, spec.varargs, spec.defaults
-        if func_defaults is None:
-            input_names = func_args
-            constants = dict(defined_constants)
-        else:
-            input_names = func_args[:-len(func_defaults)]
-            constants = dict(zip(func_args[-len(func_defaults):], func_defaults))
-            constants.update(defined_constants)
-
-        if self.forbid_none_valued_constants:
-            for key in constants:
-                if constants[key] is None:
-                    raise ValueError(self.name + ' argument ' + key + ' is None, which implies an unset '
-                                     'constant.\n  If a None constant is meaningful for this operator, the '
-                                     'operator should be defined with the appropriate decorator flag.')
-
-        resolved_inputs = []
-        input_types = []
-        for inp_n, inp in enumerate(inputs):
+    def _tensor_arguments(self, inputs):
+        """The positional arguments as graph inputs with their tensor types; anything without shape and dtype is
+        a TypeError that names the position."""
+        resolved, types = [], []
+        for position, arg in enumerate(inputs, 1):
+            if isinstance(arg, Operator):
+                arg = _resolve_output(arg)          # (ValueError for an operator with several outputs)
             try:
-                inp = _resolve_output(inp)
-            except TypeError:
-                pass
-            try:
-                input_types.append(TensorType.like(inp))
+                types.append(TensorType.like(arg))
             except (AttributeError, TypeError):
-                raise TypeError('Unexpectedly received a ' + inp.__class__.__name__ +
-                                ' instead of a tensor at argument position ' + str(inp_n + 1) +
-                                ' in the call to ' + self.name + '.  Should this argument be passed as a '
-                                'constant (keyword argument) instead?')
-            resolved_inputs.append(inp)
+                raise TypeError('%s: positional argument %d is a %s, not a tensor (compile-time constants are '
+                                'passed by keyword)' % (self.name, position, type(arg).__name__))
+            resolved.append(arg)
+        return resolved, types
 
-        num_inputs = len(input_types)
-        if len(input_names) != num_inputs and func_varargs is None:
-            err_msg = '\n' + self.name + ' function signature expects ' + str(len(input_names)) + \
-                ' input tensor argument(s):\n' + str(input_names) + '\n'
-            err_msg += 'but was supplied with ' + str(num_inputs) + '.\n'
-            if len(input_names) > num_inputs:
-                remaining_names = input_names[num_inputs - len(input_names):]
-                err_msg += 'Should ' + str(remaining_names) + ' be passed to constructor as constant?'
-            raise TypeError(err_msg)
+    def _trace_gradient(self, input_types, output_types, constants):
+        """Operator graph of the registered gradient function for these types, or None when the function declines
+        (returns None for some input).  Its leaves are placeholders in signature order: the operator's inputs,
+        then one gradient per operator output.  Every returned gradient must have its input's tensor type
+        (TypeError otherwise, opveclib/operator.py:512-523)."""
+        leaves = [GradientPlaceholder(t.shape, t.dtype) for t in list(input_types) + list(output_types)]
+        returned = self.grad_function(*leaves, **constants)
+        if returned is None or isinstance(returned, (Operator, OperatorOutput)):
+            returned = [returned]
+        returned = list(returned)
+        if any(g is None for g in returned):
+            return None
+        for index, (g, expected) in enumerate(zip(returned, input_types)):
+            if isinstance(g, Operator) and len(g.output_types) != 1:
+                raise TypeError('gradient %d of %s is an operator with %d outputs: index the one that is meant'
+                                % (index, self.name, len(g.output_types)))
+            got = TensorType.like(_resolve_output(g))
+            if got != expected:
+                raise TypeError('gradient %d of %s has type %s, its input has type %s'
+                                % (index, self.name, got, expected))
+        return build_op_dag(*returned, leaf_order=leaves)
 
+    def __call__(self, *inputs, **defined_constants):
+        """Trace the operator for these arguments: positional arguments are tensors (arrays, operator outputs,
+        placeholders), keyword arguments override the constants' defaults."""
+        tensor_names, constants, variadic = self._parameters()
+        constants.update(defined_constants)
+        if self.forbid_none_valued_constants:
+            unset = sorted(k for k, v in constants.items() if v is None)
+            if unset:
+                raise ValueError('%s: constant(s) %s are None, i.e. not set (decorate the operator with '
+                                 'forbid_none_valued_constants=False if None is a meaningful value)'
+                                 % (self.name, ', '.join(unset)))
+        resolved, input_types = self._tensor_arguments(inputs)
+        if len(input_types) != len(tensor_names) and not variadic:
+            hint = ''
+            if len(input_types) < len(tensor_names):
+                hint = '; missing: ' + ', '.join(tensor_names[len(input_types):])
+            raise TypeError('%s takes %d tensor argument(s) (%s) but got %d%s'
+                            % (self.name, len(tensor_names), ', '.join(tensor_names), len(input_types), hint))
         kernel = trace_function(self.op_function, input_types, constants, self.name)
-        output_types = kernel.output_types
-
+        # operators applied while a gradient is being traced do not get gradients of their own
+        from_gradient = any(isinstance(a, GradientPlaceholder) or getattr(a, 'from_gradient', False) for a in inputs)
         grad_dag = None
         if self.grad_function is not None and not from_gradient:
-            grad_inputs = [GradientPlaceholder(t.shape, t.dtype) for t in input_types]
-            grad_inputs += [GradientPlaceholder(t.shape, t.dtype) for t in output_types]
-            grad_outputs = self.grad_function(*grad_inputs, **constants)
-            if isinstance(grad_outputs, (Operator, OperatorOutput)) or grad_outputs is None:
-                grad_outputs = [grad_outputs]
-            grad_outputs = list(grad_outputs)
-            if not any(g is None for g in grad_outputs):
-                for gi, g in enumerate(grad_outputs):
-                    if isinstance(g, Operator) and len(g.output_types) != 1:
-                        raise TypeError('A multi-output operator was returned from a gradient function, '
-                                        'but the meaning of this is ambiguous: explicitly index each '
-                                        'output from operator: ' + str(g.name))
-                    cur_input_type = input_types[gi]
-                    cur_grad_type = TensorType.like(_resolve_output(g))
-                    if cur_input_type != cur_grad_type:
-                        raise TypeError('Gradient output index ' + str(gi) + ', with TensorType: ' +
-                                        str(cur_grad_type) + ' is inconsistent with operator input index ' +
-                                        str(gi) + ', with TensorType: ' + str(cur_input_type))
-                # the gradient graph's leaf inputs are the placeholders, in signature order: operator inputs
-                # first, then one gradient per operator output
-                grad_dag = build_op_dag(*grad_outputs, leaf_order=grad_inputs)
-
-        return Operator(kernel, resolved_inputs, grad_dag, from_gradient, self.name, self, dict(defined_constants))
+            grad_dag = self._trace_gradient(input_types, kernel.output_types, constants)
+        return Operator(kernel, resolved, grad_dag, from_gradient, self.name, self, dict(defined_constants))
 
     def add_grad(self, grad_function):
         if self.grad_function is not None:

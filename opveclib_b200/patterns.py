@@ -161,6 +161,14 @@ def match_scan(kernel, info=None):
             return None
         if pre_assigns[0].args[1] is not prd.node or pwr.node.args[2] is not acc:
             return None
+        # statement order in front of the loop: read, assign, store (a store in front of the assignment would
+        # write the variable's initial value, not the first element)
+        before = [id(nn) for nn in top]
+        try:
+            if not (before.index(id(prd.node)) < before.index(id(pre_assigns[0])) < before.index(id(pwr.node))):
+                return None
+        except ValueError:
+            return None
     else:
         if pre_accs or pre_assigns:
             return None

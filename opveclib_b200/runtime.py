@@ -13,7 +13,7 @@ import numpy as np
 
 from . import compiler, launcher
 from .fuse import merge_op_dag
-from .local import logger
+from .local import logger, get_math_mode, math_mode
 from .opgraph import build_op_dag
 
 _programs = {}
@@ -45,9 +45,10 @@ class KernelPlan(object):
     """A compiled kernel with its launchable variants (generic / vectorised / scan / reduction), created on first
     use."""
 
-    def __init__(self, kernel):
+    def __init__(self, kernel, math='exact'):
         self.kernel = kernel
-        self.cubin, self.meta = compiler.compile_kernel(kernel)
+        self.math = math
+        self.cubin, self.meta = compiler.compile_kernel(kernel, math)
         self.name = self.meta['name']
         self.in_types = kernel.input_types
         self.out_types = kernel.output_types
@@ -88,7 +89,8 @@ class KernelPlan(object):
         if which in ('gen', 'vec'):
             m = meta[which]
             block = m['block']
-            grid = max(1, min((m['items'] + block - 1) // block, sms * (2048 // block)))
+            rounds = int(os.environ.get('OVL_GRID_ROUNDS', '1'))
+            grid = max(1, min((m['items'] + block - 1) // block, sms * (2048 // block) * rounds))
             aligns = [0] * (n_in + n_out)
             if which == 'vec':
                 for kind, idx in m['aligned']:
@@ -193,29 +195,36 @@ class KernelPlan(object):
                 buf = torch.empty(need, dtype=torch.uint8, device='cuda:%d' % device)
                 self._scratch[key] = buf
             scratch_ptr, scratch_bytes = buf.data_ptr(), buf.numel()
-        total_ms = None
-        for pi, (k, use_in, use_out) in enumerate(passes):
-            akey = (which, pi, tuple(in_ptrs), tuple(out_ptrs))
-            arrays = self._arrays.get(akey)
-            if arrays is None:
-                if len(self._arrays) > 64:
-                    self._arrays.clear()
-                arrays = (launcher.tensor_array([(in_ptrs[i], self.in_types[i].dtype.code, self.in_types[i].size)
-                                                 for i in use_in]),
-                          launcher.tensor_array([(out_ptrs[i], self.out_types[i].dtype.code, self.out_types[i].size)
-                                                 for i in use_out]))
-                self._arrays[akey] = arrays
-            in_arr, out_arr = arrays
-            sp, sb = (scratch_ptr, scratch_bytes) if k.scratch_bytes else (None, 0)
-            if iterations is None:
-                st = k.launch(in_arr, len(use_in), out_arr, len(use_out), sp, sb, stream_ptr)
-                launcher.check(st, 'launching ' + self.kernel.name)
-                self.launches += 1
-            else:
-                st, ms = k.profile(in_arr, len(use_in), out_arr, len(use_out), sp, sb, stream_ptr, iterations)
-                launcher.check(st, 'profiling ' + self.kernel.name)
-                self.launches += iterations
-                total_ms = ms if total_ms is None else [a + b for a, b in zip(total_ms, ms)]
+        # A multi-pass kernel is timed one whole pass sequence per iteration: the middle pass of a three-pass scan
+        # turns the tile aggregates into prefixes in place, so repeating it alone would feed it its own output.
+        rounds = [None] if iterations is None else ([iterations] if len(passes) == 1 else [1] * iterations)
+        total_ms = None if iterations is None else []
+        for count in rounds:
+            round_ms = None
+            for pi, (k, use_in, use_out) in enumerate(passes):
+                akey = (which, pi, tuple(in_ptrs), tuple(out_ptrs))
+                arrays = self._arrays.get(akey)
+                if arrays is None:
+                    if len(self._arrays) > 64:
+                        self._arrays.clear()
+                    arrays = (launcher.tensor_array([(in_ptrs[i], self.in_types[i].dtype.code, self.in_types[i].size)
+                                                     for i in use_in]),
+                              launcher.tensor_array([(out_ptrs[i], self.out_types[i].dtype.code, self.out_types[i].size)
+                                                     for i in use_out]))
+                    self._arrays[akey] = arrays
+                in_arr, out_arr = arrays
+                sp, sb = (scratch_ptr, scratch_bytes) if k.scratch_bytes else (None, 0)
+                if count is None:
+                    st = k.launch(in_arr, len(use_in), out_arr, len(use_out), sp, sb, stream_ptr)
+                    launcher.check(st, 'launching ' + self.kernel.name)
+                    self.launches += 1
+                else:
+                    st, ms = k.profile(in_arr, len(use_in), out_arr, len(use_out), sp, sb, stream_ptr, count)
+                    launcher.check(st, 'profiling ' + self.kernel.name)
+                    self.launches += count
+                    round_ms = list(ms) if round_ms is None else [a + b for a, b in zip(round_ms, ms)]
+            if count is not None:
+                total_ms.extend(round_ms)
         return total_ms
 
     def check_status(self, stream_ptr, device):
@@ -235,9 +244,10 @@ class KernelPlan(object):
 class Program(object):
     """A compiled operator graph: kernel plans in launch order plus the wiring between them."""
 
-    def __init__(self, dag):
+    def __init__(self, dag, math='exact'):
         self.dag = dag
-        self.plans = [KernelPlan(k) for k in dag.kernels]
+        self.math = math
+        self.plans = [KernelPlan(k, math) for k in dag.kernels]
         # last consumer of every intermediate, so its memory can be released early
         self.last_use = {}
         for op_index, refs in enumerate(dag.references):
@@ -324,15 +334,17 @@ def as_output_list(outputs):
     return [outputs]
 
 
-def compile_outputs(output_list, opt_level=3):
-    """Build, fuse and compile the operator graph behind ``output_list``; cached by graph structure."""
+def compile_outputs(output_list, opt_level=3, math=None):
+    """Build, fuse and compile the operator graph behind ``output_list``; cached by graph structure and math
+    lowering (``math=None``: the current mode, :func:`opveclib_b200.local.get_math_mode`)."""
     output_list = as_output_list(output_list)
     dag = build_op_dag(*output_list)
-    key = (dag.text(), opt_level >= 3)
+    math = math or get_math_mode()
+    key = (dag.text(), opt_level >= 3, math)
     prog = _programs.get(key)
     if prog is None:
         fused = merge_op_dag(dag) if opt_level >= 3 else dag
-        prog = Program(fused)
+        prog = Program(fused, math)
         _programs[key] = prog
     return prog, dag
 
@@ -341,8 +353,11 @@ def _is_torch(x):
     return type(x).__module__.startswith('torch')
 
 
-def profile(output_list, target_language='b200', profiling_iterations=1, opt_level=3, out=None):
+def profile(output_list, target_language='b200', profiling_iterations=1, opt_level=3, out=None, math=None):
     """Evaluate operator outputs.  Returns (list of results, {kernel name: ms per iteration}).
+
+    ``math`` (extension): 'exact' or 'tolerance' for this call; None takes the current mode (``ovl.math_mode``,
+    ``ovl.set_math_mode``, environment variable OVL_B200_MATH; 'exact' unless changed).
 
     ``out`` (extension): a list with one preallocated numpy array per requested output (pinned host memory
     makes the copy back asynchronous and fast); results are written there instead of into fresh arrays.
@@ -355,6 +370,11 @@ def profile(output_list, target_language='b200', profiling_iterations=1, opt_lev
                          " (this backend runs on the GPU only: use 'b200')")
     if not isinstance(profiling_iterations, int) or profiling_iterations < 1:
         raise ValueError('profiling_iterations must be a positive int')
+    with math_mode(math):
+        return _profile(output_list, profiling_iterations, opt_level, out)
+
+
+def _profile(output_list, profiling_iterations, opt_level, out):
     prog, dag = compile_outputs(output_list, opt_level)
     if os.environ.get(_DRYRUN):
         # cache-warming mode for machines without a GPU: everything is compiled, nothing is launched
@@ -439,9 +459,9 @@ def profile(output_list, target_language='b200', profiling_iterations=1, opt_lev
     return host, times
 
 
-def evaluate(output_list, target_language='b200', opt_level=3, out=None):
+def evaluate(output_list, target_language='b200', opt_level=3, out=None, math=None):
     """Evaluate operator outputs on the GPU; a single output comes back bare, several as a list
-    (opveclib/operator.py:2099-2117)."""
+    (opveclib/operator.py:2099-2117).  ``math``: see :func:`profile`."""
     outs, _ = profile(output_list, target_language=target_language, profiling_iterations=1, opt_level=opt_level,
-                      out=out)
+                      out=out, math=math)
     return outs[0] if len(outs) == 1 else outs

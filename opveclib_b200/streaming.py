@@ -115,6 +115,43 @@ def _position_value_escapes(kernel, info):
     return False
 
 
+def _value_constants(kernel):
+    """The constants that can reach a stored value, an assigned variable, a condition or a loop bound of the
+    kernel other than through a tensor index, in program order.  Operators are specialised to their input shapes
+    when traced, and a python number derived from a shape (``x[pos] / x.shape[0]``) becomes such a constant: a
+    slab-shaped trace of that operator computes something else than the full-shaped one."""
+    nodes = list(iter_nodes(kernel.body))
+    reach = set()
+    work = []
+    for n in nodes:
+        if n.kind == 'assign_tensor':
+            work.append(n.args[2])
+        elif n.kind == 'assign_var':
+            work.append(n.args[1])
+        elif n.kind == 'if':
+            work.extend(c for c in n.conds if c is not None)
+        elif n.kind == 'for':
+            work.extend(n.args[1:])
+        elif n.kind == 'variable':
+            work.append(n.args[0])
+    while work:
+        n = work.pop()
+        if id(n) in reach:
+            continue
+        reach.add(id(n))
+        if n.kind == 'read':
+            continue                      # (what it reads is data; its index is checked by the locality proofs)
+        work.extend(a for a in n.args if getattr(a, 'is_scalar', False))
+    return [(n.dtype.name, n.attr['value']) for n in nodes if n.kind == 'const' and id(n) in reach]
+
+
+def _same_values(prog, slab_prog):
+    """The slab-shaped program computes with the same constants as the full-shaped one."""
+    if len(prog.dag.kernels) != len(slab_prog.dag.kernels):
+        return False
+    return all(_value_constants(a) == _value_constants(b) for a, b in zip(prog.dag.kernels, slab_prog.dag.kernels))
+
+
 def _retrace(outputs, rows, slab_rows, trailing=None):
     """The same operator graph traced for slabs of ``slab_rows`` rows (with the trailing extents ``trailing``
     instead of the leaves' own when given).  Returns (slab outputs, leaf map: original leaf id -> placeholder),
@@ -166,7 +203,7 @@ def _retrace(outputs, rows, slab_rows, trailing=None):
 def plan(output_list, dag, prog, opt_level):
     """A streaming plan for host inputs, or None.  Cached per graph structure."""
     from . import runtime
-    key = (dag.text(), opt_level >= 3)
+    key = (dag.text(), opt_level >= 3, prog.math)
     if key in _plans:
         return _plans[key]
     result = None
@@ -192,8 +229,9 @@ def plan(output_list, dag, prog, opt_level):
                     for ph in slab_dag.inputs:
                         orig = next(o for o, p in leaves.values() if p is ph)
                         order.append(next(i for i, x in enumerate(dag.inputs) if x is orig))
-                    result = {'slabs': slabs, 'rows': rows, 'slab_rows': rows // slabs, 'prog': slab_prog,
-                              'leaf_order': order, 'view': None}
+                    if _same_values(prog, slab_prog):
+                        result = {'slabs': slabs, 'rows': rows, 'slab_rows': rows // slabs, 'prog': slab_prog,
+                                  'leaf_order': order, 'view': None}
     except Exception:      # any doubt: evaluate in one piece
         result = None
     _plans[key] = result
@@ -225,6 +263,8 @@ def _plan_element_local(output_list, dag, prog, opt_level, rows):
         return None
     slab_outputs, leaves = traced
     slab_prog, slab_dag = runtime.compile_outputs(slab_outputs, opt_level)
+    if not _same_values(prog, slab_prog):
+        return None
     order = []
     for ph in slab_dag.inputs:
         orig = next(o for o, p in leaves.values() if p is ph)

@@ -16,14 +16,14 @@ from .opgraph import build_op_dag
 _backward_programs = {}
 
 
-def _backward_program(dag, opt_level):
-    key = (dag.text(), opt_level >= 3)
+def _backward_program(dag, opt_level, math):
+    key = (dag.text(), opt_level >= 3, math)
     hit = _backward_programs.get(key)
     if hit is None:
         bdag, has_grad = compose_backward(dag)
         if any(has_grad):
             fused = merge_op_dag(bdag) if opt_level >= 3 else bdag
-            hit = (runtime.Program(fused), has_grad)
+            hit = (runtime.Program(fused, math), has_grad)
         else:
             hit = (None, has_grad)
         _backward_programs[key] = hit
@@ -41,7 +41,7 @@ _ops = None
 
 
 def _register(prog, dag, opt_level):
-    key = (dag.text(), opt_level >= 3)
+    key = (dag.text(), opt_level >= 3, prog.math)
     if key not in _handles:
         out_types = [prog.plans[o].out_types[k] for o, k in prog.dag.outputs]
         _registry.append((prog, dag, opt_level, out_types))
@@ -77,8 +77,8 @@ def _define_ops():
 
     @torch.library.custom_op('ovl_b200::run_backward', mutates_args=())
     def run_backward(inputs: List[torch.Tensor], grads: List[torch.Tensor], handle: int) -> List[torch.Tensor]:
-        _, dag, opt_level, _ = _registry[handle]
-        bprog, has_grad = _backward_program(dag, opt_level)
+        prog, dag, opt_level, _ = _registry[handle]
+        bprog, has_grad = _backward_program(dag, opt_level, prog.math)
         device = _device_of(inputs)
         with torch.cuda.device(device):
             stream = torch.cuda.current_stream().cuda_stream
@@ -87,8 +87,8 @@ def _define_ops():
 
     @run_backward.register_fake
     def _(inputs, grads, handle):
-        _, dag, opt_level, _ = _registry[handle]
-        _, has_grad = _backward_program(dag, opt_level)
+        prog, dag, opt_level, _ = _registry[handle]
+        _, has_grad = _backward_program(dag, opt_level, prog.math)
         return [torch.empty_like(x) for x, h in zip(inputs, has_grad) if h]
 
     def setup_context(ctx, inputs, output):
@@ -98,8 +98,8 @@ def _define_ops():
 
     def backward(ctx, grad_outputs):
         handle = ctx.handle
-        _, dag, opt_level, out_types = _registry[handle]
-        bprog, has_grad = _backward_program(dag, opt_level)
+        prog, dag, opt_level, out_types = _registry[handle]
+        bprog, has_grad = _backward_program(dag, opt_level, prog.math)
         saved = list(ctx.saved_tensors)
         if bprog is None:
             return [None for _ in has_grad], None
@@ -116,15 +116,16 @@ def _define_ops():
     return _ops
 
 
-def as_torch(tensor_list, opt_level=3):
+def as_torch(tensor_list, opt_level=3, math=None):
     """Evaluate operator outputs on the GPU as torch tensors, differentiable with respect to the torch leaf
     inputs that require grad.  A single requested output comes back bare, several as a list
     (as ``as_tensorflow`` does, opveclib/operator.py:2409-2412).  The graph runs as the custom operator
-    ``torch.ops.ovl_b200.run``; its backward as ``torch.ops.ovl_b200.run_backward``."""
+    ``torch.ops.ovl_b200.run``; its backward as ``torch.ops.ovl_b200.run_backward``.  ``math``: the math lowering
+    of the forward and backward kernels ('exact', 'tolerance'; None: the current mode)."""
     import torch
     outputs = runtime.as_output_list(tensor_list)
     single = not isinstance(tensor_list, (list, tuple)) and len(outputs) == 1
-    prog, dag = runtime.compile_outputs(outputs, opt_level)
+    prog, dag = runtime.compile_outputs(outputs, opt_level, math)
     if not torch.cuda.is_available():
         raise RuntimeError('opveclib_b200 needs a CUDA device: there is no CPU execution path')
     device = torch.cuda.current_device()

@@ -74,3 +74,32 @@ def test_the_reference_timing_harness_shape():
     if not DRYRUN:
         assert np.allclose(np.cumsum(x, axis=0), got)          # the harness's own check
         np.testing.assert_allclose(got, np.cumsum(x, axis=0), rtol=1e-12, atol=1e-9)
+
+
+def test_profile_with_several_iterations_returns_the_scan():
+    """The reference's timing harness calls ``ovl.profile(cumsum(x, axis=0), profiling_iterations=10)`` and
+    checks the result (opveclib/examples/test_perf_accumulate.py:50-53).  Multi-pass scans must run one whole
+    pass sequence per timed iteration: their middle pass rewrites the tile aggregates in place."""
+    ns = cases.impl()
+    x = np.random.RandomState(2).uniform(0, 1, size=(10000, 1000))
+    outs, times = ns.ovl.profile(ns.cumsum(x, axis=0), profiling_iterations=3)
+    if not DRYRUN:
+        np.testing.assert_allclose(outs[0], np.cumsum(x, axis=0), rtol=1e-12, atol=1e-9)
+        assert all(len(ms) == 3 and np.all(ms > 0) for ms in times.values())
+
+
+@pytest.mark.skipif(DRYRUN, reason='needs a device')
+def test_profile_with_several_iterations_on_an_unaligned_long_line():
+    """Three-pass contiguous scan (a long line that does not start on a 16-byte boundary), three timed iterations."""
+    import torch
+    ns = cases.impl()
+    n = 3 * 8192 * 5 + 77
+    x = np.random.RandomState(4).normal(0, 1, n).astype(np.float32)
+    base = torch.empty(n + 1, dtype=torch.float32, device='cuda')
+    dx = base[1:]
+    dx.copy_(torch.from_numpy(x))
+    assert dx.data_ptr() % 16 != 0
+    outs, times = ns.ovl.profile(ns.cumsum(dx), profiling_iterations=3)
+    want = np.cumsum(x.astype(np.float64))
+    np.testing.assert_allclose(outs[0].cpu().numpy(), want, rtol=1e-5, atol=1e-5 * np.abs(want).max())
+    assert all(len(ms) == 3 for ms in times.values())

@@ -200,3 +200,31 @@ def test_reduction_layout_follows_the_contiguous_direction():
     assert prog.plans[0].meta['red']['layout'] == 'along'
     prog, _ = runtime.compile_outputs([u.colsum(np.zeros((300, 16), np.float32))])      # too few columns for a warp
     assert prog.plans[0].meta['red']['layout'] == 'along'
+
+
+def test_seeded_scan_needs_assignment_before_the_first_store():
+    """``acc <<= x[line, 0]; y[line, 0] = acc; for i in 1..n`` is an inclusive scan; with the first store in front
+    of the assignment, y[line, 0] is the variable's initial value and the loop is left to the generic kernel."""
+    ovl = cases.impl().ovl
+    x = np.zeros((4, 4096), np.float32)
+
+    def make(store_first):
+        @ovl.operator()
+        def scan(a):
+            out = ovl.output_like(a)
+            line = ovl.position_in([a.shape[0]])[0]
+            acc = ovl.variable(0, a.dtype)
+            if store_first:
+                out[line, 0] = acc
+                acc <<= a[line, 0]
+            else:
+                acc <<= a[line, 0]
+                out[line, 0] = acc
+            for i in ovl.arange(1, a.shape[1]):
+                acc <<= acc + a[line, i]
+                out[line, i] = acc
+            return out
+        return scan(x)
+
+    assert patterns.match_scan(_kernel(make(False))) is not None
+    assert patterns.match_scan(_kernel(make(True))) is None

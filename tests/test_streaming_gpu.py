@@ -73,3 +73,27 @@ def test_graphs_that_are_not_row_local_are_evaluated_in_one_piece():
                  [ns.cumsum(np.zeros((1 << 12, 4096), np.float32), axis=0)]):          # scan down the rows
         prog, dag = runtime.compile_outputs(outs)
         assert streaming.plan(outs, dag, prog, 3) is None
+
+
+def test_shape_derived_constants_keep_the_graph_in_one_piece():
+    """An operator that bakes a number taken from its input's shape into a value computes something else when it is
+    traced again for a slab; such graphs are not streamed, and the result is the one-piece result."""
+    ns = cases.impl()
+    ovl = ns.ovl
+
+    @ovl.operator()
+    def mean_scaled(x):
+        out = ovl.output_like(x)
+        pos = ovl.position_in(x.shape)
+        out[pos] = x[pos] / float(x.shape[0]) + float(x.shape[1])
+        return out
+
+    x = np.random.RandomState(3).uniform(-1, 1, (16, 1 << 20)).astype(np.float32)
+
+    def build(ns_, a):
+        return [mean_scaled(a)]
+    plan, streamed, whole = _both_ways(build, [x])
+    assert plan is None
+    if streamed is not None:
+        assert_exact(streamed[0], whole[0], 'shape-derived constants')
+        assert_exact(streamed[0], x / np.float32(16.0) + np.float32(1 << 20), 'value')
