@@ -149,6 +149,38 @@ int ovl_scan_f32_begin(int op, const float* in, uint64_t n, double* out_total, v
                        void* cuda_stream);
 int ovl_scan_f32_finish(int op, const float* in, float* out, uint64_t n, const double* carry, void* scratch,
                         uint64_t scratch_bytes, void* cuda_stream);
+/* The same pair for GPUs of one box that exchange their totals through peer memory, without a collective library
+ * call between the two kernels (the reference has no multi-GPU support; this is the shard-boundary exchange of a
+ * scan along an axis split over 2 to 8 GPUs).  Every rank allocates one exchange buffer (ovl_peer_alloc: device
+ * memory plus a 64-byte handle that another process of the same box turns into a mapping with ovl_peer_open) and
+ * fills OvlPeerExchange with all ranks' buffers as mapped in its own process, its rank, the number of ranks and
+ * an epoch that starts at 1 and grows by one with every begin/finish pair - the same on all ranks.
+ * ovl_scan_f32_begin_peer reads the shard once and stores its total into every rank's buffer (plain stores over
+ * NVLink, also into *out_total); ovl_scan_f32_finish_peer scans the shard in one cooperative launch whose first
+ * step waits - bounded, OVL_ERR_TIMEOUT in the scratch's status word on expiry - until the totals of all ranks of
+ * this epoch have arrived in its own buffer, and combines those of the ranks before it, in rank order, into its
+ * carry.  Only shards that the ring scan takes are accepted: more than 8192 elements, `in` and `out` 16-byte
+ * aligned (OVL_ERR_ALIGNMENT otherwise - use the plain pair with a collective then).  All ranks must call both
+ * functions once per epoch; kernels of different ranks wait for each other, so each rank needs its own GPU (on one
+ * GPU, enqueue every rank's begin before any rank's finish). */
+#define OVL_PEER_HANDLE_BYTES 64
+#define OVL_MAX_PEERS 8
+typedef struct OvlPeerExchange {
+    void* buffers[OVL_MAX_PEERS]; /* rank p's exchange buffer as mapped in this process */
+    uint32_t world;               /* number of ranks, 1..8 */
+    uint32_t rank;                /* this rank */
+    uint32_t epoch;               /* 1, 2, 3, ...: one per begin/finish pair, equal on all ranks */
+} OvlPeerExchange;
+uint64_t ovl_peer_buffer_bytes(void);
+int ovl_peer_alloc(void** out_ptr, unsigned char* out_handle /* OVL_PEER_HANDLE_BYTES */);
+int ovl_peer_open(const unsigned char* handle, void** out_ptr);
+int ovl_peer_close(void* ptr);
+int ovl_peer_free(void* ptr);
+int ovl_scan_f32_begin_peer(int op, const float* in, uint64_t n, double* out_total, void* scratch,
+                            uint64_t scratch_bytes, const OvlPeerExchange* px, void* cuda_stream);
+int ovl_scan_f32_finish_peer(int op, const float* in, float* out, uint64_t n, void* scratch, uint64_t scratch_bytes,
+                             const OvlPeerExchange* px, void* cuda_stream);
+
 /* Reduce `n` fp32 elements to one double (sum or product, fixed combination order): the shard total that
  * ranks exchange before a scan that crosses shard boundaries.  `scratch` must hold
  * ovl_reduce_f32_scratch_bytes(n) bytes. */

@@ -341,6 +341,21 @@ __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_f32_kernel(con
     ovl::scan_ring<float, double, Op, 4, HAS_CARRY, MULTI>(in, out, carry, lines, n, scratch, withhold_block);
 }
 
+// the pair of a sharded scan whose totals travel through peer memory
+template <class Op>
+__global__ void __launch_bounds__(ovl::kScanBlock) reduce_publish_f32_kernel(const float* __restrict__ in, uint64_t n,
+                                                                            double* __restrict__ out_total, void* scratch,
+                                                                            const ovl::PeerExchange px) {
+    ovl::reduce_all<float, double, Op, 4, true, true>(in, n, out_total, scratch, &px);
+}
+
+template <class Op>
+__global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_peer_f32_kernel(const float* __restrict__ in,
+                                                                                 float* __restrict__ out, uint64_t n,
+                                                                                 void* scratch, const ovl::PeerExchange px) {
+    ovl::scan_ring<float, double, Op, 4, true, false>(in, out, nullptr, 1, n, scratch, -1, &px);
+}
+
 template <class Op>
 __global__ void __launch_bounds__(ovl::kWarpScanBlock) scan_warp_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
                                                                           uint64_t lines, uint64_t n) {
@@ -627,6 +642,120 @@ extern "C" int ovl_scan_f32_finish(int op, const float* in, float* out, uint64_t
     }
     if (op == 0) return finish_scan<ovl::OpAdd>(in, out, 1, n, carry, scratch, aligned, stream);
     return finish_scan<ovl::OpMul>(in, out, 1, n, carry, scratch, aligned, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Sharded scan whose shard totals travel through peer memory instead of a collective library call.
+
+extern "C" uint64_t ovl_peer_buffer_bytes(void) { return (uint64_t)ovl::kPeerBufferWords * sizeof(uint64_t); }
+
+extern "C" int ovl_peer_alloc(void** out_ptr, unsigned char* out_handle) {
+    if (!out_ptr || !out_handle) return OVL_ERR_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == OVL_PEER_HANDLE_BYTES, "handle size");
+    void* p = nullptr;
+    OVL_CUDA(cudaMalloc(&p, ovl_peer_buffer_bytes()));
+    cudaError_t e = cudaMemset(p, 0, ovl_peer_buffer_bytes());
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        return cuda_fail(e);
+    }
+    memcpy(out_handle, &h, sizeof(h));
+    *out_ptr = p;
+    return OVL_OK;
+}
+
+extern "C" int ovl_peer_open(const unsigned char* handle, void** out_ptr) {
+    if (!handle || !out_ptr) return OVL_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    OVL_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *out_ptr = p;
+    return OVL_OK;
+}
+
+extern "C" int ovl_peer_close(void* ptr) {
+    if (!ptr) return OVL_ERR_NULL;
+    OVL_CUDA(cudaIpcCloseMemHandle(ptr));
+    return OVL_OK;
+}
+
+extern "C" int ovl_peer_free(void* ptr) {
+    if (!ptr) return OVL_ERR_NULL;
+    OVL_CUDA(cudaFree(ptr));
+    return OVL_OK;
+}
+
+namespace {
+
+int check_peer_args(int op, const float* in, uint64_t n, const void* scratch, uint64_t scratch_bytes,
+                    const OvlPeerExchange* px) {
+    if (!px) return OVL_ERR_NULL;
+    int st = check_scan_args(op, in, 1, n, nullptr, scratch, scratch_bytes);
+    if (st != OVL_OK) return st;
+    if (px->world == 0 || px->world > (uint32_t)ovl::kMaxPeers || px->rank >= px->world || px->epoch == 0)
+        return OVL_ERR_INVALID;
+    for (uint32_t p = 0; p < px->world; ++p)
+        if (!px->buffers[p] || ((uintptr_t)px->buffers[p] % 16) != 0) return OVL_ERR_NULL;
+    // only shards that the ring scan takes: longer than a tile, 16-byte aligned
+    if (!shard_uses_ring(in, n)) return OVL_ERR_ALIGNMENT;
+    return OVL_OK;
+}
+
+ovl::PeerExchange device_exchange(const OvlPeerExchange* px) {
+    ovl::PeerExchange d;
+    memset(&d, 0, sizeof(d));
+    for (uint32_t p = 0; p < px->world; ++p) d.slots[p] = reinterpret_cast<uint64_t*>(px->buffers[p]);
+    d.world = px->world;
+    d.rank = px->rank;
+    d.epoch = px->epoch;
+    return d;
+}
+
+}  // namespace
+
+extern "C" int ovl_scan_f32_begin_peer(int op, const float* in, uint64_t n, double* out_total, void* scratch,
+                                       uint64_t scratch_bytes, const OvlPeerExchange* px, void* cuda_stream) {
+    if (!out_total) return OVL_ERR_NULL;
+    int st = check_peer_args(op, in, n, scratch, scratch_bytes, px);
+    if (st != OVL_OK) return st;
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const uint64_t want = (n / 4 + ovl::kScanBlock - 1) / ovl::kScanBlock;
+    const uint64_t max_grid = (uint64_t)sm_count_cached() * 8;
+    uint32_t grid = (uint32_t)(want < max_grid ? want : max_grid);
+    if (grid == 0) grid = 1;
+    // status word of the scan and the reduction's block counter sit side by side: one clear for both
+    OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader) + 16, stream));
+    void* red = reinterpret_cast<char*>(scratch) + sizeof(ovl::ScanHeader);
+    const ovl::PeerExchange d = device_exchange(px);
+    if (op == 0) reduce_publish_f32_kernel<ovl::OpAdd><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, red, d);
+    else reduce_publish_f32_kernel<ovl::OpMul><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, red, d);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? OVL_OK : cuda_fail(e);
+}
+
+extern "C" int ovl_scan_f32_finish_peer(int op, const float* in, float* out, uint64_t n, void* scratch,
+                                        uint64_t scratch_bytes, const OvlPeerExchange* px, void* cuda_stream) {
+    if (!out) return OVL_ERR_NULL;
+    int st = check_peer_args(op, in, n, scratch, scratch_bytes, px);
+    if (st != OVL_OK) return st;
+    if (((uintptr_t)out % 16) != 0) return OVL_ERR_ALIGNMENT;
+    cudaStream_t stream = (cudaStream_t)cuda_stream;
+    const uint64_t tiles = (n + kTile - 1) / kTile;
+    uint64_t cap = (uint64_t)sm_count_cached();
+    if (cap > (uint64_t)ovl::kRingMaxGrid) cap = ovl::kRingMaxGrid;
+    const uint32_t grid = (uint32_t)(tiles < cap ? tiles : cap);
+    const size_t smem = (size_t)ovl::kRingSlots * kTile * sizeof(float) + ovl::kRingCtlBytes;
+    const void* kernel = op == 0 ? (const void*)scan_ring_peer_f32_kernel<ovl::OpAdd>
+                                 : (const void*)scan_ring_peer_f32_kernel<ovl::OpMul>;
+    OVL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader) + tiles * 16, stream));
+    ovl::PeerExchange d = device_exchange(px);
+    void* args[] = {(void*)&in, (void*)&out, (void*)&n, (void*)&scratch, (void*)&d};
+    OVL_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(ovl::kRingThreads), args, smem, stream));
+    return OVL_OK;
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -247,8 +247,9 @@ __device__ __forceinline__ f2 flog(f2 x) {
     q = fma2(q, f, splat(OVL_TOL_LQ0));
     f2 r = fma2(mul2(f, f), q, f);
     r = fma2(kf, splat(OVL_TOL_LN2), r);
+    // one test for the pair: k of a positive normal number lies in [-126, 127] (k is never NaN)
     const f2 c = sub2(kf, splat(0.5f));
-    if (!(fabsf(c.x) <= 126.5f) || !(fabsf(c.y) <= 126.5f)) {
+    if (!(fmaxf(fabsf(c.x), fabsf(c.y)) <= 126.5f)) {
         r.x = flog(x.x);
         r.y = flog(x.y);
     }
@@ -329,6 +330,10 @@ __device__ __forceinline__ f2 min2(f2 a, f2 b) { return make2(a.x < b.x ? a.x : 
 __device__ __forceinline__ f2 max2(f2 a, f2 b) { return make2(a.x > b.x ? a.x : b.x, a.y > b.y ? a.y : b.y); }
 __device__ __forceinline__ f2 neg2(f2 a) { return make2(-a.x, -a.y); }
 __device__ __forceinline__ f2 abs2(f2 a) { return make2(fabsf(a.x), fabsf(a.y)); }
+// isinf(a) && a > 0 in one comparison
+__device__ __forceinline__ f2 isposinf2(f2 a) {
+    return make2(a.x == INFINITY ? 1.0f : 0.0f, a.y == INFINITY ? 1.0f : 0.0f);
+}
 __device__ __forceinline__ f2 isinf2(f2 a) { return make2(isinf(a.x) ? 1.0f : 0.0f, isinf(a.y) ? 1.0f : 0.0f); }
 __device__ __forceinline__ f2 isnan2(f2 a) { return make2(isnan(a.x) ? 1.0f : 0.0f, isnan(a.y) ? 1.0f : 0.0f); }
 __device__ __forceinline__ f2 isfinite2(f2 a) {

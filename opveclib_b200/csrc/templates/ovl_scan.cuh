@@ -698,6 +698,66 @@ __device__ __forceinline__ void ring_peek(const uint64_t* desc, uint64_t tile, u
     asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(desc + 2 * tile) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Exchange of shard totals between the GPUs of one box through peer memory (a scan along an axis that is split
+// over several GPUs).  Every GPU owns one exchange buffer; `slots[p]` is the buffer of rank p as mapped into this
+// process (an IPC mapping for p != rank).  A buffer holds, for each of two epoch parities and each source rank,
+// two 8-byte words that carry 32 payload bits and the 32-bit epoch as a tag: a word is valid on its own when its
+// tag equals the epoch of the call, so no fence and no reset between calls is needed.  The reduction kernel of
+// rank r stores its total into slot [epoch & 1][r] of EVERY rank's buffer (plain stores over NVLink); the scan
+// kernel of every rank polls its OWN buffer (local memory) until all `world` totals of the epoch are there, and
+// folds those of the ranks before it, in rank order, into its carry.  Waiting for all ranks, not only for the
+// earlier ones, keeps any rank from running more than one call ahead of another, which is what makes two
+// parities enough.  The wait is bounded like every other wait of the ring scan.
+constexpr int kMaxPeers = 8;
+struct PeerExchange {
+    uint64_t* slots[kMaxPeers];
+    uint32_t world;
+    uint32_t rank;
+    uint32_t epoch;      // 1, 2, 3, ... (0 is the tag of a cleared buffer)
+    uint32_t pad;
+};
+constexpr uint32_t kPeerBufferWords = 2 * kMaxPeers * 2;
+
+template <typename Acc>
+__device__ __forceinline__ void peer_publish(const PeerExchange& px, Acc total) {
+    static_assert(sizeof(Acc) == 8, "totals travel as two tagged 32-bit halves");
+    uint64_t bits = 0;
+    memcpy(&bits, &total, sizeof(Acc));
+    const uint64_t tag = (uint64_t)px.epoch << 32;
+    const uint64_t w0 = tag | (bits & 0xffffffffull), w1 = tag | (bits >> 32);
+    const uint32_t at = ((px.epoch & 1u) * kMaxPeers + px.rank) * 2;
+    for (uint32_t p = 0; p < px.world; ++p)
+        asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(px.slots[p] + at), "l"(w0), "l"(w1) : "memory");
+}
+
+// called by one whole warp; returns false when the totals did not arrive within `limit` clock cycles
+template <typename Acc, class Op>
+__device__ __forceinline__ bool peer_carry(const PeerExchange& px, const int lane, const long long limit, Acc& carry) {
+    const uint64_t* mine = px.slots[px.rank] + (px.epoch & 1u) * kMaxPeers * 2;
+    uint64_t w0 = 0, w1 = 0;
+    bool have = lane >= (int)px.world;
+    const long long t0 = clock64();
+    bool all = false;
+    while (true) {
+        if (!have) {
+            asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(mine + 2 * lane) : "memory");
+            have = (uint32_t)(w0 >> 32) == px.epoch && (uint32_t)(w1 >> 32) == px.epoch;
+        }
+        all = __all_sync(0xffffffffu, have);
+        if (all || clock64() - t0 >= limit) break;
+    }
+    const uint64_t bits = (w0 & 0xffffffffull) | (w1 << 32);
+    carry = Op::template identity<Acc>();
+    for (uint32_t r = 0; r < px.rank; ++r) {
+        const uint64_t b = __shfl_sync(0xffffffffu, bits, (int)r);
+        Acc t;
+        memcpy(&t, &b, sizeof(Acc));
+        carry = Op::apply(carry, t);
+    }
+    return all;
+}
+
 // slot index and barrier phase of a role's current wave, advanced without divisions
 struct RingCursor {
     int slot;
@@ -740,7 +800,7 @@ struct RingTile {
 template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY, bool MULTI>
 __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry_in,
                                           const uint64_t lines, const uint64_t n, void* scratch,
-                                          const int withhold_block = -1) {
+                                          const int withhold_block = -1, const PeerExchange* px = nullptr) {
     constexpr int VPT = kScanVpt;
     constexpr int SW = kRingScanWarps, RW = kRingReduceWarps;
     constexpr int CPR = SW / RW;                   // chunks (one per scan warp) handled by one reduce warp
@@ -972,7 +1032,14 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         // -------------------------------------------------------------------------------------- prefix warp
         RingCursor cur;
         Acc carry = Op::template identity<Acc>();
-        if (HAS_CARRY) carry = *carry_in;
+        if (HAS_CARRY) {
+            if (px != nullptr) {
+                // the carry is the combination of the totals that the ranks before this one published
+                if (!peer_carry<Acc, Op>(*px, lane, wait_limit, carry)) ring_fail(hdr, abort_flag);
+            } else {
+                carry = *carry_in;
+            }
+        }
         // With several lines, `carry` is the reduction of the tiles before the current wave that belong to the line
         // in which the wave starts, and prefixes restart at every line start.  Which tiles of a wave belong to which
         // line follows from the positions of the wave's first tile, of this block's tile and of the next wave's
@@ -1056,9 +1123,12 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
 // Reduction of n elements to one Acc, combination order fixed by the launch shape: per-thread strided partials,
 // block tree, then the last block to finish combines the per-block partials in block order.
 // scratch: [uint32 done_counter, pad to 16 bytes][Acc partial per block]
-template <typename T, typename Acc, class Op, int VEC, bool ALIGNED>
+// With REVERSE the vectors are visited from the end of the array to its start, so that what the caches still hold
+// when the kernel ends is the START of the array - where a scan of the same array that follows begins.  `px`
+// (optional): publish the total to the GPUs of the exchange as well.
+template <typename T, typename Acc, class Op, int VEC, bool ALIGNED, bool REVERSE = false>
 __device__ __forceinline__ void reduce_all(const T* __restrict__ in, const uint64_t n, Acc* __restrict__ out_total,
-                                           void* scratch) {
+                                           void* scratch, const PeerExchange* px = nullptr) {
     constexpr int BLOCK = kScanBlock;
     __shared__ Acc s_part[BLOCK / 32];
     __shared__ bool s_last;
@@ -1075,14 +1145,14 @@ __device__ __forceinline__ void reduce_all(const T* __restrict__ in, const uint6
     for (; g + 3 * stride < nvec; g += 4 * stride) {
         Vec<T, VEC> v[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) v[u] = load_vec<T, VEC>(in + (g + u * stride) * VEC);
+        for (int u = 0; u < 4; ++u) v[u] = load_vec<T, VEC>(in + (REVERSE ? nvec - 1 - (g + u * stride) : g + u * stride) * VEC);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
 #pragma unroll
             for (int e = 0; e < VEC; ++e) acc[u] = Op::apply(acc[u], (Acc)v[u].v[e]);
     }
     for (; g < nvec; g += stride) {
-        const Vec<T, VEC> v = load_vec<T, VEC>(in + g * VEC);
+        const Vec<T, VEC> v = load_vec<T, VEC>(in + (REVERSE ? nvec - 1 - g : g) * VEC);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) acc[0] = Op::apply(acc[0], (Acc)v.v[e]);
     }
@@ -1118,6 +1188,7 @@ __device__ __forceinline__ void reduce_all(const T* __restrict__ in, const uint6
         Acc total = Op::template identity<Acc>();
         for (uint32_t b = 0; b < gridDim.x; ++b) total = Op::apply(total, *(volatile Acc*)&partials[b]);
         *out_total = total;
+        if (px != nullptr) peer_publish<Acc>(*px, total);
     }
 }
 

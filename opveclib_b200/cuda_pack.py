@@ -163,6 +163,10 @@ class PairEmitter(object):
             self.put('const ' + decl + self.fresh(node) + ' = ' + rhs + ';')
         elif k == 'binary':
             fn = node.attr['fn']
+            whole = self._positive_infinity_test(node)
+            if whole is not None:
+                self.put('const ' + decl + self.fresh(node) + ' = ' + _T + 'isposinf2(' + self.name(whole) + ');')
+                return
             x, y = self.name(node.args[0]), self.name(node.args[1])
             if fn in _ARITH:
                 rhs = _T + _ARITH[fn] + '(' + x + ', ' + y + ')'
@@ -172,6 +176,25 @@ class PairEmitter(object):
             self.put('const ' + decl + self.fresh(node) + ' = ' + rhs + ';')
         else:
             raise NotImplementedError(k)
+
+    @staticmethod
+    def _positive_infinity_test(node):
+        """``v`` when the node is ``logical_and(isinf(v), v > 0)`` (either order) - the guard the example operators
+        put in front of their formulas - which is the single comparison ``v == +inf``."""
+        if node.attr['fn'] != 'and':
+            return None
+
+        def source(n):          # through same-type copies of a variable or value
+            while n.kind == 'cast' and n.args[0].kind != 'const' and n.args[0].dtype == n.dtype:
+                n = n.args[0]
+            return n
+        for a, b in (node.args, node.args[::-1]):
+            if a.kind == 'unary' and a.attr['fn'] == 'isinf' and b.kind == 'binary' and b.attr['fn'] == 'gt':
+                zero = b.args[1]
+                if zero.kind == 'cast' and zero.args[0].kind == 'const' and zero.args[0].attr['value'] == 0 and \
+                        source(a.args[0]) is source(b.args[0]):
+                    return a.args[0]
+        return None
 
     _PURE = ('const', 'read', 'cast', 'unary', 'binary', 'limit')
 

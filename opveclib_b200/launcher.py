@@ -19,13 +19,21 @@ class OvlKernelSpec(ctypes.Structure):
 
 
 KERNEL_COOPERATIVE = 1
+PEER_HANDLE_BYTES = 64
+MAX_PEERS = 8
+
+
+class OvlPeerExchange(ctypes.Structure):
+    _fields_ = [('buffers', ctypes.c_void_p * MAX_PEERS), ('world', ctypes.c_uint32), ('rank', ctypes.c_uint32),
+                ('epoch', ctypes.c_uint32)]
 
 
 EXPORTS = ['ovl_version', 'ovl_status_string', 'ovl_last_cuda_error', 'ovl_device_sm_count', 'ovl_module_load',
            'ovl_module_load_file', 'ovl_module_unload', 'ovl_kernel_create', 'ovl_kernel_destroy', 'ovl_launch',
            'ovl_profile', 'ovl_run_host', 'ovl_read_kernel_status', 'ovl_scan_f32_scratch_bytes', 'ovl_scan_f32',
            'ovl_reduce_f32_scratch_bytes', 'ovl_reduce_f32', 'ovl_scan_f32_static', 'ovl_scan_f32_static_status', 'ovl_scan_f32_begin',
-           'ovl_scan_f32_finish', 'ovl_selftest_scan_timeout']
+           'ovl_scan_f32_finish', 'ovl_selftest_scan_timeout', 'ovl_peer_buffer_bytes', 'ovl_peer_alloc',
+           'ovl_peer_open', 'ovl_peer_close', 'ovl_peer_free', 'ovl_scan_f32_begin_peer', 'ovl_scan_f32_finish_peer']
 
 _lib = None
 
@@ -79,6 +87,14 @@ def library():
     lib.ovl_scan_f32_begin.argtypes = [ctypes.c_int, vp, u64, vp, vp, u64, vp]
     lib.ovl_scan_f32_finish.argtypes = [ctypes.c_int, vp, vp, u64, vp, vp, u64, vp]
     lib.ovl_selftest_scan_timeout.argtypes = [vp, vp, u64, vp, u64, vp]
+    pxp = ctypes.POINTER(OvlPeerExchange)
+    lib.ovl_peer_buffer_bytes.restype = u64
+    lib.ovl_peer_alloc.argtypes = [ctypes.POINTER(vp), ctypes.c_char_p]
+    lib.ovl_peer_open.argtypes = [ctypes.c_char_p, ctypes.POINTER(vp)]
+    lib.ovl_peer_close.argtypes = [vp]
+    lib.ovl_peer_free.argtypes = [vp]
+    lib.ovl_scan_f32_begin_peer.argtypes = [ctypes.c_int, vp, u64, vp, vp, u64, pxp, vp]
+    lib.ovl_scan_f32_finish_peer.argtypes = [ctypes.c_int, vp, vp, u64, vp, u64, pxp, vp]
     lib.ovl_scan_f32_static.argtypes = [ctypes.c_int, vp, vp, u64, u64, vp, vp]
     lib.ovl_scan_f32_static_status.argtypes = [vp, ctypes.POINTER(i32)]
     _lib = lib

@@ -11,6 +11,12 @@ opveclib/examples/test_accumulate.py:40-41):
 3. every rank combines the totals of the ranks before it into its carry and scans its shard seeded with it
    (``ovl_scan_f32_finish``: the ring scan, one launch).
 
+On GPUs that can map each other's memory the exchange needs no collective call: the kernel of step 1 stores its
+total straight into every rank's exchange buffer (plain stores over NVLink), and the scan kernel of step 3 starts
+by waiting - bounded - for the totals of the epoch in its own buffer and folds them itself
+(``ovl_scan_f32_begin_peer`` / ``ovl_scan_f32_finish_peer``; ``exchange='peer'``).  Two kernels per step and
+nothing in between.
+
 Per element this moves 4 bytes in step 1 and 8 in step 3: a shard's total is only known after all of it has been
 read, so every shard but the first is read twice - 12 bytes per element against the 8 of the one-GPU scan.
 
@@ -57,12 +63,18 @@ def _op_code(op):
 class ShardedScan(object):
     """Inclusive cumsum / cumprod of a rank-1 fp32 tensor split contiguously over the ranks of ``group``.
 
-    Buffers (scratch, totals) are allocated once per instance; ``__call__`` enqueues the three steps on torch's
-    current stream and returns the rank's part of the result."""
+    ``exchange``: 'peer' - totals travel through peer memory inside the two kernels (needs one GPU per rank on one
+    box and 16-byte aligned shards longer than 8192 elements); 'collective' - ``all_gather`` of the totals between
+    the two kernels; 'auto' (default) - 'peer' when it can be set up, else 'collective'.
 
-    def __init__(self, shard_len, op='add', group=None, device=None):
+    Buffers (scratch, totals, exchange buffer) are allocated once per instance; ``__call__`` enqueues the steps on
+    torch's current stream and returns the rank's part of the result."""
+
+    def __init__(self, shard_len, op='add', group=None, device=None, exchange='auto'):
         import torch
         import torch.distributed as dist
+        if exchange not in ('auto', 'peer', 'collective'):
+            raise ValueError("exchange must be 'auto', 'peer' or 'collective'")
         self.torch, self.dist = torch, dist
         self.op = op
         self.code = _op_code(op)
@@ -79,9 +91,23 @@ class ShardedScan(object):
         self.total = torch.zeros(1, dtype=torch.float64, device=self.device)
         self.totals = torch.zeros(self.world, dtype=torch.float64, device=self.device)
         self.carry = torch.zeros(1, dtype=torch.float64, device=self.device)
-        # mask[r] = 1 for ranks before this one: the carry is a masked reduction of the gathered totals
-        self.before = torch.arange(self.world, device=self.device) < self.rank
         self.launches = 0
+        self.peer = None
+        self.exchange = 'collective'
+        if self.world > 1 and exchange in ('auto', 'peer'):
+            # all ranks must take the same path: agree on whether every shard qualifies and every mapping worked
+            try:
+                votes = [None] * self.world
+                dist.all_gather_object(votes, self.shard_len > 8192 and self.world <= launcher.MAX_PEERS, group=group)
+                if not all(votes):
+                    raise ValueError('the peer exchange needs shards of more than 8192 elements on at most %d ranks'
+                                     % launcher.MAX_PEERS)
+                self.peer = PeerTotals(self.world, self.rank, group, self.device)
+                self.exchange = 'peer'
+            except Exception:
+                if exchange == 'peer':
+                    raise
+                self.peer = None
 
     def __call__(self, x, out=None):
         torch = self.torch
@@ -95,17 +121,29 @@ class ShardedScan(object):
                                                  self.scan_scratch.data_ptr(), self.scan_bytes, stream), 'scan')
             self.launches += 1
             return out
+        if self.peer is not None:
+            if x.data_ptr() % 16 or out.data_ptr() % 16:
+                raise ValueError("the peer exchange needs 16-byte aligned shards: construct with exchange='collective'")
+            px = self.peer.next_epoch()
+            launcher.check(self.lib.ovl_scan_f32_begin_peer(self.code, x.data_ptr(), self.shard_len, self.total.data_ptr(),
+                                                            self.scan_scratch.data_ptr(), self.scan_bytes, px, stream),
+                           'shard total')
+            launcher.check(self.lib.ovl_scan_f32_finish_peer(self.code, x.data_ptr(), out.data_ptr(), self.shard_len,
+                                                             self.scan_scratch.data_ptr(), self.scan_bytes, px, stream),
+                           'shard scan')
+            self.launches += 2
+            return out
         # step 1: the shard total
         launcher.check(self.lib.ovl_scan_f32_begin(self.code, x.data_ptr(), self.shard_len, self.total.data_ptr(),
                                                    self.scan_scratch.data_ptr(), self.scan_bytes, stream), 'shard totals')
         # step 2: exchange, carry = combination of the totals of the ranks before this one
         self.dist.all_gather_into_tensor(self.totals, self.total, group=self.group)
-        if self.op == 'add':
-            torch.sum(torch.where(self.before, self.totals, torch.zeros_like(self.totals)), dim=0, keepdim=True,
-                      out=self.carry)
+        if self.rank == 0:
+            self.carry.fill_(0.0 if self.op == 'add' else 1.0)
+        elif self.op == 'add':
+            torch.sum(self.totals[:self.rank], dim=0, keepdim=True, out=self.carry)
         else:
-            torch.prod(torch.where(self.before, self.totals, torch.ones_like(self.totals)), dim=0, keepdim=True,
-                       out=self.carry)
+            torch.prod(self.totals[:self.rank], dim=0, keepdim=True, out=self.carry)
         # step 3: the scan of the shard, seeded with the carry
         launcher.check(self.lib.ovl_scan_f32_finish(self.code, x.data_ptr(), out.data_ptr(), self.shard_len,
                                                     self.carry.data_ptr(), self.scan_scratch.data_ptr(),
@@ -121,6 +159,59 @@ class ShardedScan(object):
                        'reading scan status')
         if status.value != 0:
             raise launcher.OvlError(status.value, 'sharded scan')
+
+
+class PeerTotals(object):
+    """The exchange buffers of a sharded scan whose totals travel through peer memory: one small device buffer per
+    rank, mapped into every other rank's process through CUDA IPC handles exchanged once over ``group``."""
+
+    def __init__(self, world, rank, group, device):
+        import torch
+        import torch.distributed as dist
+        if world > launcher.MAX_PEERS:
+            raise ValueError('at most %d ranks' % launcher.MAX_PEERS)
+        self.lib = launcher.library()
+        self.world, self.rank = world, rank
+        self.epoch = 0
+        self.own = ctypes.c_void_p()
+        self.opened = []
+        handle = ctypes.create_string_buffer(launcher.PEER_HANDLE_BYTES)
+        with torch.cuda.device(device):
+            launcher.check(self.lib.ovl_peer_alloc(ctypes.byref(self.own), handle), 'allocating the exchange buffer')
+            handles = [None] * world
+            dist.all_gather_object(handles, (rank, bytes(handle.raw)), group=group)
+            self.px = launcher.OvlPeerExchange()
+            self.px.world, self.px.rank = world, rank
+            ok = True
+            for r, h in handles:
+                if r == rank:
+                    self.px.buffers[r] = self.own.value
+                    continue
+                p = ctypes.c_void_p()
+                if self.lib.ovl_peer_open(h, ctypes.byref(p)) != 0:
+                    ok = False
+                    continue
+                self.opened.append(p)
+                self.px.buffers[r] = p.value
+            # every rank must come to the same decision
+            votes = [None] * world
+            dist.all_gather_object(votes, ok, group=group)
+            if not all(votes):
+                self.close()
+                raise RuntimeError('peer memory of another rank could not be mapped')
+
+    def next_epoch(self):
+        self.epoch += 1
+        self.px.epoch = self.epoch
+        return ctypes.byref(self.px)
+
+    def close(self):
+        for p in self.opened:
+            self.lib.ovl_peer_close(p)
+        self.opened = []
+        if self.own:
+            self.lib.ovl_peer_free(self.own)
+            self.own = ctypes.c_void_p()
 
 
 def combine_partials(partials, op='add'):

@@ -26,8 +26,10 @@ import subprocess
 import sys
 import types
 
-REFERENCE_ROOT = os.environ.get('OVL_REFERENCE_ROOT', '/root/reference')
 _HERE = os.path.dirname(os.path.abspath(__file__))
+# where the reference tree lies: OVL_REFERENCE_ROOT, else a directory `reference` beside this repository
+REFERENCE_ROOT = os.environ.get('OVL_REFERENCE_ROOT',
+                                os.path.join(os.path.dirname(os.path.dirname(_HERE)), 'reference'))
 REF_VERSION = '1.0.3-dev0'   # opveclib/local.py:18
 
 

@@ -108,6 +108,64 @@ def test_rank_emulation_begin_exchange_finish(op, world):
     np.testing.assert_allclose(np.concatenate(parts), _reference(x, op), rtol=1.3e-7, atol=0)
 
 
+@pytest.mark.parametrize('op', ['add', 'mul'])
+@pytest.mark.parametrize('world', [2, 5, 8])
+def test_rank_emulation_of_the_peer_exchange(op, world):
+    """The pair whose totals travel through exchange buffers instead of a collective, with every rank's buffer on
+    this one device: every rank's `begin` is enqueued before any rank's `finish`, so no kernel ever waits for a
+    later launch.  Three epochs in a row reuse the buffers (two parities, tagged words, no reset)."""
+    import torch
+    lib = launcher.library()
+    code = 0 if op == 'add' else 1
+    shard = 8192 * 5 + 64
+    n = shard * world
+    stream = torch.cuda.current_stream().cuda_stream
+    nwords = int(lib.ovl_peer_buffer_bytes()) // 8
+    buffers = [torch.zeros(nwords, dtype=torch.int64, device='cuda') for _ in range(world)]
+    exchanges = []
+    for r in range(world):
+        px = launcher.OvlPeerExchange()
+        px.world, px.rank = world, r
+        for q in range(world):
+            px.buffers[q] = buffers[q].data_ptr()
+        exchanges.append(px)
+    nbytes = int(lib.ovl_scan_f32_scratch_bytes(1, shard))
+    scratches = [torch.empty(nbytes, dtype=torch.uint8, device='cuda') for _ in range(world)]
+    totals = torch.zeros(world, dtype=torch.float64, device='cuda')
+    for epoch in (1, 2, 3):
+        rs = np.random.RandomState(100 * world + epoch)
+        x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.9999, 1.0001, n)).astype(np.float32)
+        shards = [torch.from_numpy(x[r * shard:(r + 1) * shard]).cuda() for r in range(world)]
+        outs = [torch.empty_like(s) for s in shards]
+        for r in range(world):
+            exchanges[r].epoch = epoch
+            launcher.check(lib.ovl_scan_f32_begin_peer(code, shards[r].data_ptr(), shard, totals[r:].data_ptr(),
+                                                       scratches[r].data_ptr(), nbytes, ctypes.byref(exchanges[r]),
+                                                       stream), 'begin')
+        for r in range(world):
+            launcher.check(lib.ovl_scan_f32_finish_peer(code, shards[r].data_ptr(), outs[r].data_ptr(), shard,
+                                                        scratches[r].data_ptr(), nbytes, ctypes.byref(exchanges[r]),
+                                                        stream), 'finish')
+        for r in range(world):
+            status = ctypes.c_int32(-1)
+            launcher.check(lib.ovl_read_kernel_status(scratches[r].data_ptr(), stream, ctypes.byref(status)), 'status')
+            assert status.value == 0
+        got = np.concatenate([o.cpu().numpy() for o in outs])
+        np.testing.assert_allclose(got, _reference(x, op), rtol=1.3e-7, atol=0)
+    # arguments the pair refuses: an unaligned shard, a short shard, epoch 0
+    bad = launcher.OvlPeerExchange()
+    bad.world, bad.rank, bad.epoch = world, 0, 0
+    for q in range(world):
+        bad.buffers[q] = buffers[q].data_ptr()
+    assert lib.ovl_scan_f32_begin_peer(code, shards[0].data_ptr(), shard, totals.data_ptr(), scratches[0].data_ptr(),
+                                       nbytes, ctypes.byref(bad), stream) == 11
+    bad.epoch = 4
+    assert lib.ovl_scan_f32_begin_peer(code, shards[0].data_ptr() + 4, shard - 1, totals.data_ptr(),
+                                       scratches[0].data_ptr(), nbytes, ctypes.byref(bad), stream) == 9
+    assert lib.ovl_scan_f32_begin_peer(code, shards[0].data_ptr(), 4096, totals.data_ptr(), scratches[0].data_ptr(),
+                                       nbytes, ctypes.byref(bad), stream) == 9
+
+
 def test_single_pass_lookback_mode_agrees_with_three_pass_mode():
     """OVL_SCAN_MODE=lookback selects the decoupled look-back kernel for lines of several tiles; it is read once
     per process, so the check runs in a child process.  Both modes accumulate in fp64 and must give the same
@@ -138,24 +196,60 @@ print('lookback ok')
     assert res.returncode == 0 and 'lookback ok' in res.stdout, res.stdout + res.stderr
 
 
-def _nccl_rank(rank, world, port, op, n, queue):
+def _nccl_rank(rank, world, port, op, n, queue, exchange='collective'):
     import torch
     import torch.distributed as dist
     os.environ['MASTER_ADDR'] = '127.0.0.1'
     os.environ['MASTER_PORT'] = str(port)
+    os.environ['NCCL_NVLS_ENABLE'] = '0'
     torch.cuda.set_device(rank)
     dist.init_process_group('nccl', rank=rank, world_size=world, device_id=torch.device('cuda', rank))
     try:
         rs = np.random.RandomState(9)
         x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.999, 1.001, n)).astype(np.float32)
         mine = np.ascontiguousarray(parallel.shard_leading_axis(x, rank, world))
-        scan = parallel.ShardedScan(mine.size, op)
-        y = scan(torch.from_numpy(mine).cuda())
+        scan = parallel.ShardedScan(mine.size, op, exchange=exchange)
+        assert scan.exchange == exchange
+        d = torch.from_numpy(mine).cuda()
+        y = scan(d)
+        for _ in range(3):              # the buffers of the exchange are reused call after call
+            y = scan(d, out=y)
         scan.check_status()
         queue.put((rank, y.cpu().numpy()))
         dist.barrier()
+        if scan.peer is not None:
+            scan.peer.close()
     finally:
         dist.destroy_process_group()
+
+
+@pytest.mark.parametrize('op', ['add', 'mul'])
+def test_two_gpus_exchange_totals_through_peer_memory(op):
+    """Two processes, one GPU each: the reduction kernel stores the shard total into both ranks' exchange
+    buffers, the scan kernel of each rank waits for both totals in its own buffer.  No collective between the two
+    kernels."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(('127.0.0.1', 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    world, n = 2, 300032
+    procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, op, n, queue, 'peer')) for r in range(world)]
+    for p in procs:
+        p.start()
+    parts = dict(queue.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0
+    rs = np.random.RandomState(9)
+    x = (rs.normal(0, 1, n) if op == 'add' else rs.uniform(0.999, 1.001, n)).astype(np.float32)
+    np.testing.assert_allclose(np.concatenate([parts[r] for r in range(world)]), _reference(x, op), rtol=1.3e-7,
+                               atol=0)
 
 
 @pytest.mark.parametrize('op', ['add', 'mul'])
