@@ -764,7 +764,9 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
         op = ns.lstm(np_inputs[0], np_inputs[1], forget_bias=0.0)
         return [op[0], op[1]]
     if workload == 'c3_stdops':
-        return cases.stdops_lstm(ns, np_inputs[0], np_inputs[1])
+        # (graph inputs come in the order the graph walk met them: tell the gates from the cell state by shape)
+        gates, cell = sorted(np_inputs, key=lambda a: -a.shape[1])
+        return cases.stdops_lstm(ns, gates, cell)
     if workload == 'c3_grad':
         op = ns.lstm_grad(np_inputs[0], np_inputs[1], np_inputs[2], np_inputs[3], forget_bias=0.0)
         return [op[0], op[1]]

@@ -337,8 +337,16 @@ __global__ void __launch_bounds__(ovl::kScanBlock) reduce_f32_kernel(const float
 template <class Op, bool HAS_CARRY, bool MULTI>
 __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
                                                                             const double* __restrict__ carry, uint64_t lines,
-                                                                            uint64_t n, void* scratch, int withhold_block) {
-    ovl::scan_ring<float, double, Op, 4, HAS_CARRY, MULTI>(in, out, carry, lines, n, scratch, withhold_block);
+                                                                            uint64_t n, void* scratch) {
+    ovl::scan_ring<float, double, Op, 4, HAS_CARRY, MULTI>(in, out, carry, lines, n, scratch);
+}
+
+// the bounded-wait self-test: block `withhold_block` keeps its aggregates to itself, waits use the short bound
+template <class Op>
+__global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_selftest_f32_kernel(const float* __restrict__ in,
+                                                                                     float* __restrict__ out, uint64_t n,
+                                                                                     void* scratch, int withhold_block) {
+    ovl::scan_ring<float, double, Op, 4, false, false, true>(in, out, nullptr, 1, n, scratch, withhold_block);
 }
 
 // the pair of a sharded scan whose totals travel through peer memory
@@ -353,7 +361,7 @@ template <class Op>
 __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_peer_f32_kernel(const float* __restrict__ in,
                                                                                  float* __restrict__ out, uint64_t n,
                                                                                  void* scratch, const ovl::PeerExchange px) {
-    ovl::scan_ring<float, double, Op, 4, true, false>(in, out, nullptr, 1, n, scratch, -1, &px);
+    ovl::scan_ring<float, double, Op, 4, true, false, false, true>(in, out, nullptr, 1, n, scratch, -1, &px);
 }
 
 template <class Op>
@@ -486,12 +494,20 @@ int launch_ring(const float* in, float* out, uint64_t lines, uint64_t n, const d
     const uint32_t grid = (uint32_t)(tiles < cap ? tiles : cap);
     const size_t smem = (size_t)ovl::kRingSlots * kTile * sizeof(float) + ovl::kRingCtlBytes;
     // (a carry is only accepted together with a single line)
+    if (withhold_block >= 0) {
+        const void* kernel = (const void*)scan_ring_selftest_f32_kernel<Op>;
+        OVL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader) + tiles * 16, stream));
+        void* args[] = {(void*)&in, (void*)&out, (void*)&n, (void*)&scratch, (void*)&withhold_block};
+        OVL_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(ovl::kRingThreads), args, smem, stream));
+        return OVL_OK;
+    }
     const void* kernel = lines > 1 ? (const void*)scan_ring_f32_kernel<Op, false, true>
                          : carry   ? (const void*)scan_ring_f32_kernel<Op, true, false>
                                    : (const void*)scan_ring_f32_kernel<Op, false, false>;
     OVL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader) + tiles * 16, stream));
-    void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&lines, (void*)&n, (void*)&scratch, (void*)&withhold_block};
+    void* args[] = {(void*)&in, (void*)&out, (void*)&carry, (void*)&lines, (void*)&n, (void*)&scratch};
     OVL_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(ovl::kRingThreads), args, smem, stream));
     return OVL_OK;
 }

@@ -10,6 +10,13 @@
 //   col_prefixes     every column: exclusive scan of its chunk totals, in place           (tiny)
 //   col_scan         every tile: running values seeded with the chunk's prefix, rounded on store
 // Accumulation is in Acc (double for floating-point data), as in the scans along the contiguous axis.
+//
+// When the tensor has enough columns, one launch does it (`col_walk`): the columns are cut into strips of C
+// neighbouring columns, and one thread block walks down ALL rows of its strip, tile after tile, with the strip's
+// running totals in registers - no block ever needs anything from another block, every element is read once and
+// written once.  Inside a block the rows of a tile are split over the warps (and, for narrow strips, over groups of
+// lanes), combined through shuffles and a few words of shared memory; the loads of the next tile are in flight
+// while the current one is scanned.
 #pragma once
 #include "ovl_scan.cuh"
 
@@ -115,6 +122,80 @@ __device__ __forceinline__ void col_prefixes(Acc* __restrict__ agg, const uint64
             }
             carry = Op::apply(carry, shfl_any(t, 31));
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// One block per strip of C columns (C a power of two, 4..32).  A warp's 32 lanes are G = 32 / C groups of C lanes:
+// lane = g * C + c owns column c of the strip and, per tile, the U consecutive rows of row-worker (warp * G + g).
+// A tile is WARPS * G * U rows.  Per tile: every lane totals its U rows, the totals are scanned across the groups of
+// the warp (shuffles) and across the warps (shared memory, double-buffered so that one barrier per tile is enough),
+// which gives every lane the value in front of its first row; it then writes its U running values.
+template <typename T, typename Acc, class Op, int C, int WARPS, int U>
+__device__ __forceinline__ void col_walk(const T* __restrict__ in, T* __restrict__ out, const uint64_t outer, const uint64_t n,
+                                         const uint64_t inner) {
+    constexpr int G = 32 / C;
+    constexpr int TILE_ROWS = WARPS * G * U;
+    __shared__ Acc s_tot[2][WARPS][C];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int c = lane % C, g = lane / C;
+    const uint64_t strips_per = (inner + C - 1) / C;
+    const uint64_t strips = outer * strips_per;
+    for (uint64_t strip = blockIdx.x; strip < strips; strip += gridDim.x) {
+        const uint64_t o = strip / strips_per;
+        const uint64_t col = (strip - o * strips_per) * C + c;
+        const bool live = col < inner;
+        const T* src = in + o * n * inner + col;
+        T* dst = out + o * n * inner + col;
+        const uint64_t my_row = (uint64_t)(warp * G + g) * U;       // first row of this lane inside a tile
+        Acc carry = Op::template identity<Acc>();                   // everything above the current tile, this column
+        T next[U];
+        auto fetch = [&](uint64_t row0) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint64_t r = row0 + my_row + u;
+                next[u] = (live && r < n) ? src[r * inner] : (T)Op::template identity<Acc>();
+            }
+        };
+        fetch(0);
+        int buf = 0;
+        for (uint64_t row0 = 0; row0 < n; row0 += TILE_ROWS, buf ^= 1) {
+            T cur[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) cur[u] = next[u];
+            if (row0 + TILE_ROWS < n) fetch(row0 + TILE_ROWS);      // the next tile travels while this one is scanned
+            Acc part = Op::template identity<Acc>();
+#pragma unroll
+            for (int u = 0; u < U; ++u) part = Op::apply(part, (Acc)cur[u]);
+            // inclusive scan of the groups' totals inside the warp (same column: lanes C apart)
+            Acc incl = part;
+#pragma unroll
+            for (int d = C; d < 32; d <<= 1) {
+                const Acc y = shfl_up_any(incl, d);
+                if (lane >= d) incl = Op::apply(y, incl);
+            }
+            if (g == G - 1) s_tot[buf][warp][c] = incl;             // the warp's total for column c
+            __syncthreads();
+            Acc seed = carry, all = carry;
+#pragma unroll
+            for (int w = 0; w < WARPS; ++w) {
+                const Acc t = s_tot[buf][w][c];
+                if (w < warp) seed = Op::apply(seed, t);
+                all = Op::apply(all, t);
+            }
+            carry = all;
+            // what lies in front of this lane's rows: the earlier warps, then the earlier groups of this warp
+            Acc before = shfl_up_any(incl, C);
+            if (g == 0) before = Op::template identity<Acc>();
+            Acc run = Op::apply(seed, before);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                run = Op::apply(run, (Acc)cur[u]);
+                const uint64_t r = row0 + my_row + u;
+                if (live && r < n) dst[r * inner] = (T)run;
+            }
+        }
+        __syncthreads();       // (the next strip starts with buffer 0 again)
     }
 }
 

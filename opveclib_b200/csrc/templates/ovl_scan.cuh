@@ -797,7 +797,9 @@ struct RingTile {
     }
 };
 
-template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY, bool MULTI>
+// SELFTEST: the bounded-wait self-test (one block withholds its aggregates; every wait uses the short bound).
+// PEER: the carry comes from the totals that all ranks published into this rank's exchange buffer (`px`).
+template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY, bool MULTI, bool SELFTEST = false, bool PEER = false>
 __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry_in,
                                           const uint64_t lines, const uint64_t n, void* scratch,
                                           const int withhold_block = -1, const PeerExchange* px = nullptr) {
@@ -815,7 +817,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
     RingCtl<Acc>* ctl = reinterpret_cast<RingCtl<Acc>*>(ring_smem + (size_t)R * TILE_BYTES);
     volatile int* abort_flag = &ctl->abort;
     // (the self-test that withholds one block's aggregates lets every wait run out: it uses a short bound)
-    const long long wait_limit = withhold_block >= 0 ? kRingSelfTestWaitCycles : kRingWaitCycles;
+    constexpr long long wait_limit = SELFTEST ? kRingSelfTestWaitCycles : kRingWaitCycles;
 
     ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
     uint64_t* desc = reinterpret_cast<uint64_t*>(hdr + 1);
@@ -967,7 +969,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
 #pragma unroll
                 for (int w = 1; w < RW; ++w) a = Op::apply(a, ctl->rpart[parity][w]);
                 // (self-test of the bounded waits: one block may be told to keep its aggregates to itself)
-                if ((int)b != withhold_block) ring_publish<Acc>(desc, tile, a);
+                if (!SELFTEST || (int)b != withhold_block) ring_publish<Acc>(desc, tile, a);
             }
         }
     } else if (wid == SW + RW) {
@@ -1033,7 +1035,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         RingCursor cur;
         Acc carry = Op::template identity<Acc>();
         if (HAS_CARRY) {
-            if (px != nullptr) {
+            if (PEER) {
                 // the carry is the combination of the totals that the ranks before this one published
                 if (!peer_carry<Acc, Op>(*px, lane, wait_limit, carry)) ring_fail(hdr, abort_flag);
             } else {

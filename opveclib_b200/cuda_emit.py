@@ -59,6 +59,8 @@ RING_MAX_GRID = 256
 # must match kColBlock / kColRows of csrc/templates/ovl_colscan.cuh
 COL_BLOCK = 256
 COL_ROWS = 64
+COL_WALK_REGS = 32            # registers a lane spends on the rows it holds per tile of the one-launch column scan
+COL_WALK_MIN_STRIPS = 148     # ... which needs at least a strip of columns per SM
 WARP_SCAN_BLOCK = 256
 WARP_SCAN_MIN_LINES = 2048     # from this many lines on, a warp scans a whole line by itself
 WARP_SCAN_MIN_AXIS = 64        # ... if the line is at least this long
@@ -537,6 +539,25 @@ def _emit_tile(kernel, info, name, params, widx_t, math='exact'):
                  'staged_writes': len(wslots)}
 
 
+def plan_column_walk(spec):
+    """Columns per strip (32, 16, 8 or 4) for the one-launch column scan, or None when the tensor has too few
+    columns to give every SM a strip of its own (the three streaming passes split the rows instead).  Wide strips
+    move whole 128-byte lines per row; narrower ones are taken only as far as needed to get a strip per SM, and never
+    below 32 bytes per row."""
+    itemsize = spec.dtype.itemsize
+    widths = [w for w in (32, 16, 8, 4) if w * itemsize >= 32]
+    strips = lambda w: spec.outer * ((spec.inner + w - 1) // w)      # noqa: E731
+    for w in widths:
+        if strips(w) >= COL_WALK_MIN_STRIPS:
+            tile_rows = (COL_BLOCK // 32) * (32 // w) * col_walk_rows(itemsize)
+            return w if spec.n * 2 >= tile_rows else None
+    return None
+
+
+def col_walk_rows(itemsize):
+    return COL_WALK_REGS // max(1, itemsize // 4)        # 32 rows of up to 4-byte elements, 16 rows of 8-byte ones
+
+
 def _reduce_across_workers(kernel, info, red):
     """Should the threads of a warp be neighbouring WORKERS of a reduction loop rather than neighbouring trips of one
     worker's loop?  Yes when the loop's reads are strided along the loop variable but contiguous along the innermost
@@ -788,7 +809,17 @@ def emit_cuda(kernel, name, math='exact', pack=True):
                         ', ' + dims + ');', '}', '']
             src += ['extern "C" __global__ void __launch_bounds__(' + str(COL_BLOCK) + ') ' + name + '_cpfx(void* scratch) {',
                     '    ovl::col_prefixes<' + acc + ', ' + op + '>(' + agg_ptr + ', ' + dims + ');', '}', '']
-            meta['scan'] = {'name': name, 'strided': True, 'aligned_variant': bool(can_align), 'block': COL_BLOCK,
+            walk = None
+            width = plan_column_walk(spec)
+            if width is not None:
+                # enough columns: one block walks down all rows of a strip of `width` columns, one launch
+                src += ['extern "C" __global__ void __launch_bounds__(' + str(COL_BLOCK) + ', 2) ' + name +
+                        '_cwalk(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0) {',
+                        '    ovl::col_walk<' + t + ', ' + acc + ', ' + op + ', ' + str(width) + ', ' + str(COL_BLOCK // 32) +
+                        ', ' + str(col_walk_rows(spec.dtype.itemsize)) + '>(in0, out0, ' + dims + ');', '}', '']
+                walk = {'symbol': name + '_cwalk', 'block': COL_BLOCK, 'width': width,
+                        'strips': spec.outer * ((spec.inner + width - 1) // width)}
+            meta['scan'] = {'name': name, 'strided': True, 'aligned_variant': bool(can_align), 'block': COL_BLOCK, 'walk': walk,
                             'tiles': tiles, 'columns': spec.outer * spec.inner,
                             'scratch_bytes': SCAN_HEADER_BYTES + spec.outer * chunks * spec.inner * acc_size,
                             'zero_bytes': SCAN_HEADER_BYTES, 'align_bytes': 16, 'lines': spec.lines, 'n': spec.n,

@@ -111,6 +111,9 @@ class KernelPlan(object):
             return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
         m = meta['scan']
         block, name = m['block'], m['name']
+        if which == 'cwalk':
+            w = m['walk']
+            return [self._make(device, w['symbol'], max(1, min(w['strips'], sms * 2)), w['block'], [0], [0], [0, 0])]
         if which in ('cscan', 'cscanu'):
             suffix = '' if which == 'cscan' else 'u'
             al = 16 if which == 'cscan' else 0
@@ -151,6 +154,8 @@ class KernelPlan(object):
     def choose(self, in_ptrs, out_ptrs):
         meta = self.meta
         if meta.get('scan') and meta['scan'].get('strided'):
+            if meta['scan'].get('walk') and os.environ.get('OVL_COLSCAN_MODE') != 'threepass':
+                return 'cwalk'
             if meta['scan']['aligned_variant'] and all(p % 16 == 0 for p in in_ptrs + out_ptrs):
                 return 'cscan'
             return 'cscanu'

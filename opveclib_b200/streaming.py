@@ -28,6 +28,7 @@ from .opgraph import GradientPlaceholder, Operator, OperatorOutput, _resolve_out
 MIN_BYTES = 32 << 20          # below this much leaf data one piece is as fast
 MAX_SLABS = 8                 # row-local graphs
 FINE_SLABS = 32               # element-local graphs
+BUFFERS = 3                   # device-side slab buffers per tensor
 _plans = {}
 
 
@@ -275,7 +276,7 @@ def _plan_element_local(output_list, dag, prog, opt_level, rows):
 
 def run(plan_, host_inputs, host_outputs, out_types, device):
     """Execute a streaming plan: ``host_inputs`` / ``host_outputs`` are numpy arrays (pinned memory makes the
-    copies asynchronous), full-size; slabs are double-buffered on the device."""
+    copies asynchronous), full-size; slabs rotate through three buffers on the device."""
     import torch
     prog = plan_['prog']
     slabs, sr = plan_['slabs'], plan_['slab_rows']
@@ -291,13 +292,16 @@ def run(plan_, host_inputs, host_outputs, out_types, device):
         s_in, s_run, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
         for s in (s_in, s_run, s_out):
             s.wait_stream(main)
-        d_in = [[torch.empty((sr,) + tuple(h.shape[1:]), dtype=h.dtype, device=dev) for h in ins_h] for _ in range(2)]
-        d_out = [[torch.empty((sr,) + tuple(h.shape[1:]), dtype=h.dtype, device=dev) for h in outs_h] for _ in range(2)]
-        loaded = [None, None]
-        computed = [None, None]
-        stored = [None, None]
+        # three slabs in flight: one travelling in, one being computed, one travelling out, whatever their order
+        d_in = [[torch.empty((sr,) + tuple(h.shape[1:]), dtype=h.dtype, device=dev) for h in ins_h]
+                for _ in range(BUFFERS)]
+        d_out = [[torch.empty((sr,) + tuple(h.shape[1:]), dtype=h.dtype, device=dev) for h in outs_h]
+                 for _ in range(BUFFERS)]
+        loaded = [None] * BUFFERS
+        computed = [None] * BUFFERS
+        stored = [None] * BUFFERS
         for i in range(slabs):
-            b = i % 2
+            b = i % BUFFERS
             lo, hi = i * sr, (i + 1) * sr
             with torch.cuda.stream(s_in):
                 if computed[b] is not None:

@@ -51,6 +51,8 @@ def workloads(ns):
         'c3_lstm_grad_512x1024': [lstm_grad[0], lstm_grad[1]],
         'c4_chain16_1x%d' % C4_SAMPLE_COLS: [cases.chain16(ns, z(1, C4_SAMPLE_COLS))],
         'c5_cumsum_%d' % C5_SAMPLE: [ns.cumsum(z(C5_SAMPLE))],
+        # the same operator traced for fp64 input: "run in fp64 and cast", the oracle of the sharded scan
+        'c5_cumsum_f64_%d' % C5_SAMPLE: [ns.cumsum(np.zeros(C5_SAMPLE, dtype=np.float64))],
     }
 
 

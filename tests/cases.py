@@ -388,6 +388,9 @@ def case_merge_graph(ns):
     return [stack3(sum0, prod0, sum1), sum0], [in0]
 
 
+_cache = {}
+
+
 def merge_ops(ns):
     """Operators of the reference's merge tests (opveclib/test/test_operator_merge.py:22-179): scans down the rows
     and along the columns with zero-seeded accumulators, a loop that overwrites its variable (so it is NOT a

@@ -1,4 +1,5 @@
-"""Scans along an axis that is not the contiguous one: warps walk down strips of columns, three passes.
+"""Scans along an axis that is not the contiguous one: a block walks down all rows of a strip of columns (one
+launch) when there is a strip per SM, else warps walk down chunks of rows in three passes.
 
 Checked against numpy (fp64 accumulation for floating-point data, wrapping integer arithmetic otherwise) on shapes
 with ragged row chunks, ragged column strips, several outer slabs, and on the shape of the reference's own timing
@@ -14,6 +15,10 @@ pytestmark = pytest.mark.gpu
 SHAPES = [((1000, 200), 0, 'float64'), ((300, 7, 33), 0, 'float32'), ((5, 400, 64), 1, 'float32'),
           ((2000, 33), 0, 'int32'), ((257, 128), 0, 'float32'), ((3, 1000, 4), 1, 'float64'), ((4096, 64), 0, 'float32'),
           ((700, 3, 5), 0, 'uint8')]
+# enough columns for the one-launch walk: ragged last strips, ragged last tiles, narrow strips (8 and 4 columns),
+# several outer slabs, an integer type
+WALK_SHAPES = [((1000, 5000), 0, 'float32', 32), ((300, 1201), 0, 'float64', 8), ((3, 500, 2000), 1, 'int32', 32),
+               ((2100, 601), 0, 'float64', 4), ((261, 4800), 0, 'float32', 32), ((6, 3000, 200), 1, 'float32', 8)]
 
 
 def _reference(x, fn, axis):
@@ -50,6 +55,33 @@ def test_scan_along_a_strided_axis(shape, axis, dtype, fn):
         np.testing.assert_array_equal(got, want)
 
 
+@pytest.mark.parametrize('fn', ['cumsum', 'cumprod'])
+@pytest.mark.parametrize('shape,axis,dtype,width', WALK_SHAPES)
+def test_one_launch_walk_down_strips_of_columns(shape, axis, dtype, width, fn):
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    rs = np.random.RandomState(sum(shape) + axis)
+    if dtype.startswith('float'):
+        x = (rs.normal(0, 1, shape) if fn == 'cumsum' else rs.uniform(0.999, 1.001, shape)).astype(dtype)
+    else:
+        x = rs.randint(-2, 3, shape).astype(dtype)
+    op = getattr(ns, fn)(x, axis=axis)
+    got = ns.ovl.evaluate([op])
+    prog, _ = runtime.compile_outputs([op])
+    plan = prog.plans[0]
+    assert plan.meta['scan']['walk'] is not None and plan.meta['scan']['walk']['width'] == width
+    if DRYRUN:
+        return
+    assert plan.last_variant == 'cwalk'
+    want = _reference(x, fn, axis)
+    if dtype == 'float32':
+        np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
+    elif dtype == 'float64':
+        np.testing.assert_allclose(got, want, rtol=1e-12, atol=1e-10)
+    else:
+        np.testing.assert_array_equal(got, want)
+
+
 @pytest.mark.skipif(DRYRUN, reason='needs a device')
 def test_unaligned_device_tensor_uses_the_scalar_variant():
     import torch
@@ -63,7 +95,7 @@ def test_unaligned_device_tensor_uses_the_scalar_variant():
     op = ns.cumsum(dx, axis=0)
     got = ns.ovl.evaluate([op]).cpu().numpy()
     prog, _ = runtime.compile_outputs([op])
-    assert prog.plans[0].last_variant == 'cscanu'
+    assert prog.plans[0].meta['scan']['walk'] is None and prog.plans[0].last_variant == 'cscanu'
     np.testing.assert_allclose(got, _reference(x, 'cumsum', 0), rtol=1.3e-7, atol=0)
 
 

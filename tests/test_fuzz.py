@@ -45,3 +45,23 @@ def test_cuda_reproduces_the_oracle_exactly(seed, opt_level):
         got, want = [got], [want]
     for i, (g, w) in enumerate(zip(got, want)):
         assert_exact(np.asarray(g), w, 'seed %d opt %d output %d' % (seed, opt_level, i))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize('seed', SEEDS)
+def test_tolerance_lowering_keeps_exact_arithmetic_exact(seed):
+    """The graphs use no division and no transcendental function, so the tolerance lowering may change nothing: its
+    packed two-element additions, subtractions and multiplications round like single ones, and conditionals turned
+    into selects pick the same values.  (Bodies of pure fp32 arithmetic take the packed path; everything else runs
+    the same code in both lowerings.)"""
+    from oracle import runner
+    ns = cases.impl()
+    outs, _ = fuzz_graphs.build(ns, seed)
+    got = ns.ovl.evaluate(outs, math='tolerance')
+    if DRYRUN:
+        return
+    want = runner.evaluate(outs)
+    if len(outs) == 1:
+        got, want = [got], [want]
+    for i, (g, w) in enumerate(zip(got, want)):
+        assert_exact(np.asarray(g), w, 'seed %d output %d (tolerance lowering)' % (seed, i))

@@ -144,8 +144,8 @@ def test_generated_scan_of_a_long_line(dtype, fn):
 
 def test_a_wait_that_nothing_satisfies_ends_with_a_status_not_a_hang():
     """The library's self-test entry point withholds one block's aggregates: every block's bounded wait expires
-    (about two seconds), the kernel returns, the status word says OVL_ERR_TIMEOUT - and the same context then
-    scans the same data correctly."""
+    (the self-test's bound is 2^27 clock cycles, about 70 ms, so that the device is not held for long), the kernel
+    returns, the status word says OVL_ERR_TIMEOUT - and the same context then scans the same data correctly."""
     import time
     import torch
     lib = launcher.library()
@@ -163,7 +163,7 @@ def test_a_wait_that_nothing_satisfies_ends_with_a_status_not_a_hang():
     launcher.check(lib.ovl_read_kernel_status(scratch.data_ptr(), stream, ctypes.byref(status)), 'status')
     elapsed = time.time() - t0
     assert status.value == 8                      # OVL_ERR_TIMEOUT
-    assert 0.2 < elapsed < 30.0
+    assert 0.02 < elapsed < 10.0
     assert lib.ovl_status_string(status.value).decode().startswith('bounded device-side wait')
     got = _scan(dx, 0).cpu().numpy()
     np.testing.assert_allclose(got, _exact(x, 0), rtol=1.3e-7, atol=0)

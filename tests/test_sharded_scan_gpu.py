@@ -117,7 +117,7 @@ def test_rank_emulation_of_the_peer_exchange(op, world):
     import torch
     lib = launcher.library()
     code = 0 if op == 'add' else 1
-    shard = 8192 * 5 + 64
+    shard = 8192 * 160 + 64          # (long enough for the scan's scratch to hold the reduction's partials too)
     n = shard * world
     stream = torch.cuda.current_stream().cuda_stream
     nwords = int(lib.ovl_peer_buffer_bytes()) // 8
@@ -238,7 +238,7 @@ def test_two_gpus_exchange_totals_through_peer_memory(op):
     s.close()
     ctx = mp.get_context('spawn')
     queue = ctx.Queue()
-    world, n = 2, 300032
+    world, n = 2, 3000064
     procs = [ctx.Process(target=_nccl_rank, args=(r, world, port, op, n, queue, 'peer')) for r in range(world)]
     for p in procs:
         p.start()
