@@ -11,8 +11,9 @@
 //   log        exponent split + degree-7 polynomial on [2/3, 4/3)     <= 2 ulp, also next to 1
 //   tanh       odd polynomial below 0.55, 1 - 2 / (exp(2x) + 1) above <= 6e-7 relative
 //
-// NaN, +-inf and zero arguments give what the exact functions give.  Subnormal arguments and results of exp and
-// of the division are flushed to zero (the approximate instructions do).  The user's own +, -, * stay separate,
+// NaN, +-inf and zero arguments give what the exact functions give.  Subnormal arguments (of log, too: its result
+// is then -inf) and subnormal results of exp and of the division count as zero (the approximate instructions flush
+// them).  The user's own +, -, * stay separate,
 // exactly rounded operations (no contraction); explicit fma appears only inside these routines, as in any libm.
 //
 // Everything exists twice: for one float, and for a pair of floats held in one 64-bit register, where additions,
@@ -109,25 +110,38 @@ __device__ __forceinline__ float flog_poly(float f, float kf) {
 }
 
 // x = 2^k * m with m in [2/3, 4/3): the bits of m, and k as 12582912 + k in float (12582912 = 1.5 * 2^23, so the
-// integer add lands in the mantissa).  For x that is not a positive normal number k falls outside [-126, 127].
-// Two of the three integer steps are multiply-adds, which run beside the logic unit instead of on it:
-// (t * 2^9) >> 32 = t >> 23, and ix - (k << 23) = ix + kb * (-2^23) because 0x4b400000 << 23 is 0 modulo 2^32.
-__device__ __forceinline__ void flog_split(float x, float& m, float& kbiased) {
+// integer add lands in the mantissa).  Returns true when x is NOT a positive normal number (zero, subnormal,
+// negative, inf, NaN): one unsigned comparison of ix - 0x00800000.
+// The two other integer steps are multiply-adds, which run beside the logic unit instead of on it:
+// with t = ix - 0x3f2aaaab (the bits of 2/3), k = t >> 23 is the high word of t * 2^9, computed from
+// ix - 0x00800000 by folding the difference of the two offsets and the 0x4b400000 into the 64-bit addend; and
+// ix - (k << 23) = ix + kb * (-2^23) because 0x4b400000 << 23 is 0 modulo 2^32.
+__device__ __forceinline__ bool flog_split(float x, float& m, float& kbiased) {
     const int ix = __float_as_int(x);
-    const int t = ix - 0x3f2aaaab;
-    int kb, im;
-    asm("mad.hi.s32 %0, %1, 512, 0x4b400000;" : "=r"(kb) : "r"(t));
+    const int t2 = ix - 0x00800000;
+    long long wide;
+    // -(0x3eaaaaab * 512) + (0x4b400000 << 32)
+    asm("mad.wide.s32 %0, %1, 512, %2;" : "=l"(wide) : "r"(t2), "l"(0x4b3fff82aaaaaa00ll));
+    const int kb = (int)(wide >> 32);
+    int im;
     asm("mad.lo.s32 %0, %1, -8388608, %2;" : "=r"(im) : "r"(kb), "r"(ix));
     m = __int_as_float(im);
     kbiased = __int_as_float(kb);
+    return (unsigned)t2 >= 0x7f000000u;
+}
+
+// log of an argument that is not a positive normal number: -inf for zero and (counted as zero) subnormals, +inf
+// for +inf, NaN for negative arguments and NaN (x * inf + inf gives the last three)
+__device__ __forceinline__ float flog_special(float x) {
+    return fabsf(x) < 1.17549435e-38f ? -INFINITY : __fmaf_rn(x, INFINITY, INFINITY);
 }
 
 __device__ __forceinline__ float flog(float x) {
     float m, kb;
-    flog_split(x, m, kb);
+    const bool odd = flog_split(x, m, kb);
     const float kf = kb - 12582912.0f;
     float r = flog_poly(m - 1.0f, kf);
-    if (!(fabsf(kf - 0.5f) <= 126.5f)) r = logf(x);      // zero, negative, subnormal, inf, NaN
+    if (odd) r = flog_special(x);
     return r;
 }
 
@@ -233,8 +247,8 @@ __device__ __forceinline__ f2 fexp(f2 x) {
 
 __device__ __forceinline__ f2 flog(f2 x) {
     f2 m, kb;
-    flog_split(x.x, m.x, kb.x);
-    flog_split(x.y, m.y, kb.y);
+    const bool odd_x = flog_split(x.x, m.x, kb.x);
+    const bool odd_y = flog_split(x.y, m.y, kb.y);
     const f2 kf = sub2(kb, splat(12582912.0f));
     const f2 f = sub2(m, splat(1.0f));
     f2 q = splat(OVL_TOL_LQ7);
@@ -247,11 +261,9 @@ __device__ __forceinline__ f2 flog(f2 x) {
     q = fma2(q, f, splat(OVL_TOL_LQ0));
     f2 r = fma2(mul2(f, f), q, f);
     r = fma2(kf, splat(OVL_TOL_LN2), r);
-    // one test for the pair: k of a positive normal number lies in [-126, 127] (k is never NaN)
-    const f2 c = sub2(kf, splat(0.5f));
-    if (!(fmaxf(fabsf(c.x), fabsf(c.y)) <= 126.5f)) {
-        r.x = flog(x.x);
-        r.y = flog(x.y);
+    if (odd_x | odd_y) {
+        if (odd_x) r.x = flog_special(x.x);
+        if (odd_y) r.y = flog_special(x.y);
     }
     return r;
 }

@@ -494,7 +494,11 @@ constexpr int kWarpScanVecs = 4;
 struct WarpScanShape {
     uint32_t grid, block;
 };
+constexpr uint64_t kWarpScanManyLines = 32768;
 __host__ __device__ inline WarpScanShape warp_scan_shape(uint64_t lines, uint32_t sms) {
+    // tens of thousands of (then short) lines: one line per warp in blocks of four warps, handed out by the hardware
+    // as earlier blocks finish (fp32 [131072, 512]: 0.081 ms against 0.091 ms with resident warps walking the lines)
+    if (lines >= kWarpScanManyLines) return WarpScanShape{(uint32_t)((lines + 3) / 4), 128};
     const uint32_t shapes[][2] = {{3, 7}, {4, 5}, {3, 6}, {2, 8}, {2, 7}, {3, 5}, {2, 6}, {3, 4}};   // {blocks per SM, warps}
     double best = -1.0;
     WarpScanShape pick = {1, 32};

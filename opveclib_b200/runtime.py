@@ -31,6 +31,10 @@ def warp_scan_shape(lines, sms):
     warp walks whole lines one after the other, so among the residencies the kernel's registers allow - 12 to 21
     warps per SM as two to four blocks of four to eight warps - take the one that leaves the fewest warp slots idle
     in the last round, and among equals (within 2 %) the one with the most warps."""
+    if lines >= 32768:
+        # tens of thousands of (then short) lines: one line per warp in blocks of four warps, handed out by the
+        # hardware as earlier blocks finish
+        return ((lines + 3) // 4, 128)
     best, pick = -1.0, (1, 32)
     for per_sm, warps in ((3, 7), (4, 5), (3, 6), (2, 8), (2, 7), (3, 5), (2, 6), (3, 4)):
         slots = sms * per_sm * warps
@@ -129,6 +133,7 @@ class KernelPlan(object):
                                [0], [al, al], scratch, 0)]
         if which == 'wscan':
             grid, block = warp_scan_shape(m['lines'], sms)
+
             return [self._make(device, m['warp']['symbol'], grid, block, [0], [0], [16, 16])]
         cap = sms * m['blocks_per_sm']
         scratch = m['scratch_bytes']

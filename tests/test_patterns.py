@@ -179,7 +179,7 @@ def test_what_is_not_staged():
 
 def test_warp_scan_shape_divides_the_lines_evenly():
     from opveclib_b200 import runtime
-    for lines in (2048, 4096, 5000, 10 ** 5, 2 ** 17):
+    for lines in (2048, 4096, 5000, 20000, 32767):
         grid, block = runtime.warp_scan_shape(lines, 148)
         warps = block // 32
         assert 4 <= warps <= 8 and block % 32 == 0 and 1 <= grid <= 148 * 4
@@ -187,6 +187,9 @@ def test_warp_scan_shape_divides_the_lines_evenly():
         rounds = -(-lines // slots)
         assert lines / float(rounds * slots) > 0.85
     assert runtime.warp_scan_shape(4096, 148) == (296, 224)      # two even rounds of 2072 warps
+    # tens of thousands of lines: one line per warp, four warps per block
+    assert runtime.warp_scan_shape(2 ** 17, 148) == (2 ** 15, 128)
+    assert runtime.warp_scan_shape(10 ** 5 + 1, 148) == (25001, 128)
 
 
 def test_reduction_layout_follows_the_contiguous_direction():

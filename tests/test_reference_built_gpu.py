@@ -119,6 +119,55 @@ def test_tolerance_mode_leaves_integer_and_exact_arithmetic_alone():
     assert_exact(got_i, np.cumsum(i, axis=1, dtype=np.int32), 'int scan')
 
 
+def test_packed_bodies_with_nested_and_partial_branches():
+    """Branch shapes that the packed body cannot turn into one nested select - branches that assign several
+    variables, nested chains, a chain without else, a store under a condition - are evaluated with per-worker masks.
+    Exact arithmetic only, so the result must equal the exact lowering and the CPU oracle bit for bit."""
+    from opveclib_b200 import runtime
+    from oracle import runner
+    ns = cases.impl()
+    ovl = ns.ovl
+
+    @ovl.operator()
+    def tangle(a, b):
+        out = ovl.output_like(a)
+        side = ovl.output_like(a)
+        pos = ovl.position_in(a.shape)
+        p = ovl.variable(0, a.dtype)
+        q = ovl.variable(1, a.dtype)
+        with ovl.if_(a[pos] > b[pos]):
+            p <<= a[pos] - b[pos]
+            q <<= a[pos] * 2.0
+            with ovl.if_(a[pos] > 1.0):
+                p <<= p + 0.25
+            with ovl.elif_(b[pos] < -1.0):
+                q <<= q - b[pos]
+        with ovl.elif_(a[pos] < -0.5):
+            p <<= b[pos] * b[pos]
+        with ovl.if_(ovl.logical_or(p > 2.0, q < 0.0)):
+            side[pos] = p * q
+        with ovl.else_():
+            side[pos] = ovl.minimum(p, q) - ovl.maximum(a[pos], b[pos])
+        out[pos] = p + q * 0.5
+        return out, side
+
+    rs = np.random.RandomState(4)
+    a = rs.uniform(-2, 2, (3, 4096)).astype(np.float32)
+    b = rs.uniform(-2, 2, (3, 4096)).astype(np.float32)
+    op = tangle(a, b)
+    outs = [op[0], op[1]]
+    exact = ns.ovl.evaluate(outs, math='exact')
+    packed = ns.ovl.evaluate(outs, math='tolerance')
+    prog, _ = runtime.compile_outputs(outs, math='tolerance')
+    assert prog.plans[0].meta['vec']['paired']
+    if DRYRUN:
+        return
+    want = runner.evaluate(outs)
+    for k in range(2):
+        assert_exact(exact[k], want[k], 'exact lowering output %d' % k)
+        assert_exact(packed[k], want[k], 'packed body output %d' % k)
+
+
 def test_tolerance_mode_special_values():
     """Zero, negative, infinite, NaN and subnormal arguments: log, exp, tanh and the division give what the exact
     functions give, except that subnormal arguments and results count as zero."""
