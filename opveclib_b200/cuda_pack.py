@@ -4,9 +4,11 @@ A vectorised fp32 kernel gives each thread four consecutive workers.  When the b
 arithmetic - every tensor access hoisted into the group's vector loads and stores, no loops, no worker-local
 tensors, no integer values that feed results - the four workers can be evaluated as two pairs whose additions,
 multiplications and fused multiply-adds are single ``*.f32x2`` instructions (``ovl::tol::f2`` in
-csrc/templates/ovl_fastmath.cuh).  Conditionals become masks: every branch of an ``if_/elif_/else_`` chain is
-evaluated for both workers of a pair, and assignments inside it keep the old value where the branch's condition
-does not hold - which leaves results unchanged because branches may only assign variables and hoisted outputs.
+csrc/templates/ovl_fastmath.cuh).  Conditionals lose their branches: every branch of an ``if_/elif_/else_`` chain is
+evaluated for both workers of a pair.  A chain whose branches do nothing but assign one and the same variable (or
+output) becomes one nested select, ``c0 ? v0 : (c1 ? v1 : ...)``; in any other chain the assignments keep the old
+value where the branch's condition does not hold for a worker (masks).  Results are unchanged either way because
+branches may only assign variables and hoisted outputs.
 
 ``plan_pairs`` decides whether a kernel qualifies; ``PairEmitter`` writes the body.  Statement order, operand
 types and rounding points are those of the scalar body (opveclib/expression.py:559-566 and the per-node
@@ -47,7 +49,7 @@ def plan_pairs(kernel, plan):
 
     for node in iter_nodes(kernel.body):
         k = node.kind
-        if k in ('for', 'local', 'const_tensor'):
+        if k in ('for', 'local'):       # (constant tensors only ever initialise worker-local tensors)
             return None
         if k == 'assign_tensor':
             if id(node) not in hoisted_writes:
@@ -63,12 +65,12 @@ def plan_pairs(kernel, plan):
     while stack:
         node = stack.pop()
         k = node.kind
+        if not _is_f32(node):
+            return None
         if k == 'read':
             if id(node) not in hoisted_reads:
                 return None
             continue
-        if not _is_f32(node):
-            return None
         if k in ('variable', 'cast'):
             src = node.args[0]
             if src.kind == 'const':

@@ -1,4 +1,4 @@
-"""Parity at the full BASELINE sizes.
+"""Parity at the full sizes of the benchmark configurations.
 
 Where the CPU oracle finishes in seconds (configs 1 and 3) the whole result is compared with it.  For the
 configurations that are too large for that, properties that do not depend on the size are checked on the full
@@ -130,7 +130,7 @@ def test_config5_full_size_scan_properties_and_sharding():
         worst_loose = max(worst_loose, float((err - 1e-5 * ref.abs()).max()))
         worst_tight = max(worst_tight, float((err - 6.0e-8 * ref.abs()).max()))
         del ref, err
-    assert worst_loose <= 1e-6, worst_loose          # BASELINE tolerance: rtol 1e-5 against the fp64 run
+    assert worst_loose <= 1e-6, worst_loose          # stated tolerance: rtol 1e-5 against the fp64 run
     assert worst_tight <= 1e-6, worst_tight          # in fact the fp64 result rounded once to fp32
     # first differences give the input back (to the rounding of the two neighbours)
     i = torch.randint(1, n, (1 << 22,), device='cuda', generator=gen)

@@ -1,5 +1,5 @@
 """The CUDA path against the REFERENCE-BUILT CPU operators (oracle/_ref: C++ emitted by the reference's own tracer,
-merger and generator, compiled against its headers) at the BASELINE sizes, in both math lowerings.
+merger and generator, compiled against its headers) at the sizes of the benchmark configurations, in both math lowerings.
 
 exact       integer work and data movement bit-exact; transcendental chains within rtol 1e-5 (floor 1e-6 * max|ref|
             where the reference value comes from a cancellation) and at least 99.5 % of the elements inside the
@@ -206,7 +206,7 @@ def test_tolerance_mode_special_values():
 
 def test_operator_library_lstm_is_one_vectorised_kernel():
     """The LSTM cell composed from the operator library (split, sigmoid, tanh, mul, add: the graph of
-    opveclib/test/test_operator_merge.py:311-321) at BASELINE config 3's size fuses into ONE kernel that takes the
+    opveclib/test/test_operator_merge.py:311-321) at the size of benchmark configuration 3 fuses into ONE kernel that takes the
     vectorised path - the hand-fused cell's kernel shape - and agrees with the CPU oracle."""
     from opveclib_b200 import runtime
     from oracle import runner
