@@ -211,3 +211,24 @@ def test_generated_scan_of_several_long_lines_along_the_last_axis():
     assert plan.meta['scan']['ring'] is not None and plan.last_variant == 'ring'
     want = np.cumsum(x.astype(np.float64), axis=2).astype(np.float32)
     np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
+
+
+@pytest.mark.parametrize('lines,n', [(32768, 64), (40001, 100), (70000, 512)])
+def test_tens_of_thousands_of_short_lines(lines, n):
+    """From 32768 lines on the warp-per-line kernel is launched with one line per warp in blocks of four warps (the
+    hardware hands out blocks as earlier ones finish) instead of resident warps that walk the lines: through the
+    C entry point and through a generated cumsum."""
+    import torch
+    from opveclib_b200 import runtime
+    rs = np.random.RandomState(lines % 1000 + n)
+    x = rs.normal(0, 1, (lines, n)).astype(np.float32)
+    want = np.cumsum(x.astype(np.float64), axis=1).astype(np.float32)
+    got = _scan_lines(torch.from_numpy(x).cuda(), 0).cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
+    ns = cases.impl()
+    op = ns.cumsum(x, axis=1)
+    got = ns.ovl.evaluate([op])
+    prog, _ = runtime.compile_outputs([op])
+    assert prog.plans[0].last_variant == 'wscan'
+    assert runtime.warp_scan_shape(lines, 148) == ((lines + 3) // 4, 128)
+    np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
