@@ -159,10 +159,8 @@ int ovl_scan_f32_finish(int op, const float* in, float* out, uint64_t n, const d
  * NVLink, also into *out_total); ovl_scan_f32_finish_peer scans the shard in one cooperative launch whose first
  * step waits - bounded, OVL_ERR_TIMEOUT in the scratch's status word on expiry - until the totals of all ranks of
  * this epoch have arrived in its own buffer, and combines those of the ranks before it, in rank order, into its
- * carry.  Only shards that the ring scan takes are accepted: `in` and `out` 16-byte aligned and long enough for the
- * scan's scratch to hold the reduction's per-block partials as well (ovl_scan_f32_scratch_bytes(1, n) >= 16 +
- * ovl_reduce_f32_scratch_bytes(n): about a million elements); OVL_ERR_ALIGNMENT otherwise - use the plain pair with
- * a collective then.  All ranks must call both
+ * carry.  Only shards that the ring scan takes are accepted: more than 8192 elements, `in` and `out` 16-byte
+ * aligned; OVL_ERR_ALIGNMENT otherwise - use the plain pair with a collective then.  All ranks must call both
  * functions once per epoch; kernels of different ranks wait for each other, so each rank needs its own GPU (on one
  * GPU, enqueue every rank's begin before any rank's finish). */
 #define OVL_PEER_HANDLE_BYTES 64

@@ -354,7 +354,7 @@ template <class Op>
 __global__ void __launch_bounds__(ovl::kScanBlock) reduce_publish_f32_kernel(const float* __restrict__ in, uint64_t n,
                                                                             double* __restrict__ out_total, void* scratch,
                                                                             const ovl::PeerExchange px) {
-    ovl::reduce_all<float, double, Op, 4, true, true>(in, n, out_total, scratch, &px);
+    ovl::reduce_all<float, double, Op, 4, true>(in, n, out_total, scratch, &px);
 }
 
 template <class Op>
@@ -597,10 +597,7 @@ namespace {
 // total of n elements into *out_total; `scratch` holds ovl_reduce_f32_scratch_bytes(n) bytes
 int launch_reduce(int op, const float* in, uint64_t n, double* out_total, void* scratch, cudaStream_t stream) {
     const bool aligned = ((uintptr_t)in % 16 == 0);
-    const uint64_t want = (n / 4 + ovl::kScanBlock - 1) / ovl::kScanBlock;
-    const uint64_t max_grid = (uint64_t)sm_count_cached() * 8;
-    uint32_t grid = (uint32_t)(want < max_grid ? want : max_grid);
-    if (grid == 0) grid = 1;
+    const uint32_t grid = (uint32_t)ovl::reduce_chunks(n);       // one block per chunk
     OVL_CUDA(cudaMemsetAsync(scratch, 0, 16, stream));
     if (op == 0) {
         if (aligned) reduce_f32_kernel<ovl::OpAdd, true><<<grid, ovl::kScanBlock, 0, stream>>>(in, n, out_total, scratch);
@@ -738,10 +735,7 @@ extern "C" int ovl_scan_f32_begin_peer(int op, const float* in, uint64_t n, doub
     int st = check_peer_args(op, in, n, scratch, scratch_bytes, px);
     if (st != OVL_OK) return st;
     cudaStream_t stream = (cudaStream_t)cuda_stream;
-    const uint64_t want = (n / 4 + ovl::kScanBlock - 1) / ovl::kScanBlock;
-    const uint64_t max_grid = (uint64_t)sm_count_cached() * 8;
-    uint32_t grid = (uint32_t)(want < max_grid ? want : max_grid);
-    if (grid == 0) grid = 1;
+    const uint32_t grid = (uint32_t)ovl::reduce_chunks(n);
     // status word of the scan and the reduction's block counter sit side by side: one clear for both
     OVL_CUDA(cudaMemsetAsync(scratch, 0, sizeof(ovl::ScanHeader) + 16, stream));
     void* red = reinterpret_cast<char*>(scratch) + sizeof(ovl::ScanHeader);
@@ -831,8 +825,8 @@ extern "C" int ovl_scan_f32_static_status(void* cuda_stream, int32_t* out_status
 }
 
 extern "C" uint64_t ovl_reduce_f32_scratch_bytes(uint64_t n) {
-    (void)n;
-    return 16 + (uint64_t)sm_count_cached() * 8 * sizeof(double);
+    // block counter + one partial per chunk
+    return 16 + ovl::reduce_chunks(n ? n : 1) * sizeof(double);
 }
 
 extern "C" int ovl_reduce_f32(int op, const float* in, uint64_t n, double* out_total, void* scratch, uint64_t scratch_bytes,

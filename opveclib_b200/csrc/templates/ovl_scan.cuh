@@ -1129,10 +1129,33 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
 // Reduction of n elements to one Acc, combination order fixed by the launch shape: per-thread strided partials,
 // block tree, then the last block to finish combines the per-block partials in block order.
 // scratch: [uint32 done_counter, pad to 16 bytes][Acc partial per block]
-// With REVERSE the vectors are visited from the end of the array to its start, so that what the caches still hold
-// when the kernel ends is the START of the array - where a scan of the same array that follows begins.  `px`
-// (optional): publish the total to the GPUs of the exchange as well.
-template <typename T, typename Acc, class Op, int VEC, bool ALIGNED, bool REVERSE = false>
+//
+// Every block totals ONE chunk of kReduceChunk consecutive elements (the grid is one block per chunk and the
+// hardware hands chunks to SMs as earlier blocks finish, so no SM waits behind a slow one); the block that finishes
+// last combines the per-chunk partials - all of its threads, in an order fixed by the chunk count alone, so the
+// result does not depend on which block that was or on how the blocks were scheduled.
+// (Visiting the chunks from the end of the array to its start, so that the caches would still hold the START of the
+// array for a scan that follows, was measured and is not done: the reversed walk itself runs at 5.6 TB/s against
+// 6.9 TB/s forward, more than the warm start gives back.)  `px` (optional): publish the total to the GPUs of the
+// exchange as well.
+constexpr uint64_t kReduceChunk = 1ull << 17;
+
+__host__ __device__ constexpr uint64_t reduce_chunks(uint64_t n) { return (n + kReduceChunk - 1) / kReduceChunk; }
+
+template <typename Acc, class Op, int BLOCK>
+__device__ __forceinline__ Acc block_total(Acc t, Acc* s_part) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) t = Op::apply(t, shfl_down_any(t, d));
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) s_part[wid] = t;
+    __syncthreads();
+    Acc b = Op::template identity<Acc>();
+    if (threadIdx.x == 0)
+        for (int w = 0; w < BLOCK / 32; ++w) b = Op::apply(b, s_part[w]);
+    return b;       // valid in thread 0
+}
+
+template <typename T, typename Acc, class Op, int VEC, bool ALIGNED>
 __device__ __forceinline__ void reduce_all(const T* __restrict__ in, const uint64_t n, Acc* __restrict__ out_total,
                                            void* scratch, const PeerExchange* px = nullptr) {
     constexpr int BLOCK = kScanBlock;
@@ -1141,58 +1164,48 @@ __device__ __forceinline__ void reduce_all(const T* __restrict__ in, const uint6
     uint32_t* counter = reinterpret_cast<uint32_t*>(scratch);
     Acc* partials = reinterpret_cast<Acc*>(reinterpret_cast<char*>(scratch) + 16);
 
+    const uint64_t chunks = gridDim.x;
+    const uint64_t chunk = blockIdx.x;
+    const uint64_t begin = chunk * kReduceChunk;
+    const uint64_t len = (n - begin < kReduceChunk) ? n - begin : kReduceChunk;
+    const T* src = in + begin;          // (a chunk starts on a 16-byte boundary whenever the array does)
     Acc acc[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) acc[u] = Op::template identity<Acc>();
-    const uint64_t nvec = ALIGNED ? n / VEC : 0;
-    const uint64_t stride = (uint64_t)gridDim.x * BLOCK;
-    uint64_t g = (uint64_t)blockIdx.x * BLOCK + threadIdx.x;
+    const uint64_t nvec = ALIGNED ? len / VEC : 0;
+    uint64_t g = threadIdx.x;
     // four independent vectors in flight per thread
-    for (; g + 3 * stride < nvec; g += 4 * stride) {
+    for (; g + 3 * BLOCK < nvec; g += 4 * BLOCK) {
         Vec<T, VEC> v[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) v[u] = load_vec<T, VEC>(in + (REVERSE ? nvec - 1 - (g + u * stride) : g + u * stride) * VEC);
+        for (int u = 0; u < 4; ++u) v[u] = load_vec<T, VEC>(src + (g + u * BLOCK) * VEC);
 #pragma unroll
         for (int u = 0; u < 4; ++u)
 #pragma unroll
             for (int e = 0; e < VEC; ++e) acc[u] = Op::apply(acc[u], (Acc)v[u].v[e]);
     }
-    for (; g < nvec; g += stride) {
-        const Vec<T, VEC> v = load_vec<T, VEC>(in + (REVERSE ? nvec - 1 - g : g) * VEC);
+    for (; g < nvec; g += BLOCK) {
+        const Vec<T, VEC> v = load_vec<T, VEC>(src + g * VEC);
 #pragma unroll
         for (int e = 0; e < VEC; ++e) acc[0] = Op::apply(acc[0], (Acc)v.v[e]);
     }
-    for (uint64_t i = nvec * VEC + (uint64_t)blockIdx.x * BLOCK + threadIdx.x; i < n; i += stride)
-        acc[0] = Op::apply(acc[0], (Acc)in[i]);
-    Acc t = Op::apply(Op::apply(acc[0], acc[1]), Op::apply(acc[2], acc[3]));
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-        Acc y;
-        if constexpr (sizeof(Acc) == 8) {
-            long long xx = *reinterpret_cast<long long*>(&t);
-            xx = __shfl_down_sync(0xffffffffu, xx, d);
-            y = *reinterpret_cast<Acc*>(&xx);
-        } else {
-            y = __shfl_down_sync(0xffffffffu, t, d);
-        }
-        t = Op::apply(t, y);
-    }
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    if (lane == 0) s_part[wid] = t;
-    __syncthreads();
+    for (uint64_t i = nvec * VEC + threadIdx.x; i < len; i += BLOCK) acc[0] = Op::apply(acc[0], (Acc)src[i]);
+    const Acc mine = block_total<Acc, Op, BLOCK>(Op::apply(Op::apply(acc[0], acc[1]), Op::apply(acc[2], acc[3])), s_part);
     if (threadIdx.x == 0) {
-        Acc b = Op::template identity<Acc>();
-        for (int w = 0; w < BLOCK / 32; ++w) b = Op::apply(b, s_part[w]);
-        partials[blockIdx.x] = b;
+        partials[chunk] = mine;
         __threadfence();
         const uint32_t ticket = atomicAdd(counter, 1u);
         s_last = (ticket == gridDim.x - 1);
     }
     __syncthreads();
-    if (s_last && threadIdx.x == 0) {
-        __threadfence();
-        Acc total = Op::template identity<Acc>();
-        for (uint32_t b = 0; b < gridDim.x; ++b) total = Op::apply(total, *(volatile Acc*)&partials[b]);
+    if (!s_last) return;
+    // the last block to finish: thread t folds partials t, t + BLOCK, ... (chunk order), then the threads are combined
+    __threadfence();
+    Acc t = Op::template identity<Acc>();
+    for (uint64_t c = threadIdx.x; c < chunks; c += BLOCK) t = Op::apply(t, *(volatile Acc*)&partials[c]);
+    __syncthreads();                    // (s_part is reused)
+    const Acc total = block_total<Acc, Op, BLOCK>(t, s_part);
+    if (threadIdx.x == 0) {
         *out_total = total;
         if (px != nullptr) peer_publish<Acc>(*px, total);
     }

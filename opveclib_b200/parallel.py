@@ -98,14 +98,13 @@ class ShardedScan(object):
             # all ranks must take the same path: agree on whether every shard qualifies and every mapping worked
             try:
                 votes = [None] * self.world
-                # (the pair shares the scan's scratch: it must also hold the reduction's per-block partials, which
-                # it does from about a million elements on)
+                # (the pair shares the scan's scratch, which must also hold the reduction's per-chunk partials)
                 fits = self.shard_len > 8192 and \
                     self.scan_bytes >= 16 + int(lib.ovl_reduce_f32_scratch_bytes(self.shard_len))
                 dist.all_gather_object(votes, fits and self.world <= launcher.MAX_PEERS, group=group)
                 if not all(votes):
-                    raise ValueError('the peer exchange needs shards of about a million elements or more on at most '
-                                     '%d ranks' % launcher.MAX_PEERS)
+                    raise ValueError('the peer exchange needs shards of more than 8192 elements on at most %d ranks'
+                                     % launcher.MAX_PEERS)
                 self.peer = PeerTotals(self.world, self.rank, group, self.device)
                 self.exchange = 'peer'
             except Exception:
