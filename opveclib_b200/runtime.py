@@ -18,7 +18,11 @@ from .opgraph import build_op_dag
 
 _programs = {}
 _DRYRUN = 'OVL_B200_DRYRUN'
+# How many times the number of blocks that fit on the device at once a grid may hold (see KernelPlan._passes):
+# element-wise kernels, tile (transposed operand) kernels, reduction-loop kernels.
 GRID_ROUNDS = int(os.environ.get('OVL_GRID_ROUNDS', '16'))
+TILE_ROUNDS = int(os.environ.get('OVL_TILE_ROUNDS', '16'))
+RED_ROUNDS = int(os.environ.get('OVL_RED_ROUNDS', '4'))
 
 
 def _torch():
@@ -106,12 +110,12 @@ class KernelPlan(object):
             return [self._make(device, m['symbol'], grid, block, all_in, all_out, aligns)]
         if which == 'tile':
             m = meta['tile']
-            grid = max(1, min(m['tiles'], sms * (2048 // m['block'])))
+            grid = max(1, min(m['tiles'], sms * (2048 // m['block']) * TILE_ROUNDS))
             return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
         if which == 'red':
             m = meta['red']
             blocks = (m['items'] + m['workers_per_block'] - 1) // m['workers_per_block']
-            grid = max(1, min(blocks, sms * (2048 // m['block'])))
+            grid = max(1, min(blocks, sms * (2048 // m['block']) * RED_ROUNDS))
             return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
         m = meta['scan']
         block, name = m['block'], m['name']
