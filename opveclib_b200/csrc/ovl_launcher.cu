@@ -349,18 +349,20 @@ __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_selftest_f32_k
     ovl::scan_ring<float, double, Op, 4, false, false, true>(in, out, nullptr, 1, n, scratch, withhold_block);
 }
 
-// the pair of a sharded scan whose totals travel through peer memory
+// the pair of a sharded scan whose totals travel through peer memory (the exchange is a __grid_constant__ parameter:
+// its address can be taken without every thread copying it to local memory)
 template <class Op>
 __global__ void __launch_bounds__(ovl::kScanBlock) reduce_publish_f32_kernel(const float* __restrict__ in, uint64_t n,
                                                                             double* __restrict__ out_total, void* scratch,
-                                                                            const ovl::PeerExchange px) {
+                                                                            const __grid_constant__ ovl::PeerExchange px) {
     ovl::reduce_all<float, double, Op, 4, true>(in, n, out_total, scratch, &px);
 }
 
 template <class Op>
 __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_peer_f32_kernel(const float* __restrict__ in,
                                                                                  float* __restrict__ out, uint64_t n,
-                                                                                 void* scratch, const ovl::PeerExchange px) {
+                                                                                 void* scratch,
+                                                                                 const __grid_constant__ ovl::PeerExchange px) {
     ovl::scan_ring<float, double, Op, 4, true, false, false, true>(in, out, nullptr, 1, n, scratch, -1, &px);
 }
 

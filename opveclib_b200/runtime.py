@@ -23,6 +23,7 @@ _DRYRUN = 'OVL_B200_DRYRUN'
 GRID_ROUNDS = int(os.environ.get('OVL_GRID_ROUNDS', '16'))
 TILE_ROUNDS = int(os.environ.get('OVL_TILE_ROUNDS', '16'))
 RED_ROUNDS = int(os.environ.get('OVL_RED_ROUNDS', '4'))
+SCAN_ROUNDS = int(os.environ.get('OVL_SCAN_ROUNDS', '1'))
 
 
 def _torch():
@@ -139,7 +140,7 @@ class KernelPlan(object):
             grid, block = warp_scan_shape(m['lines'], sms)
 
             return [self._make(device, m['warp']['symbol'], grid, block, [0], [0], [16, 16])]
-        cap = sms * m['blocks_per_sm']
+        cap = sms * m['blocks_per_sm'] * SCAN_ROUNDS
         scratch = m['scratch_bytes']
         passes = []
         ring = m.get('ring')
