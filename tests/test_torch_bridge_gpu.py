@@ -69,6 +69,37 @@ def test_hand_fused_lstm_through_as_torch_and_evaluate_on_device_tensors():
     torch.testing.assert_close(out[0], rc.detach(), rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.skipif(DRYRUN, reason='needs a device')
+def test_as_torch_with_the_tolerance_lowering():
+    """``as_torch(..., math='tolerance')``: forward and backward graphs are both generated with the tolerance
+    lowering (a handle of its own: the exact graph of the same operators is untouched) and agree with torch."""
+    import torch
+    from opveclib_b200 import torch_bridge
+    ns = cases.impl()
+    rs = np.random.RandomState(6)
+    g = torch.tensor(rs.normal(size=(16, 128)).astype(np.float32), device='cuda', requires_grad=True)
+    c = torch.tensor(rs.normal(size=(16, 32)).astype(np.float32), device='cuda', requires_grad=True)
+    op = ns.lstm(g, c, forget_bias=0.0)
+    handles_before = len(torch_bridge._registry)
+    nc_exact, _ = ns.ovl.as_torch([op[0], op[1]], math='exact')
+    nc, nh = ns.ovl.as_torch([op[0], op[1]], math='tolerance')
+    # (the exact graph of these operators may have a handle from an earlier call; the tolerance one is new)
+    assert handles_before + 1 <= len(torch_bridge._registry) <= handles_before + 2
+    assert torch_bridge._registry[-1][0].math == 'tolerance'
+    assert torch_bridge._registry[-1][0].plans[0].meta['vec']['paired']
+    (nc.sum() + 2 * nh.sum()).backward()
+    g2 = g.detach().clone().requires_grad_(True)
+    c2 = c.detach().clone().requires_grad_(True)
+    ti, tj, tf, to = g2.chunk(4, dim=1)
+    rc = c2 * torch.sigmoid(tf) + torch.sigmoid(ti) * torch.tanh(tj)
+    rh = torch.tanh(rc) * torch.sigmoid(to)
+    (rc.sum() + 2 * rh.sum()).backward()
+    torch.testing.assert_close(nc.detach(), rc.detach(), rtol=1e-5, atol=2e-6)
+    torch.testing.assert_close(nc.detach(), nc_exact.detach(), rtol=1e-5, atol=2e-6)
+    torch.testing.assert_close(g.grad, g2.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(c.grad, c2.grad, rtol=1e-4, atol=1e-5)
+
+
 def test_backward_kernels_compile():
     """Cache warming for the two tests above (also runs without a device): trace, compose, fuse, compile."""
     from opveclib_b200 import runtime
