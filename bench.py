@@ -171,6 +171,9 @@ def build_graph(workload, rows_local=None, n_local=None):
     if workload == 'colscan':
         # a column scan far larger than L2: cumsum of fp32 [32768, 8192] along axis 0 (1 GiB in, 1 GiB out)
         return [ns.cumsum(z(32768, 8192), axis=0)], 32768 * 8192, 8
+    if workload == 'colscan_wide':
+        # more strips of columns than blocks fit on the device: cumsum of fp32 [8192, 32768] along axis 0
+        return [ns.cumsum(z(8192, 32768), axis=0)], 8192 * 32768, 8
     if workload == 'colsum':
         # column sums as a per-column reduction loop over the rows of fp32 [16384, 8192]: the matrix is read once
         return [cases.user_ops(ns).colsum(z(16384, 8192))], 16384 * 8192, 4
@@ -204,7 +207,7 @@ def _precompile_all(runtime, streaming):
         prog, dag = runtime.compile_outputs(outs)
         streaming.plan(outs, dag, prog, 3)          # the slab-shaped kernels of the end-to-end leg
     for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'c3_stdops', 'light16', 'matvec', 'op_tanh', 'op_exp',
-              'op_log1p', 'op_expm1', 'op_mulc', 'op_add', 'op_where', 'perf_accumulate', 'colscan', 'transpose',
+              'op_log1p', 'op_expm1', 'op_mulc', 'op_add', 'op_where', 'perf_accumulate', 'colscan', 'colscan_wide', 'transpose',
               'transpose_axpy', 'rows_short', 'colsum'):
         runtime.compile_outputs(build_graph(w)[0])
 
@@ -327,6 +330,7 @@ def workload_config(workload, n):
         'matvec': 'matrix-vector product as a per-row reduction loop, fp32 [16384, 8192] x [8192] normal(0,1)',
         'perf_accumulate': "cumsum along axis 0, fp64 [10000, 1000] uniform[0,1] (the reference's own timing harness)",
         'colscan': 'cumsum along axis 0, fp32 [32768, 8192] normal(0,1)',
+        'colscan_wide': 'cumsum along axis 0, fp32 [8192, 32768] normal(0,1)',
         'rows_short': 'cumsum along axis 1, fp32 [131072, 512] normal(0,1)',
         'colsum': 'column sums as a per-column reduction loop, fp32 [16384, 8192] normal(0,1)',
         'transpose': 'transpose of fp32 [16384, 16384] normal(0,1) written as an operator that reads its operand transposed',
@@ -339,7 +343,7 @@ def workload_config(workload, n):
     if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
         names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
-            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec', 'colscan', 'colsum', 'rows_short', 'transpose', 'transpose_axpy')
+            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec', 'colscan', 'colscan_wide', 'colsum', 'rows_short', 'transpose', 'transpose_axpy')
                                                       or workload.startswith('op_'))
             else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
 
@@ -758,7 +762,7 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
         return [cases.user_ops(ns).transpose(np_inputs[0])]
     if workload == 'transpose_axpy':
         return [cases.user_ops(ns).transpose_axpy(np_inputs[0], np_inputs[1], alpha=0.5)]
-    if workload in ('perf_accumulate', 'colscan'):
+    if workload in ('perf_accumulate', 'colscan', 'colscan_wide'):
         return [ns.cumsum(np_inputs[0], axis=0)]
     if workload == 'c3':
         op = ns.lstm(np_inputs[0], np_inputs[1], forget_bias=0.0)

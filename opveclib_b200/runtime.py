@@ -122,7 +122,8 @@ class KernelPlan(object):
         block, name = m['block'], m['name']
         if which == 'cwalk':
             w = m['walk']
-            return [self._make(device, w['symbol'], max(1, min(w['strips'], sms * 2)), w['block'], [0], [0], [0, 0])]
+            # (one block per strip: with more strips than fit at once the hardware hands them out as blocks finish)
+            return [self._make(device, w['symbol'], max(1, w['strips']), w['block'], [0], [0], [0, 0])]
         if which in ('cscan', 'cscanu'):
             suffix = '' if which == 'cscan' else 'u'
             al = 16 if which == 'cscan' else 0
