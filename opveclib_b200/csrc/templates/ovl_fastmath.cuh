@@ -10,6 +10,8 @@
 //   exp        ex2.approx of x * log2(e)                              <= 2^-22 + 6e-8 * |x| relative
 //   log        exponent split + degree-7 polynomial on [2/3, 4/3)     <= 2 ulp, also next to 1
 //   tanh       odd polynomial below 0.55, 1 - 2 / (exp(2x) + 1) above <= 6e-7 relative
+//   log10      log * log10(e)                                         <= 3 ulp
+//   sqrt       sqrt.approx                                            <= 2^-23 relative
 //
 // NaN, +-inf and zero arguments give what the exact functions give.  Subnormal arguments (of log, too: its result
 // is then -inf) and subnormal results of exp and of the division count as zero (the approximate instructions flush
@@ -35,6 +37,11 @@ namespace tol {
 __device__ __forceinline__ float mufu_rcp(float x) {
     float r;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float mufu_sqrt(float x) {
+    float r;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
     return r;
 }
 __device__ __forceinline__ float mufu_ex2(float x) {
@@ -153,6 +160,10 @@ __device__ __forceinline__ float clamp_nan(float x, float lo, float hi) {
     return r;
 }
 
+__device__ __forceinline__ float flog10(float x) { return flog(x) * 0.4342944819032518f; }
+// sqrt.approx: relative error <= 2^-23 (one ulp); -0 gives -0, negative arguments NaN, subnormal ones zero
+__device__ __forceinline__ float fsqrt(float x) { return mufu_sqrt(x); }
+
 __device__ __forceinline__ float ftanh(float x) {
 #if OVL_TOL_TANH_RATIONAL
     const float c = clamp_nan(x, -9.0f, 9.0f);
@@ -267,6 +278,9 @@ __device__ __forceinline__ f2 flog(f2 x) {
     }
     return r;
 }
+
+__device__ __forceinline__ f2 flog10(f2 x) { return mul2(flog(x), splat(0.4342944819032518f)); }
+__device__ __forceinline__ f2 fsqrt(f2 x) { return make2(mufu_sqrt(x.x), mufu_sqrt(x.y)); }
 
 __device__ __forceinline__ f2 ftanh(f2 x) {
 #if OVL_TOL_TANH_RATIONAL

@@ -39,7 +39,8 @@ _ABS_INT = {'int8': 'ovl::abs_8', 'int16': 'ovl::abs_16', 'int32': 'abs', 'int64
 _INFIX = {'add': '+', 'sub': '-', 'mul': '*', 'div': '/', 'mod': '%', 'eq': '==', 'ne': '!=', 'lt': '<',
           'le': '<=', 'gt': '>', 'ge': '>=', 'and': '&&', 'or': '||'}
 # math='tolerance': fp32 division and these fp32 functions go to csrc/templates/ovl_fastmath.cuh
-_TOLERANCE_F32 = {'exp': 'ovl::tol::fexp', 'log': 'ovl::tol::flog', 'tanh': 'ovl::tol::ftanh'}
+_TOLERANCE_F32 = {'exp': 'ovl::tol::fexp', 'log': 'ovl::tol::flog', 'tanh': 'ovl::tol::ftanh',
+                  'log10': 'ovl::tol::flog10', 'sqrt': 'ovl::tol::fsqrt'}
 MATH_MODES = ('exact', 'tolerance')
 _LIMITS = {('min_value', 'float32'): 'FLT_MIN', ('min_value', 'float64'): 'DBL_MIN',
            ('max_value', 'float32'): 'FLT_MAX', ('max_value', 'float64'): 'DBL_MAX',

@@ -21,9 +21,10 @@ _ARITH = {'add': 'add2', 'sub': 'sub2', 'mul': 'mul2', 'div': 'fdiv', 'eq': 'eq2
           'le': 'le2', 'gt': 'gt2', 'ge': 'ge2', 'and': 'and2', 'or': 'or2', 'min': 'min2', 'max': 'max2'}
 _BINARY_LIBM = {'pow': 'powf', 'atan2': 'atan2f', 'mod': 'fmodf'}
 _UNARY = {'negate': 'neg2', 'not': 'not2', 'abs': 'abs2', 'isinf': 'isinf2', 'isnan': 'isnan2',
-          'isfinite': 'isfinite2', 'exp': 'fexp', 'log': 'flog', 'tanh': 'ftanh'}
+          'isfinite': 'isfinite2', 'exp': 'fexp', 'log': 'flog', 'tanh': 'ftanh', 'log10': 'flog10',
+          'sqrt': 'fsqrt'}
 _UNARY_LIBM = {'acos': 'acosf', 'asin': 'asinf', 'atan': 'atanf', 'cos': 'cosf', 'cosh': 'coshf', 'sin': 'sinf',
-               'sinh': 'sinhf', 'tan': 'tanf', 'log10': 'log10f', 'sqrt': 'sqrtf', 'ceil': 'ceilf', 'floor': 'floorf'}
+               'sinh': 'sinhf', 'tan': 'tanf', 'ceil': 'ceilf', 'floor': 'floorf'}
 
 
 def _is_f32(node):

@@ -51,8 +51,8 @@ cuda_enabled = _detect_cuda()
 
 # ---------------------------------------------------------------------------------------------------------
 # math lowering of generated kernels: 'exact' (CUDA's libm and IEEE division: results within an ulp or two of the
-# reference's C++ operator) or 'tolerance' (fp32 division, exp, log, tanh with bounded error - division within
-# 2 ulp, the functions within rtol 1e-5 - and packed two-element arithmetic; several times fewer instructions
+# reference's C++ operator) or 'tolerance' (fp32 division, exp, log, log10, sqrt, tanh with bounded error - division
+# and sqrt within 1.8e-7 relative, the functions within rtol 1e-5 - and packed two-element arithmetic; several times fewer instructions
 # for chains of transcendentals).  The reference's own CUDA path is built with --use_fast_math
 # (opveclib/operator.py:2081); 'tolerance' is this backend's counterpart with stated bounds.
 MATH_MODES = ('exact', 'tolerance')

@@ -12,6 +12,8 @@ inline float fdiv(float n, float d) { return n / d; }
 inline float fexp(float x) { return expf(x); }
 inline float flog(float x) { return logf(x); }
 inline float ftanh(float x) { return tanhf(x); }
+inline float flog10(float x) { return log10f(x); }
+inline float fsqrt(float x) { return sqrtf(x); }
 
 struct f2 {
     float x, y;
@@ -29,6 +31,8 @@ inline f2 fdiv(f2 n, f2 d) { return make2(n.x / d.x, n.y / d.y); }
 inline f2 fexp(f2 x) { return make2(expf(x.x), expf(x.y)); }
 inline f2 flog(f2 x) { return make2(logf(x.x), logf(x.y)); }
 inline f2 ftanh(f2 x) { return make2(tanhf(x.x), tanhf(x.y)); }
+inline f2 flog10(f2 x) { return make2(log10f(x.x), log10f(x.y)); }
+inline f2 fsqrt(f2 x) { return make2(sqrtf(x.x), sqrtf(x.y)); }
 inline b2 truth(f2 v) { b2 r; r.x = v.x != 0.0f; r.y = v.y != 0.0f; return r; }
 inline b2 both(b2 a, b2 b) { b2 r; r.x = a.x && b.x; r.y = a.y && b.y; return r; }
 inline b2 andnot(b2 a, b2 b) { b2 r; r.x = a.x && !b.x; r.y = a.y && !b.y; return r; }

@@ -87,6 +87,35 @@ def test_cuda_matches_oracle_at_both_opt_levels(name, opt_level):
     _check(name, got, want, 'oracle opt%d' % opt_level)
 
 
+@pytest.mark.parametrize('name', sorted(cases.CASES))
+def test_tolerance_lowering_matches_reference_golden(name):
+    """Every shared case once more with ``math='tolerance'``: the same bounds hold - integer work, data movement,
+    scans and exactly rounded arithmetic do not change at all; division, exp, log, log10, sqrt and tanh stay inside
+    the tolerances of the transcendental cases.  (Division and sqrt are exactly rounded in the exact lowering and
+    within 1.8e-7 relative here: cases that use them outside the transcendental set are compared at rtol 1e-6.)"""
+    ns = cases.impl()
+    _, want = load_golden(name)
+    outs, _ = cases.CASES[name](ns)
+    got = ns.ovl.evaluate(outs, target_language='b200', math='tolerance')
+    if len(outs) == 1:
+        got = [got]
+    if name in cases.TRANSCENDENTAL or name in cases.SCANS or name in cases.REDUCTIONS:
+        _check(name, got, want, 'golden (tolerance lowering)')
+        return
+    if DRYRUN:
+        return
+    for i, (g, w) in enumerate(zip(got, want)):
+        g = np.asarray(g)
+        what = '%s output %d vs golden (tolerance lowering)' % (name, i)
+        if g.dtype != np.float32:
+            if g.dtype.kind == 'f':
+                assert_close(g, w, rtol=1e-12, atol=0.0, what=what)
+            else:
+                assert_exact(g, w, what)
+        else:
+            assert_close(g, w, rtol=1e-6, atol=0.0, what=what)
+
+
 @pytest.mark.parametrize('name,group', [('dot_f64_rows', 32), ('matvec_i32', 32), ('rowprod_scaled', 32),
                                         ('matvec_f32_long', 256)])
 def test_reduction_loops_run_on_the_cooperative_kernel(name, group):

@@ -177,24 +177,27 @@ def test_tolerance_mode_special_values():
     @ovl.operator()
     def probe(a, b):
         lg, ex, th, dv = ovl.output_like(a), ovl.output_like(a), ovl.output_like(a), ovl.output_like(a)
+        l10, sq = ovl.output_like(a), ovl.output_like(a)
         pos = ovl.position_in(a.shape)
         lg[pos] = ovl.log(a[pos])
         ex[pos] = ovl.exp(a[pos])
         th[pos] = ovl.tanh(a[pos])
         dv[pos] = a[pos] / b[pos]
-        return lg, ex, th, dv
+        l10[pos] = ovl.log10(a[pos])
+        sq[pos] = ovl.sqrt(a[pos])
+        return lg, ex, th, dv, l10, sq
 
     inf, nan = np.inf, np.nan
     a = np.array([0.0, -0.0, 1.0, -1.0, inf, -inf, nan, 1e-30, 3e38, 88.0, -87.0, 100.0, -104.0, 20.0, -20.0, 0.5],
                  dtype=np.float32)
     b = np.array([1.0, 1.0, 0.0, inf, 1.0, 2.0, 1.0, 1e30, 1e-30, nan, -0.0, inf, -inf, 3.0, 7.0, 0.0], dtype=np.float32)
     op = probe(a, b)
-    got = ovl.evaluate([op[0], op[1], op[2], op[3]], math='tolerance')
+    got = ovl.evaluate([op[0], op[1], op[2], op[3], op[4], op[5]], math='tolerance')
     if DRYRUN:
         return
     with np.errstate(all='ignore'):
-        want = [np.log(a), np.exp(a), np.tanh(a), a / b]
-    for name, g, w in zip(('log', 'exp', 'tanh', 'div'), got, want):
+        want = [np.log(a), np.exp(a), np.tanh(a), a / b, np.log10(a), np.sqrt(a)]
+    for name, g, w in zip(('log', 'exp', 'tanh', 'div', 'log10', 'sqrt'), got, want):
         w = w.astype(np.float32)
         assert np.array_equal(np.isnan(g), np.isnan(w)), name
         fin = np.isfinite(w) & (np.abs(w) >= 1.2e-38)
