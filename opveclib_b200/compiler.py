@@ -26,9 +26,12 @@ _lock = threading.Lock()
 
 
 def _template_stamp():
+    """Digest of everything that shapes generated code: the device templates and the emitters themselves."""
     h = hashlib.sha224()
-    for fn in sorted(os.listdir(TEMPLATE_DIR)):
-        with open(os.path.join(TEMPLATE_DIR, fn), 'rb') as f:
+    paths = [os.path.join(TEMPLATE_DIR, fn) for fn in sorted(os.listdir(TEMPLATE_DIR))]
+    paths += [os.path.join(_PKG, fn) for fn in ('cuda_emit.py', 'cuda_pack.py', 'patterns.py', 'access.py')]
+    for path in paths:
+        with open(path, 'rb') as f:
             h.update(f.read())
     return h.hexdigest()[:16]
 

@@ -592,7 +592,7 @@ def emit_cuda(kernel, name, math='exact', pack=True):
     block size and the number of loop iterations the grid should cover.
 
     ``math``: 'exact' - CUDA's libm and IEEE division, results within an ulp or two of the reference's C++
-    operator; 'tolerance' - fp32 division, exp, log and tanh from csrc/templates/ovl_fastmath.cuh (results within
+    operator; 'tolerance' - fp32 division, exp, log, log10, sqrt and tanh from csrc/templates/ovl_fastmath.cuh (results within
     rtol 1e-5, division within 2 ulp), and vectorised bodies of pure fp32 arithmetic evaluated two workers at a
     time with packed instructions (:mod:`opveclib_b200.cuda_pack`).  Integer work, data movement, fp64 and
     scans are the same in both."""
