@@ -35,7 +35,7 @@ def warp_scan_shape(lines, sms):
     """(grid, block) of the warp-per-line scan (the same rule as ``ovl::warp_scan_shape`` of the templates): every
     warp walks whole lines one after the other, so among the residencies the kernel's registers allow - 12 to 21
     warps per SM as two to four blocks of four to eight warps - take the one that leaves the fewest warp slots idle
-    in the last round, and among equals (within 2 %) the one with the most warps."""
+    in the final pass over the lines, and among equals (within 2 %) the one with the most warps."""
     if lines >= 32768:
         # tens of thousands of (then short) lines: one line per warp in blocks of four warps, handed out by the
         # hardware as earlier blocks finish
