@@ -189,6 +189,13 @@ def build_graph(workload, rows_local=None, n_local=None):
     if workload == 'matvec':
         # reduction loop per row (documentation/programming.rst:320-344): the matrix is read once, 4 B per element
         return [cases.user_ops(ns).matvec(z(16384, 8192), z(8192))], 16384 * 8192, 4
+    if workload == 'dot_long':
+        # ONE dot product of 2^28 terms (matvec with a single row): the loop is cut into slices that many blocks
+        # fold; 1 GiB + 1 GiB, every element read once
+        return [cases.user_ops(ns).matvec(z(1, 1 << 28), z(1 << 28))], 2 << 28, 4
+    if workload == 'colsum_narrow':
+        # column sums of fp32 [2^22, 64]: two groups of 32 columns, the rows cut into slices for many blocks
+        return [cases.user_ops(ns).colsum(z(1 << 22, 64))], 64 << 22, 4
     raise ValueError('unknown workload ' + workload)
 
 
@@ -208,7 +215,7 @@ def _precompile_all(runtime, streaming):
         streaming.plan(outs, dag, prog, 3)          # the slab-shaped kernels of the end-to-end leg
     for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'c3_stdops', 'light16', 'matvec', 'op_tanh', 'op_exp',
               'op_log1p', 'op_expm1', 'op_mulc', 'op_add', 'op_where', 'perf_accumulate', 'colscan', 'colscan_wide', 'transpose',
-              'transpose_axpy', 'rows_short', 'colsum'):
+              'transpose_axpy', 'rows_short', 'colsum', 'dot_long', 'colsum_narrow'):
         runtime.compile_outputs(build_graph(w)[0])
 
 
@@ -333,6 +340,8 @@ def workload_config(workload, n):
         'colscan_wide': 'cumsum along axis 0, fp32 [8192, 32768] normal(0,1)',
         'rows_short': 'cumsum along axis 1, fp32 [131072, 512] normal(0,1)',
         'colsum': 'column sums as a per-column reduction loop, fp32 [16384, 8192] normal(0,1)',
+        'dot_long': 'one dot product of 2^28 terms (matvec fp32 [1, 2^28] x [2^28]), the loop split over the blocks',
+        'colsum_narrow': 'column sums of fp32 [2^22, 64] normal(0,1), rows split over the blocks',
         'transpose': 'transpose of fp32 [16384, 16384] normal(0,1) written as an operator that reads its operand transposed',
         'transpose_axpy': 'a^T * 0.5 + b, fp32 [16384, 16384] normal(0,1)',
     }
@@ -343,7 +352,7 @@ def workload_config(workload, n):
     if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
         names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
-            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec', 'colscan', 'colscan_wide', 'colsum', 'rows_short', 'transpose', 'transpose_axpy')
+            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec', 'colscan', 'colscan_wide', 'colsum', 'rows_short', 'transpose', 'transpose_axpy', 'dot_long', 'colsum_narrow')
                                                       or workload.startswith('op_'))
             else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
 
@@ -754,8 +763,11 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
         return [cases.user_ops(ns).shift_cyclic(np_inputs[0])]
     if workload == 'matvec':
         return [cases.user_ops(ns).matvec(np_inputs[0], np_inputs[1])]
-    if workload == 'colsum':
+    if workload in ('colsum', 'colsum_narrow'):
         return [cases.user_ops(ns).colsum(np_inputs[0])]
+    if workload == 'dot_long':
+        mat, vec = sorted(np_inputs, key=lambda a: -a.ndim)
+        return [cases.user_ops(ns).matvec(mat, vec)]
     if workload == 'rows_short':
         return [ns.cumsum(np_inputs[0], axis=1)]
     if workload == 'transpose':
@@ -774,6 +786,12 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
     if workload == 'c3_grad':
         op = ns.lstm_grad(np_inputs[0], np_inputs[1], np_inputs[2], np_inputs[3], forget_bias=0.0)
         return [op[0], op[1]]
+    if workload.startswith('op_'):
+        u, x = cases.user_ops(ns), np_inputs[0]
+        single = {'op_tanh': lambda: u.ew_tanh(x), 'op_exp': lambda: u.ew_exp(x), 'op_log1p': lambda: ns.log1p(x),
+                  'op_expm1': lambda: ns.expm1(x), 'op_mulc': lambda: u.ew_mulc(x, c=0.5), 'op_add': lambda: u.ew_add(x, x),
+                  'op_where': lambda: u.where_greater(x, x)}
+        return [single[workload]()]
     raise ValueError(workload)
 
 

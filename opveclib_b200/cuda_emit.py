@@ -74,6 +74,10 @@ REDUCE_BLOCK = 256
 REDUCE_BLOCK_TRIPS = 2048
 REDUCE_FEW_WORKERS = 2048
 REDUCE_ACROSS_WIDE_BELOW = 1184      # blocks of 32 workers: fewer than eight per SM get 1024 threads each
+REDUCE_SPLIT_MAX_WORKERS = 592       # block-per-worker loops of so few workers are cut into slices ...
+REDUCE_SPLIT_MIN_TRIPS = 1 << 16     # ... when they are at least this long,
+REDUCE_SPLIT_SLICE = 1 << 14         # into slices of at least this many trips
+REDUCE_SPLIT_MAX = 2048              # (at most this many per worker)
 
 
 def ctype(dtype):
@@ -567,7 +571,7 @@ def _reduce_across_workers(kernel, info, red):
     shape = kernel.workgroup_shape
     last = ('p', len(shape) - 1)
     sym = info.loop_vars.get(id(red.loop.args[0]))
-    if sym is None or shape[-1] < 32:
+    if sym is None or shape[-1] < 8:        # (rows of fewer than 32 bytes: no layout reads them well)
         return False
     in_loop = set(id(n) for n in iter_nodes(red.loop.body))
     along = across = False
@@ -721,9 +725,20 @@ def emit_cuda(kernel, name, math='exact', pack=True):
         acc_t = ctype(red.acc.dtype)
         opname = 'ovl::OpAdd' if red.op == 'add' else 'ovl::OpMul'
         ivar = em.name(red.loop.args[0])
+        # few workers with long loops: the loop of a worker is cut into slices that different blocks fold
+        if across:
+            split = (W + 31) // 32 <= REDUCE_SPLIT_MAX_WORKERS // 2 and red.n >= REDUCE_SPLIT_MIN_TRIPS // 2
+        else:
+            split = group == REDUCE_BLOCK and W <= REDUCE_SPLIT_MAX_WORKERS and red.n >= REDUCE_SPLIT_MIN_TRIPS
+        split = split and os.environ.get('OVL_RED_SPLIT') != 'off'
         em.put(acc_t + ' ovl_partial = ' + opname + '::identity<' + acc_t + '>();')
         em.put('#pragma unroll ' + ('8' if across else '4'))
-        em.put('for(' + ivar + ' = ovl_member; ' + ivar + ' < ' + str(red.n) + '; ' + ivar + ' += ' + str(group) + '){')
+        if split:
+            ivar_t = ctype(red.loop.args[0].dtype)
+            em.put('for(' + ivar + ' = (' + ivar_t + ')(ovl_lo + ovl_member); ' + ivar + ' < (' + ivar_t + ')ovl_hi; ' +
+                   ivar + ' += ' + str(group) + '){')
+        else:
+            em.put('for(' + ivar + ' = ovl_member; ' + ivar + ' < ' + str(red.n) + '; ' + ivar + ' += ' + str(group) + '){')
         em.depth += 1
         for node in red.loop.body.nodes:
             if node is red.update:
@@ -732,7 +747,65 @@ def emit_cuda(kernel, name, math='exact', pack=True):
                 em.node(node)
         em.depth -= 1
         em.put('}')
-        if across:
+        fold_cols = ['ovl_red_cols[ovl_member][ovl_tx] = %s;', '__syncthreads();']
+        if across and split:
+            col_groups = (W + 31) // 32
+            slice_min = REDUCE_SPLIT_SLICE // 4
+            max_splits = max(1, min(REDUCE_SPLIT_MAX, red.n // slice_min))
+            counter_bytes = SCAN_HEADER_BYTES + (4 * col_groups + 15) // 16 * 16
+            acc_size = red.acc.dtype.itemsize
+            fold_all = ['    ' + acc_t + ' ovl_all = ovl_red_cols[0][ovl_tx];', '    #pragma unroll',
+                        '    for (int ovl_s = 1; ovl_s < ' + str(group) + '; ++ovl_s) ovl_all = ' + opname + '::apply<' +
+                        acc_t + '>(ovl_all, ovl_red_cols[ovl_s][ovl_tx]);']
+            # every block leaves the totals of its slice (32 columns) in the column group's row of partial results;
+            # the block that delivers the last slice folds the row in slice order and finishes the 32 workers
+            for line in [fold_cols[0] % 'ovl_partial', fold_cols[1],
+                         acc_t + '* const ovl_row = reinterpret_cast<' + acc_t + '*>(reinterpret_cast<char*>(scratch) + ' +
+                         str(counter_bytes) + ') + (uint64_t)ovl_group_index * ' + str(max_splits * 32) + 'ull;',
+                         'if (ovl_member == 0) {'] + fold_all + [
+                         '    ovl_row[ovl_split * 32u + ovl_tx] = ovl_all;', '    __threadfence();', '}',
+                         '__syncthreads();',
+                         'if (threadIdx.x == 0) ovl_last = atomicAdd(reinterpret_cast<uint32_t*>(reinterpret_cast<char*>('
+                         'scratch) + ' + str(SCAN_HEADER_BYTES) + ') + ovl_group_index, 1u) == ovl_splits - 1u;',
+                         '__syncthreads();', 'if (!ovl_last) return;', '__threadfence();',
+                         acc_t + ' ovl_fold = ' + opname + '::identity<' + acc_t + '>();',
+                         'for (uint32_t ovl_s = ovl_member; ovl_s < ovl_splits; ovl_s += ' + str(group) + 'u) ovl_fold = ' +
+                         opname + '::apply<' + acc_t + '>(ovl_fold, *(volatile ' + acc_t + '*)&ovl_row[ovl_s * 32u + ovl_tx]);',
+                         fold_cols[0] % 'ovl_fold', fold_cols[1], 'if (ovl_member == 0) {'] + fold_all:
+                em.put(line)
+            em.depth += 1
+            em.put(em.name(red.acc) + ' = ' + opname + '::apply<' + acc_t + '>(' + em.name(red.acc) + ', ovl_all);')
+            em.put('if (ovl_live) {')
+            em.depth += 1
+            for node in top[at + 1:]:
+                em.node(node)
+            em.depth -= 1
+            em.put('}')
+            em.depth -= 1
+            em.put('}')
+            slice_len = '((' + str(red.n) + 'ull + ovl_splits - 1u) / ovl_splits + ' + str(group - 1) + 'ull) / ' + \
+                str(group) + 'ull * ' + str(group) + 'ull'
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(red_block) + ') ' + name + '_red(' + params +
+                    ', void* scratch) {',
+                    '    __shared__ ' + acc_t + ' ovl_red_cols[' + str(group) + '][32];',
+                    '    __shared__ bool ovl_last;',
+                    '    const uint32_t ovl_tx = threadIdx.x & 31u, ovl_member = threadIdx.x >> 5;',
+                    '    // grid = groups of 32 workers x slices of the loop',
+                    '    const uint32_t ovl_splits = gridDim.x / ' + str(col_groups) + 'u;',
+                    '    const uint32_t ovl_group_index = blockIdx.x / ovl_splits, ovl_split = blockIdx.x % ovl_splits;',
+                    '    const uint64_t ovl_len = ' + slice_len + ';',
+                    '    const uint64_t ovl_lo = (uint64_t)ovl_split * ovl_len;',
+                    '    const uint64_t ovl_hi = ovl_lo + ovl_len < ' + str(red.n) + 'ull ? ovl_lo + ovl_len : ' + str(red.n) + 'ull;',
+                    '    const ' + widx_t + ' ovl_base = (' + widx_t + ')ovl_group_index * 32u;',
+                    '    const bool ovl_live = ovl_base + ovl_tx < ' + str(W) + 'ull;',
+                    '    const ' + widx_t + ' worker_index = ovl_live ? ovl_base + ovl_tx : (' + widx_t + ')' + str(W - 1) + 'ull;',
+                    '    {'] + em.lines + ['    }', '}', '']
+            meta['red'] = {'symbol': name + '_red', 'block': red_block, 'workers_per_block': 32, 'items': W,
+                           'group': group, 'trips': red.n, 'op': red.op, 'layout': 'across',
+                           'split': {'max': max_splits, 'slice': slice_min, 'units': col_groups,
+                                     'scratch_bytes': counter_bytes + col_groups * max_splits * 32 * acc_size,
+                                     'zero_bytes': counter_bytes}}
+        elif across:
             em.put('ovl_red_cols[ovl_member][ovl_tx] = ovl_partial;')
             em.put('__syncthreads();')
             em.put('if (ovl_member == 0) {')
@@ -763,7 +836,61 @@ def emit_cuda(kernel, name, math='exact', pack=True):
                     'ull;'] + em.lines + ['    }', '}', '']
             meta['red'] = {'symbol': name + '_red', 'block': red_block, 'workers_per_block': 32, 'items': W,
                            'group': group, 'trips': red.n, 'op': red.op, 'layout': 'across'}
-    if red is not None and not across:
+    if red is not None and split and not across:
+        max_splits = max(1, min(REDUCE_SPLIT_MAX, red.n // REDUCE_SPLIT_SLICE))
+        # scratch: 16-byte header (the status word every kernel with scratch has; stays 0), one counter per worker,
+        # then the rows of partial results
+        counter_bytes = SCAN_HEADER_BYTES + (4 * W + 15) // 16 * 16
+        acc_size = red.acc.dtype.itemsize
+        # the slice's result goes to the worker's row of partial results; the block that delivers the last one folds
+        # the row in slice order (members take slices m, m + 256, ...; then the usual combination) and finishes the
+        # worker.  Which block that is does not matter to the result.
+        em.put('const ' + acc_t + ' ovl_slice = ovl::group_reduce<' + acc_t + ', ' + opname + ', ' + str(group) +
+               '>(ovl_partial, ovl_red_smem);')
+        em.put('uint32_t* const ovl_count = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(scratch) + ' +
+               str(SCAN_HEADER_BYTES) + ') + worker_index;')
+        em.put(acc_t + '* const ovl_row = reinterpret_cast<' + acc_t + '*>(reinterpret_cast<char*>(scratch) + ' +
+               str(counter_bytes) + ') + (uint64_t)worker_index * ' + str(max_splits) + 'ull;')
+        em.put('if (threadIdx.x == 0) {')
+        em.put('    ovl_row[ovl_split] = ovl_slice;')
+        em.put('    __threadfence();')
+        em.put('    ovl_last = atomicAdd(ovl_count, 1u) == ovl_splits - 1u;')
+        em.put('}')
+        em.put('__syncthreads();')
+        em.put('if (!ovl_last) return;')
+        em.put('__threadfence();')
+        em.put(acc_t + ' ovl_fold = ' + opname + '::identity<' + acc_t + '>();')
+        em.put('for (uint32_t ovl_s = ovl_member; ovl_s < ovl_splits; ovl_s += ' + str(group) + 'u) ovl_fold = ' + opname +
+               '::apply<' + acc_t + '>(ovl_fold, *(volatile ' + acc_t + '*)&ovl_row[ovl_s]);')
+        em.put(em.name(red.acc) + ' = ' + opname + '::apply<' + acc_t + '>(' + em.name(red.acc) + ', ovl::group_reduce<' +
+               acc_t + ', ' + opname + ', ' + str(group) + '>(ovl_fold, ovl_red_smem));')
+        em.put('if (ovl_member == 0) {')
+        em.depth += 1
+        for node in top[at + 1:]:
+            em.node(node)
+        em.depth -= 1
+        em.put('}')
+        slice_len = '((' + str(red.n) + 'ull + ovl_splits - 1u) / ovl_splits + ' + str(group - 1) + 'ull) / ' + \
+            str(group) + 'ull * ' + str(group) + 'ull'
+        src += ['extern "C" __global__ void __launch_bounds__(' + str(REDUCE_BLOCK) + ') ' + name + '_red(' + params +
+                ', void* scratch) {',
+                '    __shared__ ' + acc_t + ' ovl_red_smem[' + str(REDUCE_BLOCK // 32) + '];',
+                '    __shared__ bool ovl_last;',
+                '    const uint32_t ovl_member = threadIdx.x;',
+                '    // grid = workers x slices: block b folds slice b % slices of worker b / slices',
+                '    const uint32_t ovl_splits = gridDim.x / ' + str(W) + 'u;',
+                '    const ' + widx_t + ' worker_index = blockIdx.x / ovl_splits;',
+                '    const uint32_t ovl_split = blockIdx.x % ovl_splits;',
+                '    const uint64_t ovl_len = ' + slice_len + ';',
+                '    const uint64_t ovl_lo = (uint64_t)ovl_split * ovl_len;',
+                '    const uint64_t ovl_hi = ovl_lo + ovl_len < ' + str(red.n) + 'ull ? ovl_lo + ovl_len : ' + str(red.n) + 'ull;',
+                '    {'] + em.lines + ['    }', '}', '']
+        meta['red'] = {'symbol': name + '_red', 'block': REDUCE_BLOCK, 'workers_per_block': 1, 'items': W,
+                       'group': group, 'trips': red.n, 'op': red.op, 'layout': 'along',
+                       'split': {'max': max_splits, 'slice': REDUCE_SPLIT_SLICE, 'units': W,
+                                 'scratch_bytes': counter_bytes + W * max_splits * acc_size,
+                                 'zero_bytes': counter_bytes}}
+    elif red is not None and not across:
         em.put(em.name(red.acc) + ' = ' + opname + '::apply<' + acc_t + '>(' + em.name(red.acc) + ', ovl::group_reduce<' +
                acc_t + ', ' + opname + ', ' + str(group) + '>(ovl_partial, ovl_red_smem));')
         em.put('if (ovl_member == 0) {')

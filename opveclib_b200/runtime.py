@@ -115,6 +115,15 @@ class KernelPlan(object):
             return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
         if which == 'red':
             m = meta['red']
+            if m.get('split'):
+                # few workers, long loops: enough slices per worker (or per group of 32 workers) for twice the blocks
+                # that fit on the device at once (the hardware hands them out as earlier ones finish), each at least
+                # split['slice'] trips long
+                sp = m['split']
+                per_sm = 2 * (2048 // m['block'])
+                splits = max(1, min(sp['max'], (per_sm * sms + sp['units'] - 1) // sp['units'], m['trips'] // sp['slice']))
+                return [self._make(device, m['symbol'], sp['units'] * splits, m['block'], all_in, all_out,
+                                   [0] * (n_in + n_out), sp['scratch_bytes'], sp['zero_bytes'])]
             blocks = (m['items'] + m['workers_per_block'] - 1) // m['workers_per_block']
             grid = max(1, min(blocks, sms * (2048 // m['block']) * RED_ROUNDS))
             return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]

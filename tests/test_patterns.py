@@ -201,8 +201,30 @@ def test_reduction_layout_follows_the_contiguous_direction():
     assert prog.plans[0].meta['red']['layout'] == 'across' and prog.plans[0].meta['red']['workers_per_block'] == 32
     prog, _ = runtime.compile_outputs([u.matvec(np.zeros((64, 300), np.float32), np.zeros(300, np.float32))])
     assert prog.plans[0].meta['red']['layout'] == 'along'
-    prog, _ = runtime.compile_outputs([u.colsum(np.zeros((300, 16), np.float32))])      # too few columns for a warp
+    prog, _ = runtime.compile_outputs([u.colsum(np.zeros((300, 16), np.float32))])      # half a warp of columns
+    assert prog.plans[0].meta['red']['layout'] == 'across'
+    prog, _ = runtime.compile_outputs([u.colsum(np.zeros((300, 4), np.float32))])       # too few columns for a warp
     assert prog.plans[0].meta['red']['layout'] == 'along'
+
+
+def test_long_reduction_loops_of_few_workers_are_split_over_blocks():
+    """One dot product of a million terms must not run on one SM: its loop is cut into slices for many blocks, the
+    partial results meet in scratch memory behind the status header."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    u = cases.user_ops(ns)
+    prog, _ = runtime.compile_outputs([u.matvec(np.zeros((3, 1 << 20), np.float32), np.zeros(1 << 20, np.float32))])
+    red = prog.plans[0].meta['red']
+    assert red['layout'] == 'along' and red['split']['units'] == 3 and red['split']['max'] == 64
+    assert red['split']['zero_bytes'] == 32 and red['split']['scratch_bytes'] == 32 + 3 * 64 * 4
+    prog, _ = runtime.compile_outputs([u.colsum(np.zeros((1 << 17, 48), np.float32))])
+    red = prog.plans[0].meta['red']
+    assert red['layout'] == 'across' and red['split']['units'] == 2 and red['block'] == 1024
+    # many workers, or short loops: one block (or warp) per worker as before
+    prog, _ = runtime.compile_outputs([u.matvec(np.zeros((4096, 1 << 16), np.float32), np.zeros(1 << 16, np.float32))])
+    assert 'split' not in prog.plans[0].meta['red']
+    prog, _ = runtime.compile_outputs([u.matvec(np.zeros((3, 4096), np.float32), np.zeros(4096, np.float32))])
+    assert 'split' not in prog.plans[0].meta['red']
 
 
 def test_seeded_scan_needs_assignment_before_the_first_store():
