@@ -8,7 +8,10 @@
 // integer results are exactly those of the serial loop; floating-point results differ from it only by the order
 // of the additions.  Loops whose reads are strided along the loop variable but contiguous across workers (column
 // sums) get the other layout, written out by the code generator: a warp is 32 neighbouring workers, the block's warps
-// take slices of the loop and the slices meet in shared memory.
+// take slices of the loop and the slices meet in shared memory.  When the workers are too few to occupy the device
+// and their loops are long, the code generator also cuts every loop into slices for different blocks: a block leaves
+// its slice's result in the worker's row of a scratch array and takes a ticket from the worker's counter; the block
+// with the last ticket folds the row in slice order and finishes the worker.
 #pragma once
 #include "ovl_scan.cuh"
 
