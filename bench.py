@@ -1,7 +1,7 @@
 """Benchmark of the hot path: fused OVL operator graphs on B200, next to the reference's CPU operator.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--math tolerance|exact]
-                    [--workload c4|c5|c2_cumsum|c2_cumprod|c1|c1_shift|c3|c3_grad|c3_stdops|light16|matvec|perf_accumulate|colscan|colsum|rows_short|transpose|transpose_axpy|op_<name>]
+                    [--workload c4|c5|c2_cumsum|c2_cumprod|c1|c1_shift|c3|c3_grad|c3_stdops|light16|matvec|perf_accumulate|colscan|colscan_wide|colsum|colsum_narrow|dot_long|rows_short|transpose|transpose_axpy|op_<name>]
 
 Default workload (the one the headline metric is quoted on): the 16-operator fused element-wise chain over an
 fp32 tensor [8, 2^27] drawn from uniform[-2, 2], rows sharded contiguously over N GPUs with no communication
@@ -12,7 +12,8 @@ opveclib/operator.py:2081); the default run also times the 'exact' lowering and 
 After the headline workload the default run times the scan across shard boundaries (`c5`, fp32 [2^31] split over the
 same N GPUs, totals exchanged through peer memory or a collective) and reports it as ``secondary.c5``.
 The other workloads exist for profiling single kernels: `c5` is the scan across shard boundaries, `matvec` a
-per-row reduction loop, `perf_accumulate` the reference's own timing harness (fp64 [10000, 1000] cumsum along axis 0),
+per-row reduction loop, `dot_long` / `colsum_narrow` reduction loops of very few workers (one dot product of 2^28 terms,
+column sums of [2^22, 64]: the loop is cut into slices for many blocks), `perf_accumulate` the reference's own timing harness (fp64 [10000, 1000] cumsum along axis 0),
 `colscan` a column scan far larger than L2, `transpose` / `transpose_axpy` an operand read along the workgroup's
 first axis, `op_<name>` one operator of the chain on its own.
 
