@@ -341,6 +341,15 @@ __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_f32_kernel(con
     ovl::scan_ring<float, double, Op, 4, HAS_CARRY, MULTI>(in, out, carry, lines, n, scratch);
 }
 
+// several lines, each scanned by a group of blocks of its own (or by one block)
+template <class Op>
+__global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_grouped_f32_kernel(const float* __restrict__ in,
+                                                                                    float* __restrict__ out,
+                                                                                    const double* __restrict__ carry,
+                                                                                    uint64_t lines, uint64_t n, void* scratch) {
+    ovl::scan_ring<float, double, Op, 4, false, false, false, false, true>(in, out, nullptr, lines, n, scratch);
+}
+
 // the bounded-wait self-test: block `withhold_block` keeps its aggregates to itself, waits use the short bound
 template <class Op>
 __global__ void __launch_bounds__(ovl::kRingThreads, 1) scan_ring_selftest_f32_kernel(const float* __restrict__ in,
@@ -504,7 +513,11 @@ int launch_ring(const float* in, float* out, uint64_t lines, uint64_t n, const d
         OVL_CUDA(cudaLaunchCooperativeKernel(kernel, dim3(grid), dim3(ovl::kRingThreads), args, smem, stream));
         return OVL_OK;
     }
-    const void* kernel = lines > 1 ? (const void*)scan_ring_f32_kernel<Op, false, true>
+    // several lines: groups of blocks that take whole lines when that keeps the grid busy, else waves across line ends
+    const bool grouped = lines > 1 && getenv("OVL_RING_LAYOUT") == nullptr &&
+                         ovl::ring_group_efficiency(grid, lines, (n + kTile - 1) / kTile) >= ovl::kRingGroupedMinEfficiency;
+    const void* kernel = grouped   ? (const void*)scan_ring_grouped_f32_kernel<Op>
+                         : lines > 1 ? (const void*)scan_ring_f32_kernel<Op, false, true>
                          : carry   ? (const void*)scan_ring_f32_kernel<Op, true, false>
                                    : (const void*)scan_ring_f32_kernel<Op, false, false>;
     OVL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -801,9 +801,61 @@ struct RingTile {
     }
 };
 
+template <bool MULTI, bool GROUPED>
+struct RingTileOf {
+    typedef RingTile<MULTI> type;
+};
+
+// Several lines, GROUPED layout: the grid is cut into groups of `g` consecutive blocks and every group scans whole
+// lines on its own - group k takes the lines k, k + groups, k + 2 groups ... one after the other, each exactly like
+// a single line scanned by a grid of g blocks (tile t of a line belongs to member t % g; a wave is g tiles of one
+// line).  Groups never wait for each other, and a block's prefix warp gathers g aggregates instead of a whole
+// grid's; with g = 1 a block walks down its lines alone.  Tiles keep their line-by-line numbers in the scratch.
+struct RingGroupTile {
+    uint64_t line, q, tiles_per_line;
+    uint32_t member, g, groups;
+    __device__ __forceinline__ RingGroupTile(uint32_t block, uint64_t tpl, uint32_t group_size, uint32_t n_groups)
+        : line(block / group_size), q(block % group_size), tiles_per_line(tpl), member(block % group_size), g(group_size),
+          groups(n_groups) {}
+    __device__ __forceinline__ void advance() {
+        q += g;
+        if (q >= tiles_per_line) {
+            q = member;
+            line += groups;
+        }
+    }
+    __device__ __forceinline__ bool last_of_line() const { return q + 1 == tiles_per_line; }
+    __device__ __forceinline__ uint64_t first_element(uint64_t n, uint32_t tile_elems) const { return line * n + q * tile_elems; }
+    __device__ __forceinline__ uint64_t number() const { return line * tiles_per_line + q; }
+};
+
+// Blocks per group for `lines` lines of `tpl` tiles on a grid of G blocks: as many as the grid has per line, at most
+// one per tile of a line.  The share of the grid's block-time that does useful work with that layout (lines that do
+// not fill the last round of groups, blocks left over) decides whether the grouped layout is used at all.
+__host__ __device__ inline uint32_t ring_group_size(uint32_t G, uint64_t lines, uint64_t tpl) {
+    uint64_t g = lines >= G ? 1 : G / lines;
+    if (g > tpl) g = tpl;
+    return (uint32_t)(g < 1 ? 1 : g);
+}
+__host__ __device__ inline double ring_group_efficiency(uint32_t G, uint64_t lines, uint64_t tpl) {
+    const uint32_t g = ring_group_size(G, lines, tpl);
+    const uint64_t groups = G / g;
+    const uint64_t rounds = (lines + groups - 1) / groups;
+    return (double)lines / (double)(rounds * groups) * (double)(groups * g) / (double)G;
+}
+// (measured on fp32: groups that keep the whole grid busy run at 5.5 TB/s against 5.0 TB/s for waves across line
+// ends - 16 lines of 2^27, 148 lines of 2^22, 1024 lines of 2^20 - but at 86 % occupancy, 64 or 256 lines, they lose)
+constexpr double kRingGroupedMinEfficiency = 0.93;
+template <bool MULTI>
+struct RingTileOf<MULTI, true> {
+    typedef RingGroupTile type;
+};
+
 // SELFTEST: the bounded-wait self-test (one block withholds its aggregates; every wait uses the short bound).
 // PEER: the carry comes from the totals that all ranks published into this rank's exchange buffer (`px`).
-template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY, bool MULTI, bool SELFTEST = false, bool PEER = false>
+// GROUPED: several lines in the grouped layout above (MULTI must then be false: no wave crosses a line end).
+template <typename T, typename Acc, class Op, int VEC, bool HAS_CARRY, bool MULTI, bool SELFTEST = false, bool PEER = false,
+          bool GROUPED = false>
 __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restrict__ out, const Acc* __restrict__ carry_in,
                                           const uint64_t lines, const uint64_t n, void* scratch,
                                           const int withhold_block = -1, const PeerExchange* px = nullptr) {
@@ -826,9 +878,27 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
     ScanHeader* hdr = reinterpret_cast<ScanHeader*>(scratch);
     uint64_t* desc = reinterpret_cast<uint64_t*>(hdr + 1);
     const uint64_t tiles_per_line = (n + TILE - 1) / TILE;
+    static_assert(!(GROUPED && (MULTI || HAS_CARRY || SELFTEST || PEER)), "the grouped layout stands alone");
     const uint64_t total_tiles = tiles_per_line * (MULTI ? lines : 1);
     const uint32_t G = gridDim.x, b = blockIdx.x;
-    const uint32_t my_tiles = (total_tiles > b) ? (uint32_t)((total_tiles - b + G - 1) / G) : 0u;
+    // grouped layout: g blocks per group, `groups` groups, this block is member `me` of group b / g
+    const uint32_t g = GROUPED ? ring_group_size(G, lines, tiles_per_line) : G;
+    const uint32_t groups = GROUPED ? G / g : 1u;
+    const uint32_t me = GROUPED ? b % g : b;
+    uint32_t my_tiles = (total_tiles > b) ? (uint32_t)((total_tiles - b + G - 1) / G) : 0u;
+    if (GROUPED) {
+        const uint32_t group = b / g;
+        const uint64_t my_lines = (group < groups && lines > group) ? (lines - group + groups - 1) / groups : 0;
+        my_tiles = (uint32_t)(my_lines * ((tiles_per_line - me + g - 1) / g));      // (g <= tiles_per_line)
+    }
+    using Tile = typename RingTileOf<MULTI, GROUPED>::type;
+    auto first_tile = [&]() {
+        if constexpr (GROUPED) {
+            return RingGroupTile(b, tiles_per_line, g, groups);
+        } else {
+            return RingTile<MULTI>(b, tiles_per_line, G);
+        }
+    };
     const uint32_t tail = (uint32_t)(n - (tiles_per_line - 1) * TILE);   // valid elements of a line's last tile
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
 
@@ -852,7 +922,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         // warp `wid` scans chunk `wid` (32 * VPT vectors) of every tile of the block, on its own: the prefix in
         // front of the chunk is already in shared memory when the warp starts, so warps never wait for each other
         RingCursor cur;
-        RingTile<MULTI> at(b, tiles_per_line, G);
+        Tile at = first_tile();
         const uint32_t v0 = (uint32_t)wid * 32 * VPT + lane;            // this thread's vectors: v0 + 32 j
         for (uint32_t k = 0; k < my_tiles; ++k, at.advance(), cur.advance()) {
             if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag, wait_limit)) ring_fail(hdr, abort_flag);
@@ -928,7 +998,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         int parity = 0;
         const int rw = wid - SW;
         uint64_t tile = b;
-        RingTile<MULTI> at(b, tiles_per_line, G);
+        Tile at = first_tile();
         for (uint32_t k = 0; k < my_tiles; ++k, tile += G, at.advance(), cur.advance(), parity ^= 1) {
             if (!ring_wait(&ctl->full[cur.slot], cur.phase, abort_flag, wait_limit)) ring_fail(hdr, abort_flag);
             const bool whole = !at.last_of_line() || tail == TILE;
@@ -973,7 +1043,11 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
 #pragma unroll
                 for (int w = 1; w < RW; ++w) a = Op::apply(a, ctl->rpart[parity][w]);
                 // (self-test of the bounded waits: one block may be told to keep its aggregates to itself)
-                if (!SELFTEST || (int)b != withhold_block) ring_publish<Acc>(desc, tile, a);
+                if constexpr (GROUPED) {
+                    ring_publish<Acc>(desc, at.number(), a);
+                } else {
+                    if (!SELFTEST || (int)b != withhold_block) ring_publish<Acc>(desc, tile, a);
+                }
             }
         }
     } else if (wid == SW + RW) {
@@ -981,7 +1055,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         if (lane == 0) {
             RingCursor cur;
             uint32_t issued = 0;
-            RingTile<MULTI> at(b, tiles_per_line, G);
+            Tile at = first_tile();
             for (uint32_t k = 0; k < my_tiles; ++k, at.advance(), cur.advance()) {
                 // second and later uses of a slot: wait until the scan of its previous tile has read it
                 if (k >= (uint32_t)R && !ring_wait(&ctl->empty[cur.slot], cur.phase ^ 1u, abort_flag, wait_limit)) {
@@ -1050,14 +1124,27 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
         // in which the wave starts, and prefixes restart at every line start.  Which tiles of a wave belong to which
         // line follows from the positions of the wave's first tile, of this block's tile and of the next wave's
         // first tile inside their lines.  (With a single line all of this is constant and the masks disappear.)
+        // (Grouped layout: a wave is the g tiles of ONE line that the group's members hold at the same time; the carry
+        // restarts with every line and no masks are needed.)
         uint64_t first = 0;
-        RingTile<MULTI> wave(0, tiles_per_line, G), mine(b, tiles_per_line, G);
+        RingTile<MULTI> wave(0, tiles_per_line, G);
+        Tile mine = first_tile();
         for (uint32_t j = 0; j < my_tiles; ++j, first += G, cur.advance(), mine.advance()) {
             if (*abort_flag) break;
-            const uint32_t gj = (uint32_t)((total_tiles - first < G) ? (total_tiles - first) : G);
-            const uint64_t line_first = wave.line;
-            wave.advance();                                                 // now the next wave's first tile
-            const bool same_line_next = !MULTI || wave.line == line_first;  // the wave lies in one line that goes on
+            uint32_t gj;
+            bool same_line_next;
+            if constexpr (GROUPED) {
+                const uint64_t wave_q = mine.q - me;                        // the wave's first tile inside the line
+                first = mine.line * tiles_per_line + wave_q;
+                gj = (uint32_t)((tiles_per_line - wave_q < g) ? (tiles_per_line - wave_q) : g);
+                same_line_next = mine.q + g < tiles_per_line;               // this block's next tile: same line?
+                if (wave_q == 0) carry = Op::template identity<Acc>();
+            } else {
+                gj = (uint32_t)((total_tiles - first < G) ? (total_tiles - first) : G);
+                const uint64_t line_first = wave.line;
+                wave.advance();                                             // now the next wave's first tile
+                same_line_next = !MULTI || wave.line == line_first;         // the wave lies in one line that goes on
+            }
             const uint32_t next_lo = same_line_next ? 0u : (uint32_t)(G - wave.q);   // wave tiles from here on: next wave's line
             const bool mine_in_first = !MULTI || mine.q >= b;               // my line began at or before the wave's start
             const uint32_t mine_lo = mine_in_first ? 0u : (uint32_t)(b - mine.q);    // wave tiles from here to b: my line
@@ -1096,7 +1183,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
                         Acc v;
                         memcpy(&v, &bits, sizeof(Acc));
                         if (!MULTI || idx >= next_lo) tot = Op::apply(tot, v);
-                        if (idx < b && (!MULTI || idx >= mine_lo)) excl = Op::apply(excl, v);
+                        if (idx < me && (!MULTI || idx >= mine_lo)) excl = Op::apply(excl, v);
                     }
                 }
             }
@@ -1120,7 +1207,7 @@ __device__ __forceinline__ void scan_ring(const T* __restrict__ in, T* __restric
             // every block derives the same value)
 #pragma unroll
             for (int d = 16; d > 0; d >>= 1) tot = Op::apply(tot, shfl_xor_any(tot, d));
-            carry = same_line_next ? Op::apply(carry, tot) : tot;
+            carry = (same_line_next || GROUPED) ? Op::apply(carry, tot) : tot;
         }
     }
     __syncthreads();

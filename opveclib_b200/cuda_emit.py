@@ -563,6 +563,21 @@ def col_walk_rows(itemsize):
     return COL_WALK_REGS // max(1, itemsize // 4)        # 32 rows of up to 4-byte elements, 16 rows of 8-byte ones
 
 
+RING_GRID = 148                      # blocks of a ring scan on the target device (one per SM)
+RING_GROUPED_MIN_EFFICIENCY = 0.93
+
+
+def ring_group_efficiency(grid, lines, tiles_per_line):
+    """Share of the grid's block-time that does useful work when every line is scanned by a group of blocks of its own
+    (``ovl::ring_group_size`` / ``ovl::ring_group_efficiency`` of the templates): groups of grid // lines blocks, at
+    most one block per tile of a line; lines are dealt to the groups in rounds."""
+    g = 1 if lines >= grid else grid // lines
+    g = max(1, min(g, tiles_per_line))
+    groups = grid // g
+    rounds = (lines + groups - 1) // groups
+    return lines / float(rounds * groups) * (groups * g) / float(grid)
+
+
 def _reduce_across_workers(kernel, info, red):
     """Should the threads of a warp be neighbouring WORKERS of a reduction loop rather than neighbouring trips of one
     worker's loop?  Yes when the loop's reads are strided along the loop variable but contiguous along the innermost
@@ -1000,12 +1015,20 @@ def emit_cuda(kernel, name, math='exact', pack=True):
         # (bulk copies need every line to start on a 16-byte boundary)
         if multi and can_align and (spec.lines == 1 or (spec.n * spec.dtype.itemsize) % 16 == 0):
             # long lines, pointers aligned: a single cooperative launch that moves every element once
+            # several lines: each scanned by a group of blocks of its own when that keeps a B200's grid busy (the same
+            # rule as ovl::ring_group_efficiency), otherwise waves that cross line ends
+            layout = 'false, false'
+            if spec.lines > 1:
+                grouped = ring_group_efficiency(RING_GRID, spec.lines, tpl) >= RING_GROUPED_MIN_EFFICIENCY
+                layout = 'false, false, false, false, true' if grouped else 'false, true'
             src += ['extern "C" __global__ void __launch_bounds__(' + str(RING_THREADS) + ', 1) ' + name +
                     '_ring(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0, void* scratch) {',
-                    '    ovl::scan_ring<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', false, ' + ('true' if spec.lines > 1 else 'false') +
+                    '    ovl::scan_ring<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + ', ' + layout +
                     '>(in0, out0, nullptr, ' + str(spec.lines) + 'ull, ' + str(spec.n) + 'ull, scratch);',
                     '}', '']
             ring = {'symbol': name + '_ring', 'block': RING_THREADS, 'max_grid': RING_MAX_GRID,
+                    'layout': 'single' if spec.lines == 1 else ('grouped' if layout.endswith('true') and layout.count(',') > 1
+                                                                 else 'waves'),
                     'smem': RING_SLOTS * tile * spec.dtype.itemsize + RING_CTL_BYTES,
                     'zero_bytes': SCAN_HEADER_BYTES + tiles * 16}
         meta['scan'] = {'name': name, 'aligned_variant': bool(can_align), 'three_pass': bool(multi), 'ring': ring,

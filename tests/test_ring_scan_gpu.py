@@ -200,6 +200,47 @@ def test_several_long_lines_in_one_launch(lines, n, op):
     np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
 
 
+@pytest.mark.parametrize('layout', ['grouped', 'waves'])
+@pytest.mark.parametrize('op', [0, 1])
+@pytest.mark.parametrize('lines,n', [(16, 20 * TILE + 8), (64, 6 * TILE + 16), (145, TILE + 4), (148, 4 * TILE),
+                                     (296, 2 * TILE + 8), (1000, 3 * TILE + 4), (2000, 2 * TILE - 4)])
+def test_lines_scanned_by_groups_of_blocks(lines, n, op, layout, monkeypatch):
+    """Line counts for which every line gets a group of blocks of its own when that keeps the grid busy (16 lines: nine
+    blocks each; from 148 lines on a block walks down its lines alone; 64 lines would leave a seventh of the grid
+    idle and stay with waves), and the same shapes with waves that cross line ends forced."""
+    import torch
+    if layout == 'waves':
+        monkeypatch.setenv('OVL_RING_LAYOUT', 'waves')
+    rs = np.random.RandomState(lines + n % 89)
+    x = (rs.normal(0, 1, (lines, n)) if op == 0 else np.exp(rs.uniform(-1e-3, 1e-3, (lines, n)))).astype(np.float32)
+    got = _scan_lines(torch.from_numpy(x).cuda(), op).cpu().numpy()
+    x64 = x.astype(np.float64)
+    want = (np.cumsum(x64, axis=1) if op == 0 else np.cumprod(x64, axis=1)).astype(np.float32)
+    np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
+
+
+@pytest.mark.parametrize('shape,dtype', [((4, 4, 70000), np.float32), ((20, 50000), np.float64), ((148, 20000), np.int32)])
+def test_generated_scan_with_a_group_of_blocks_per_line(shape, dtype):
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    rs = np.random.RandomState(29)
+    x = (rs.randint(-9, 9, shape) if dtype == np.int32 else rs.normal(0, 1, shape)).astype(dtype)
+    op = ns.cumsum(x, axis=len(shape) - 1)
+    got = ns.ovl.evaluate([op])
+    prog, _ = runtime.compile_outputs([op])
+    plan = prog.plans[0]
+    assert plan.meta['scan']['ring']['layout'] == 'grouped' and plan.last_variant == 'ring'
+    if dtype == np.int32:
+        assert np.array_equal(got, np.cumsum(x, axis=-1, dtype=np.int32))
+    else:
+        want = np.cumsum(x.astype(np.float64), axis=-1)
+        if dtype == np.float32:
+            np.testing.assert_allclose(got, want.astype(np.float32), rtol=1.3e-7, atol=0)
+        else:       # both sides add in fp64, in different orders
+            bound = 1e-12 * (np.abs(want) + np.abs(want).max(axis=-1, keepdims=True))
+            assert np.all(np.abs(got - want) <= bound)
+
+
 def test_generated_scan_of_several_long_lines_along_the_last_axis():
     from opveclib_b200 import runtime
     ns = cases.impl()
