@@ -381,6 +381,12 @@ __global__ void __launch_bounds__(ovl::kWarpScanBlock) scan_warp_f32_kernel(cons
     ovl::scan_lines_warp<float, double, Op, 4>(in, out, lines, n);
 }
 
+template <class Op>
+__global__ void __launch_bounds__(ovl::kShortScanBlock) scan_short_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                                             uint64_t lines, uint32_t n) {
+    ovl::scan_lines_short<float, double, Op, 4>(in, out, lines, n);
+}
+
 // from this many lines on (all starting on 16-byte boundaries) a warp scans a whole line by itself
 constexpr uint64_t kWarpScanMinLines = 2048;
 
@@ -562,6 +568,16 @@ int finish_scan(const float* in, float* out, uint64_t lines, uint64_t n, const d
 template <class Op>
 int run_scan(const float* in, float* out, uint64_t lines, uint64_t n, const double* carry, void* scratch, bool aligned,
              cudaStream_t stream) {
+    if (aligned && !carry && ovl::scan_short_line(n, 4) && lines * n >= ovl::kShortScanMinElements &&
+        long_line_mode() == kModeRing) {
+        // short power-of-two lines: the tensor streamed as a flat array, several lines per warp
+        const uint64_t spans = (lines * (n / 4) + 511) / 512;       // 4 warps x 4 vectors x 32 lanes per block and step
+        const uint64_t cap = (uint64_t)sm_count_cached() * 128;
+        scan_short_f32_kernel<Op><<<(uint32_t)(spans < cap ? spans : cap), ovl::kShortScanBlock, 0, stream>>>(in, out, lines,
+                                                                                                            (uint32_t)n);
+        cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? OVL_OK : cuda_fail(e);
+    }
     if (aligned && !carry && lines >= kWarpScanMinLines && n % 4 == 0 && long_line_mode() == kModeRing) {
         const ovl::WarpScanShape shape = ovl::warp_scan_shape(lines, (uint32_t)sm_count_cached());
         scan_warp_f32_kernel<Op><<<shape.grid, shape.block, 0, stream>>>(in, out, lines, n);

@@ -587,6 +587,75 @@ __device__ __forceinline__ void scan_lines_warp(const T* __restrict__ in, T* __r
 }
 
 
+// Lines of a power-of-two length of at most 128 vectors (2 KB): the tensor is walked as one flat array of vectors -
+// a line is `seg` = n / VEC neighbouring lanes (32 / seg lines share a row of 32 lanes) or, from 32 vectors on, one, two
+// or four whole rows of a warp's chunk - so memory is streamed exactly as a copy would, and the shuffle scans stop at
+// line starts.  Nothing is carried from one chunk to the next.
+template <typename T, typename Acc, class Op, int VEC>
+__device__ __forceinline__ void scan_lines_short(const T* __restrict__ in, T* __restrict__ out, const uint64_t lines,
+                                                 const uint32_t n) {
+    constexpr int U = kWarpScanVecs;
+    const uint32_t per_line = n / VEC;                  // vectors per line: 1, 2, 4 ... 128
+    const uint32_t seg = per_line > 32 ? 32 : per_line; // lanes of a row that belong to one line
+    const uint32_t rows = per_line > 32 ? per_line / 32 : 1;   // rows of the chunk that belong to one line
+    const int lane = threadIdx.x & 31;
+    const uint32_t in_seg = (uint32_t)lane & (seg - 1);
+    const uint64_t vectors = lines * per_line;
+    const uint64_t per_block = blockDim.x >> 5;
+    const uint64_t step = (uint64_t)gridDim.x * per_block * (32 * U);
+    for (uint64_t base = ((uint64_t)blockIdx.x * per_block + (threadIdx.x >> 5)) * (32 * U); base < vectors; base += step) {
+        Acc part[U][VEC], inc[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const uint64_t v = base + (uint64_t)j * 32 + lane;
+            Vec<T, VEC> cur;
+            if (v < vectors) {
+                cur = load_vec<T, VEC>(in + v * VEC);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) cur.v[e] = Op::template identity<T>();
+            }
+            part[j][0] = (Acc)cur.v[0];
+#pragma unroll
+            for (int e = 1; e < VEC; ++e) part[j][e] = Op::apply(part[j][e - 1], (Acc)cur.v[e]);
+            inc[j] = part[j][VEC - 1];
+        }
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            if ((uint32_t)d < seg) {                    // (the same for every thread)
+#pragma unroll
+                for (int j = 0; j < U; ++j) {
+                    const Acc y = shfl_up_any(inc[j], d);
+                    if (in_seg >= (uint32_t)d) inc[j] = Op::apply(y, inc[j]);
+                }
+            }
+        }
+        Acc carry = Op::template identity<Acc>();           // of the rows of the same line before row j
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            Acc before = shfl_up_any(inc[j], 1);
+            if (in_seg == 0) before = Op::template identity<Acc>();
+            if (rows > 1) {
+                if (((uint32_t)j & (rows - 1)) == 0) carry = Op::template identity<Acc>();
+                before = Op::apply(carry, before);
+                carry = Op::apply(carry, shfl_any(inc[j], 31));
+            }
+            Vec<T, VEC> w;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) w.v[e] = (T)Op::apply(before, part[j][e]);
+            const uint64_t v = base + (uint64_t)j * 32 + lane;
+            if (v < vectors) store_vec<T, VEC>(out + v * VEC, w);
+        }
+    }
+}
+// lines of n elements (vectors of VEC) that scan_lines_short takes
+__host__ __device__ constexpr bool scan_short_line(uint64_t n, uint32_t vec) {
+    return n >= vec && n % vec == 0 && n / vec <= 32 * kWarpScanVecs && ((n / vec) & (n / vec - 1)) == 0;
+}
+constexpr int kShortScanBlock = 128;
+constexpr uint64_t kShortScanMinElements = 1ull << 16;
+
+
 // ---------------------------------------------------------------------------------------------------------
 // Ring scan: long lines in a single launch; every element is read from memory once and written once
 // (8 bytes per fp32 element) and no thread block ever waits for the block before it.

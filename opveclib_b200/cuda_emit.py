@@ -563,6 +563,21 @@ def col_walk_rows(itemsize):
     return COL_WALK_REGS // max(1, itemsize // 4)        # 32 rows of up to 4-byte elements, 16 rows of 8-byte ones
 
 
+SHORT_SCAN_BLOCK = 128
+SHORT_SCAN_MIN_ELEMENTS = 1 << 16
+
+
+def _short_scan_lines(spec):
+    """Lines that ``ovl::scan_lines_short`` takes: a power-of-two number (at most 128) of whole vectors each, enough of
+    them to be worth a launch of their own (``ovl::scan_short_line``)."""
+    if spec.inner != 1:
+        return False
+    vec = max(1, min(4, 16 // spec.dtype.itemsize))
+    lanes = spec.n // vec
+    return (spec.n % vec == 0 and 1 <= lanes <= 128 and lanes & (lanes - 1) == 0
+            and spec.lines * spec.n >= SHORT_SCAN_MIN_ELEMENTS)
+
+
 RING_GRID = 148                      # blocks of a ring scan on the target device (one per SM)
 RING_GROUPED_MIN_EFFICIENCY = 0.93
 
@@ -967,7 +982,7 @@ def emit_cuda(kernel, name, math='exact', pack=True):
                             'scratch_bytes': SCAN_HEADER_BYTES + spec.outer * chunks * spec.inner * acc_size,
                             'zero_bytes': SCAN_HEADER_BYTES, 'align_bytes': 16, 'lines': spec.lines, 'n': spec.n,
                             'outer': spec.outer, 'inner': spec.inner, 'op': spec.op, 'ring': None}
-    elif spec is not None and (spec.n >= patterns.SCAN_MIN_AXIS or
+    elif spec is not None and (spec.n >= patterns.SCAN_MIN_AXIS or _short_scan_lines(spec) or
                                (spec.lines >= WARP_SCAN_MIN_LINES and spec.n >= WARP_SCAN_MIN_AXIS and
                                 (spec.n * spec.dtype.itemsize) % 16 == 0)):
         src.insert(2, '#include "ovl_scan.cuh"')
@@ -1003,7 +1018,15 @@ def emit_cuda(kernel, name, math='exact', pack=True):
                     'ull, ' + str(tpl) + 'ull, nullptr, nullptr);',
                     '}', '']
         warp = None
-        if spec.lines >= WARP_SCAN_MIN_LINES and (spec.n * spec.dtype.itemsize) % 16 == 0:
+        if _short_scan_lines(spec):
+            # short power-of-two lines: the tensor streamed as a flat array of vectors, several lines per warp
+            src += ['extern "C" __global__ void __launch_bounds__(' + str(SHORT_SCAN_BLOCK) + ') ' + name +
+                    '_wscan(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0) {',
+                    '    ovl::scan_lines_short<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + '>(in0, out0, ' +
+                    str(spec.lines) + 'ull, ' + str(spec.n) + 'u);',
+                    '}', '']
+            warp = {'symbol': name + '_wscan', 'block': SHORT_SCAN_BLOCK, 'flat_vectors': spec.lines * (spec.n // vec)}
+        elif spec.lines >= WARP_SCAN_MIN_LINES and (spec.n * spec.dtype.itemsize) % 16 == 0:
             # thousands of lines: a warp per line, nothing shared between warps
             src += ['extern "C" __global__ void __launch_bounds__(' + str(WARP_SCAN_BLOCK) + ') ' + name +
                     '_wscan(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0) {',

@@ -80,3 +80,64 @@ def test_builtin_entry_point_with_many_lines(lines, n, op):
     x64 = x.astype(np.float64)
     want = (np.cumsum(x64, axis=1) if op == 0 else np.cumprod(x64, axis=1)).astype(np.float32)
     np.testing.assert_allclose(out.cpu().numpy(), want, rtol=1.3e-7, atol=0)
+
+
+SHORT_SHAPES = [((65536, 32), 'float32'), ((16384, 128), 'float32'), ((70001, 16), 'float32'), ((4096, 16), 'float64'),
+                ((32768, 8), 'int32'), ((65536, 4), 'float32'), ((16384, 64), 'uint8'), ((3, 9000, 64), 'float32'),
+                ((8192, 32), 'float64'), ((4100, 256), 'float32'), ((2049, 512), 'float32'), ((1000, 256), 'float64'),
+                ((1024, 512), 'int16')]
+
+
+@pytest.mark.parametrize('fn', ['cumsum', 'cumprod'])
+@pytest.mark.parametrize('shape,dtype', SHORT_SHAPES)
+def test_short_power_of_two_lines_are_streamed_flat(shape, dtype, fn):
+    """Lines of 4 to 512 elements (a power-of-two number of vectors): several lines share a warp - or a line takes one,
+    two or four rows of a warp's chunk - the shuffle scans stop at line starts, memory is walked as one flat array."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    rs = np.random.RandomState(shape[-1] + len(shape))
+    if dtype.startswith('float'):
+        x = (rs.normal(0, 1, shape) if fn == 'cumsum' else rs.uniform(0.9, 1.1, shape)).astype(dtype)
+    else:
+        x = rs.randint(0 if dtype == 'uint8' else -2, 3, shape).astype(dtype)
+    op = getattr(ns, fn)(x, axis=len(shape) - 1)
+    got = ns.ovl.evaluate([op])
+    prog, _ = runtime.compile_outputs([op])
+    plan = prog.plans[0]
+    assert plan.meta['scan']['warp'] is not None and plan.meta['scan']['warp'].get('flat_vectors')
+    if DRYRUN:
+        return
+    assert plan.last_variant == 'wscan'
+    want = _reference(x, fn)
+    if dtype == 'float32':
+        np.testing.assert_allclose(got, want, rtol=1.3e-7, atol=0)
+    elif dtype == 'float64':
+        np.testing.assert_allclose(got, want, rtol=1e-12, atol=1e-12)
+    else:
+        np.testing.assert_array_equal(got, want)
+
+
+@pytest.mark.skipif(DRYRUN, reason='needs a device')
+@pytest.mark.parametrize('op', [0, 1])
+@pytest.mark.parametrize('lines,n', [(1 << 14, 4), (8192, 8), (5000, 16), (70001, 32), (1 << 14, 64), (1 << 17, 128),
+                                     (1000, 64), (513, 128), (4097, 256), (300, 512), (1 << 15, 512)])
+def test_builtin_scan_of_short_lines(lines, n, op):
+    """The built-in fp32 entry point on short power-of-two lines (from 2^16 elements on: the flat kernel; below: the
+    kernels for few lines), against the exact scan."""
+    import torch
+    lib = launcher.library()
+    rs = np.random.RandomState(lines % 1000 + n)
+    x = (rs.normal(0, 1, (lines, n)) if op == 0 else rs.uniform(0.9, 1.1, (lines, n))).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    out = torch.full_like(xd, float('nan'))
+    nbytes = int(lib.ovl_scan_f32_scratch_bytes(lines, n))
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device='cuda')
+    stream = torch.cuda.current_stream().cuda_stream
+    launcher.check(lib.ovl_scan_f32(op, xd.data_ptr(), out.data_ptr(), lines, n, None, scratch.data_ptr(), nbytes, stream),
+                   'scan')
+    status = ctypes.c_int32(-1)
+    launcher.check(lib.ovl_read_kernel_status(scratch.data_ptr(), stream, ctypes.byref(status)), 'status')
+    assert status.value == 0
+    wide = x.astype(np.float64)
+    want = (np.cumsum(wide, axis=1) if op == 0 else np.cumprod(wide, axis=1)).astype(np.float32)
+    np.testing.assert_allclose(out.cpu().numpy(), want, rtol=1.3e-7, atol=0)
