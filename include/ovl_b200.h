@@ -128,10 +128,13 @@ int ovl_read_kernel_status(const void* scratch, void* cuda_stream, int32_t* out_
 /* Inclusive scan (op: 0 = sum, 1 = product) of `lines` contiguous lines of `n` fp32 elements each, device
  * memory in and out, with the same cooperative kernels the code generator uses for recognised accumulate loops
  * (the reference's one-worker-per-line loop: opveclib/examples/test_accumulate.py:22-78).  Accumulation is in
- * fp64.  Lines of at most 8192 elements are scanned in one pass by one thread block each.  Longer lines whose
+ * fp64.  Lines of at most 8192 elements are scanned in one pass by one thread block each - or, with 16-byte
+ * aligned line starts, by one warp each from 2048 lines on, and as one flat array of vectors (several lines per
+ * warp) when a line is a power-of-two number of elements from 4 to 512.  Longer lines whose
  * starts are 16-byte aligned (aligned pointers and, with several lines, n divisible by four) are scanned by the
  * ring scan: one cooperative launch (a block per SM, so nothing else should occupy the device's SMs meanwhile)
- * that reads and writes every element once.  Other long lines take three streaming passes (tile aggregates,
+ * that reads and writes every element once (several lines: a group of blocks per line when that keeps the grid
+ * busy, else waves of tiles that cross line ends).  Other long lines take three streaming passes (tile aggregates,
  * prefixes of the aggregates, seeded tile scans).  The environment variable OVL_SCAN_MODE=threepass forces the
  * three passes, OVL_SCAN_MODE=lookback selects a single pass with decoupled look-back.
  * `carry` (device pointer to one double, or NULL) is combined into every element of a single line (lines
