@@ -130,7 +130,7 @@ int ovl_read_kernel_status(const void* scratch, void* cuda_stream, int32_t* out_
  * (the reference's one-worker-per-line loop: opveclib/examples/test_accumulate.py:22-78).  Accumulation is in
  * fp64.  Lines of at most 8192 elements are scanned in one pass by one thread block each - or, with 16-byte
  * aligned line starts, by one warp each from 2048 lines on, and as one flat array of vectors (several lines per
- * warp) when a line is a power-of-two number of elements from 4 to 512.  Longer lines whose
+ * warp) when a line has at most 512 elements and a multiple of four of them.  Longer lines whose
  * starts are 16-byte aligned (aligned pointers and, with several lines, n divisible by four) are scanned by the
  * ring scan: one cooperative launch (a block per SM, so nothing else should occupy the device's SMs meanwhile)
  * that reads and writes every element once (several lines: a group of blocks per line when that keeps the grid

@@ -570,8 +570,9 @@ int run_scan(const float* in, float* out, uint64_t lines, uint64_t n, const doub
              cudaStream_t stream) {
     if (aligned && !carry && ovl::scan_short_line(n, 4) && lines * n >= ovl::kShortScanMinElements &&
         long_line_mode() == kModeRing) {
-        // short power-of-two lines: the tensor streamed as a flat array, several lines per warp
-        const uint64_t spans = (lines * (n / 4) + 511) / 512;       // 4 warps x 4 vectors x 32 lanes per block and step
+        // short lines: the tensor streamed as a flat array, as many whole lines per warp as fit into 128 vectors
+        const uint64_t per_chunk = 128 / (n / 4);
+        const uint64_t spans = ((lines + per_chunk - 1) / per_chunk + 3) / 4;       // four warps per block
         const uint64_t cap = (uint64_t)sm_count_cached() * 128;
         scan_short_f32_kernel<Op><<<(uint32_t)(spans < cap ? spans : cap), ovl::kShortScanBlock, 0, stream>>>(in, out, lines,
                                                                                                             (uint32_t)n);

@@ -587,30 +587,40 @@ __device__ __forceinline__ void scan_lines_warp(const T* __restrict__ in, T* __r
 }
 
 
-// Lines of a power-of-two length of at most 128 vectors (2 KB): the tensor is walked as one flat array of vectors -
-// a line is `seg` = n / VEC neighbouring lanes (32 / seg lines share a row of 32 lanes) or, from 32 vectors on, one, two
-// or four whole rows of a warp's chunk - so memory is streamed exactly as a copy would, and the shuffle scans stop at
-// line starts.  Nothing is carried from one chunk to the next.
+// Lines of at most 128 vectors (2 KB), any whole number of vectors long: the tensor is walked as one flat array of
+// vectors.  A warp's chunk (kWarpScanVecs rows of 32 lanes) takes as many WHOLE lines as fit into its 128 vectors - they
+// follow each other in memory, so the warp streams one contiguous piece and the next chunk starts right behind it; a
+// line is a run of neighbouring lanes that may continue from one row into the next.  The shuffle scans stop at line
+// starts (a lane takes from the lane d to its left only if that lane holds the same line), the total of the line that
+// is still open at the end of a row is handed to the next row, and nothing is carried from chunk to chunk.  With a
+// power-of-two number of vectors per line every lane of every chunk is used; otherwise the last up-to-(line - 1)
+// vectors of a chunk idle.
 template <typename T, typename Acc, class Op, int VEC>
 __device__ __forceinline__ void scan_lines_short(const T* __restrict__ in, T* __restrict__ out, const uint64_t lines,
                                                  const uint32_t n) {
     constexpr int U = kWarpScanVecs;
-    const uint32_t per_line = n / VEC;                  // vectors per line: 1, 2, 4 ... 128
-    const uint32_t seg = per_line > 32 ? 32 : per_line; // lanes of a row that belong to one line
-    const uint32_t rows = per_line > 32 ? per_line / 32 : 1;   // rows of the chunk that belong to one line
+    const uint32_t per_line = n / VEC;                          // vectors per line: 1 ... 128
+    const uint32_t lines_per_chunk = (32u * U) / per_line;
+    const uint32_t used = lines_per_chunk * per_line;           // vectors of a chunk that hold data
     const int lane = threadIdx.x & 31;
-    const uint32_t in_seg = (uint32_t)lane & (seg - 1);
+    uint32_t pos[U];                                            // this lane's vectors: how far into their lines
+#pragma unroll
+    for (int j = 0; j < U; ++j) pos[j] = (uint32_t)(j * 32 + lane) % per_line;
+    const uint64_t chunks = (lines + lines_per_chunk - 1) / lines_per_chunk;
     const uint64_t vectors = lines * per_line;
     const uint64_t per_block = blockDim.x >> 5;
-    const uint64_t step = (uint64_t)gridDim.x * per_block * (32 * U);
-    for (uint64_t base = ((uint64_t)blockIdx.x * per_block + (threadIdx.x >> 5)) * (32 * U); base < vectors; base += step) {
+    const uint64_t step = (uint64_t)gridDim.x * per_block;
+    for (uint64_t chunk = (uint64_t)blockIdx.x * per_block + (threadIdx.x >> 5); chunk < chunks; chunk += step) {
+        const uint64_t base = chunk * used;
         Acc part[U][VEC], inc[U];
+        bool live[U];
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            const uint64_t v = base + (uint64_t)j * 32 + lane;
+            const uint32_t c = (uint32_t)(j * 32 + lane);
+            live[j] = c < used && base + c < vectors;
             Vec<T, VEC> cur;
-            if (v < vectors) {
-                cur = load_vec<T, VEC>(in + v * VEC);
+            if (live[j]) {
+                cur = load_vec<T, VEC>(in + (base + c) * VEC);
             } else {
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) cur.v[e] = Op::template identity<T>();
@@ -622,35 +632,33 @@ __device__ __forceinline__ void scan_lines_short(const T* __restrict__ in, T* __
         }
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
-            if ((uint32_t)d < seg) {                    // (the same for every thread)
+            if ((uint32_t)d < per_line) {                       // (the same for every thread)
 #pragma unroll
                 for (int j = 0; j < U; ++j) {
                     const Acc y = shfl_up_any(inc[j], d);
-                    if (in_seg >= (uint32_t)d) inc[j] = Op::apply(y, inc[j]);
+                    if (lane >= d && pos[j] >= (uint32_t)d) inc[j] = Op::apply(y, inc[j]);
                 }
             }
         }
-        Acc carry = Op::template identity<Acc>();           // of the rows of the same line before row j
+        Acc open_total = Op::template identity<Acc>();          // of the line that runs on from the row before
 #pragma unroll
         for (int j = 0; j < U; ++j) {
-            Acc before = shfl_up_any(inc[j], 1);
-            if (in_seg == 0) before = Op::template identity<Acc>();
-            if (rows > 1) {
-                if (((uint32_t)j & (rows - 1)) == 0) carry = Op::template identity<Acc>();
-                before = Op::apply(carry, before);
-                carry = Op::apply(carry, shfl_any(inc[j], 31));
-            }
+            const bool continues = pos[j] > (uint32_t)lane;     // the line began in an earlier row
+            const Acc incl = continues ? Op::apply(open_total, inc[j]) : inc[j];
+            Acc before = shfl_up_any(incl, 1);
+            if (lane == 0) before = open_total;
+            if (pos[j] == 0) before = Op::template identity<Acc>();
             Vec<T, VEC> w;
 #pragma unroll
             for (int e = 0; e < VEC; ++e) w.v[e] = (T)Op::apply(before, part[j][e]);
-            const uint64_t v = base + (uint64_t)j * 32 + lane;
-            if (v < vectors) store_vec<T, VEC>(out + v * VEC, w);
+            if (live[j]) store_vec<T, VEC>(out + (base + (uint32_t)(j * 32 + lane)) * VEC, w);
+            if (per_line > 1) open_total = shfl_any(incl, 31);
         }
     }
 }
 // lines of n elements (vectors of VEC) that scan_lines_short takes
 __host__ __device__ constexpr bool scan_short_line(uint64_t n, uint32_t vec) {
-    return n >= vec && n % vec == 0 && n / vec <= 32 * kWarpScanVecs && ((n / vec) & (n / vec - 1)) == 0;
+    return n >= vec && n % vec == 0 && n / vec <= 32 * kWarpScanVecs;
 }
 constexpr int kShortScanBlock = 128;
 constexpr uint64_t kShortScanMinElements = 1ull << 16;

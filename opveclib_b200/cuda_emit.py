@@ -568,14 +568,13 @@ SHORT_SCAN_MIN_ELEMENTS = 1 << 16
 
 
 def _short_scan_lines(spec):
-    """Lines that ``ovl::scan_lines_short`` takes: a power-of-two number (at most 128) of whole vectors each, enough of
+    """Lines that ``ovl::scan_lines_short`` takes: at most 128 whole vectors each, enough of
     them to be worth a launch of their own (``ovl::scan_short_line``)."""
     if spec.inner != 1:
         return False
     vec = max(1, min(4, 16 // spec.dtype.itemsize))
     lanes = spec.n // vec
-    return (spec.n % vec == 0 and 1 <= lanes <= 128 and lanes & (lanes - 1) == 0
-            and spec.lines * spec.n >= SHORT_SCAN_MIN_ELEMENTS)
+    return spec.n % vec == 0 and 1 <= lanes <= 128 and spec.lines * spec.n >= SHORT_SCAN_MIN_ELEMENTS
 
 
 RING_GRID = 148                      # blocks of a ring scan on the target device (one per SM)
@@ -1019,13 +1018,15 @@ def emit_cuda(kernel, name, math='exact', pack=True):
                     '}', '']
         warp = None
         if _short_scan_lines(spec):
-            # short power-of-two lines: the tensor streamed as a flat array of vectors, several lines per warp
+            # short lines: the tensor streamed as a flat array of vectors, as many whole lines per warp as fit
             src += ['extern "C" __global__ void __launch_bounds__(' + str(SHORT_SCAN_BLOCK) + ') ' + name +
                     '_wscan(const ' + t + '* __restrict__ in0, ' + t + '* __restrict__ out0) {',
                     '    ovl::scan_lines_short<' + t + ', ' + acc + ', ' + op + ', ' + str(vec) + '>(in0, out0, ' +
                     str(spec.lines) + 'ull, ' + str(spec.n) + 'u);',
                     '}', '']
-            warp = {'symbol': name + '_wscan', 'block': SHORT_SCAN_BLOCK, 'flat_vectors': spec.lines * (spec.n // vec)}
+            per_chunk = 128 // (spec.n // vec)       # whole lines per warp and step
+            warp = {'symbol': name + '_wscan', 'block': SHORT_SCAN_BLOCK, 'flat_vectors': spec.lines * (spec.n // vec),
+                    'chunks': (spec.lines + per_chunk - 1) // per_chunk}
         elif spec.lines >= WARP_SCAN_MIN_LINES and (spec.n * spec.dtype.itemsize) % 16 == 0:
             # thousands of lines: a warp per line, nothing shared between warps
             src += ['extern "C" __global__ void __launch_bounds__(' + str(WARP_SCAN_BLOCK) + ') ' + name +

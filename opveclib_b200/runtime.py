@@ -147,8 +147,8 @@ class KernelPlan(object):
                     self._make(device, name + '_cscan' + suffix, max(1, min((tiles + warps - 1) // warps, cap)), block, [0],
                                [0], [al, al], scratch, 0)]
         if which == 'wscan' and m['warp'].get('flat_vectors'):
-            # short lines: a block of four warps takes 512 vectors per step
-            grid = max(1, min((m['warp']['flat_vectors'] + 511) // 512, sms * 128))
+            # short lines: a warp takes a chunk of whole lines per step, four warps per block
+            grid = max(1, min((m['warp']['chunks'] + 3) // 4, sms * 128))
             return [self._make(device, m['warp']['symbol'], grid, m['warp']['block'], [0], [0], [16, 16])]
         if which == 'wscan':
             grid, block = warp_scan_shape(m['lines'], sms)

@@ -85,14 +85,16 @@ def test_builtin_entry_point_with_many_lines(lines, n, op):
 SHORT_SHAPES = [((65536, 32), 'float32'), ((16384, 128), 'float32'), ((70001, 16), 'float32'), ((4096, 16), 'float64'),
                 ((32768, 8), 'int32'), ((65536, 4), 'float32'), ((16384, 64), 'uint8'), ((3, 9000, 64), 'float32'),
                 ((8192, 32), 'float64'), ((4100, 256), 'float32'), ((2049, 512), 'float32'), ((1000, 256), 'float64'),
-                ((1024, 512), 'int16')]
+                ((1024, 512), 'int16'), ((70000, 100), 'float32'), ((40001, 36), 'float32'), ((9000, 500), 'float32'),
+                ((5000, 250), 'float64'), ((20000, 12), 'int32'), ((2, 8200, 20), 'float32'), ((4099, 260), 'float32')]
 
 
 @pytest.mark.parametrize('fn', ['cumsum', 'cumprod'])
 @pytest.mark.parametrize('shape,dtype', SHORT_SHAPES)
-def test_short_power_of_two_lines_are_streamed_flat(shape, dtype, fn):
-    """Lines of 4 to 512 elements (a power-of-two number of vectors): several lines share a warp - or a line takes one,
-    two or four rows of a warp's chunk - the shuffle scans stop at line starts, memory is walked as one flat array."""
+def test_short_lines_are_streamed_flat(shape, dtype, fn):
+    """Lines of at most 128 vectors (4 to 512 fp32 elements): as many whole lines as fit share a warp's chunk, a line
+    may run from one row of the chunk into the next, the shuffle scans stop at line starts, memory is walked as one
+    flat array."""
     from opveclib_b200 import runtime
     ns = cases.impl()
     rs = np.random.RandomState(shape[-1] + len(shape))
@@ -120,10 +122,11 @@ def test_short_power_of_two_lines_are_streamed_flat(shape, dtype, fn):
 @pytest.mark.skipif(DRYRUN, reason='needs a device')
 @pytest.mark.parametrize('op', [0, 1])
 @pytest.mark.parametrize('lines,n', [(1 << 14, 4), (8192, 8), (5000, 16), (70001, 32), (1 << 14, 64), (1 << 17, 128),
-                                     (1000, 64), (513, 128), (4097, 256), (300, 512), (1 << 15, 512)])
+                                     (1000, 64), (513, 128), (4097, 256), (300, 512), (1 << 15, 512), (40001, 100),
+                                     (9000, 36), (3000, 500), (70000, 12), (1234, 260)])
 def test_builtin_scan_of_short_lines(lines, n, op):
-    """The built-in fp32 entry point on short power-of-two lines (from 2^16 elements on: the flat kernel; below: the
-    kernels for few lines), against the exact scan."""
+    """The built-in fp32 entry point on short lines (from 2^16 elements on: the flat kernel; below: the kernels for few
+    lines), against the exact scan."""
     import torch
     lib = launcher.library()
     rs = np.random.RandomState(lines % 1000 + n)
