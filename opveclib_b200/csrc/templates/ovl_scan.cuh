@@ -113,15 +113,6 @@ __device__ __forceinline__ A shfl_xor_any(A v, int mask) {
     }
 }
 
-// Asynchronous copy of one vector (BYTES = 4, 8 or 16) from global to shared memory, and the group fence.
-template <int BYTES>
-__device__ __forceinline__ void cp_async_vec(void* smem_dst, const void* gmem_src) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;" ::"r"(d), "l"(gmem_src), "n"(BYTES) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
 // Tile data of one thread: VPT vectors of VEC elements, warp-striped (lane L owns vector j at
 // warp_off + (j*32 + L) * VEC).  Elements past the end of the line hold the identity.
 //

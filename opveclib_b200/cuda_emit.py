@@ -24,7 +24,7 @@ import math
 import os
 
 from . import expr as E
-from .access import analyze
+from .access import analyze, Affine
 from .kernel import iter_nodes
 from . import cuda_pack
 from . import patterns
@@ -163,7 +163,9 @@ class BodyEmitter(object):
         elif k == 'read':
             n = self.fresh(node)
             if id(node) in self.read_subst:
-                self.put(ctype(node.dtype) + ' ' + n + ' = ' + self.read_subst[id(node)] + ';')
+                # ('{index}' in the text stands for the linear offset the read was traced with)
+                self.put(ctype(node.dtype) + ' ' + n + ' = ' +
+                         self.read_subst[id(node)].replace('{index}', self.name(node.args[1])) + ';')
             else:
                 self.put(ctype(node.dtype) + ' ' + n + ' = ' + self.name(node.args[0]) + '[' +
                          self.name(node.args[1]) + '];')
@@ -374,6 +376,75 @@ def _tile_edges(shape, axis, wide):
         return TILE_EDGE, TILE_EDGE
     return (TILE_WIDE if shape[axis] >= TILE_WIDE else TILE_EDGE,
             TILE_WIDE if shape[-1] >= TILE_WIDE else TILE_EDGE)
+
+
+ROWS_BLOCK = 128                     # workers (= rows) per block of a row-staged kernel
+ROWS_MAX_ROW_BYTES = 1024
+ROWS_MAX_SMEM = 200 * 1024
+
+
+def plan_row_staging(kernel, info):
+    """Input tensors that every worker reads only inside ITS OWN ROW - a run of ``rowlen`` consecutive elements that
+    starts at rowlen * (linear worker index) - with at least one such read inside a loop (``acc += a[row, i]``,
+    ``best = max(best, a[row, i])`` ...).  One thread per worker then walks through memory with a stride of a whole row
+    and a warp's loads scatter over 32 rows; staging the rows of a block's workers in shared memory first (they are one
+    contiguous piece of memory) makes the global reads coalesced and leaves the body, statement order and arithmetic
+    as they are.  Returns a list of (tensor, rowlen, padded row length in elements, read nodes) or []."""
+    shape = kernel.workgroup_shape
+    strides = _strides(shape)
+    W = 1
+    for n in shape:
+        W *= n
+    by_tensor = {}
+    for acc in info.accesses:
+        if acc.tensor.kind == 'input' and not acc.is_write:
+            by_tensor.setdefault(id(acc.tensor), (acc.tensor, []))[1].append(acc)
+    staged, smem = [], 0
+    for tensor, accs in by_tensor.values():
+        size = tensor.size
+        if W < 2 * ROWS_BLOCK or size % W:
+            continue
+        rowlen = size // W
+        itemsize = tensor.dtype.itemsize
+        if rowlen < 2 or rowlen * itemsize > ROWS_MAX_ROW_BYTES:
+            continue
+        ok, in_loop = True, False
+        for acc in accs:
+            f = acc.form
+            if f is None or f.mod is not None:
+                ok = False
+                break
+            rest = {}
+            for sym, c in f.coefs.items():
+                if sym[0] != 'p':
+                    rest[sym] = c
+            if any(f.coef(('p', d)) != rowlen * strides[d] for d, n in enumerate(shape) if n > 1):
+                ok = False
+                break
+            try:
+                lo, hi = Affine(rest, f.const).bounds(info.ranges)
+            except KeyError:            # a loop whose trip count is not known when the kernel is generated
+                ok = False
+                break
+            if lo < 0 or hi >= rowlen:
+                ok = False
+                break
+            in_loop = in_loop or acc.loop_depth > 0
+        if not ok or not in_loop:
+            continue
+        # rows padded to an odd number of 4-byte words: threads that read the same column of neighbouring rows hit
+        # different banks
+        padded = rowlen
+        while (padded * itemsize) % 4 or ((padded * itemsize) // 4) % 2 == 0:
+            padded += 1
+            if itemsize >= 8:
+                break                   # (8-byte elements: a two-way conflict is the best a row stride can do)
+        bytes_ = (ROWS_BLOCK * padded * itemsize + 15) // 16 * 16
+        if smem + bytes_ > ROWS_MAX_SMEM:
+            continue
+        staged.append((tensor, rowlen, padded, [a.node for a in accs], smem))
+        smem += bytes_
+    return staged, smem
 
 
 def plan_tiling(kernel, info):
@@ -653,7 +724,7 @@ def emit_cuda(kernel, name, math='exact', pack=True):
             'u + threadIdx.x; worker_index < ' + str(W) + 'ull; worker_index += ovl_stride) {'] + em.lines + \
            ['    }', '}', '']
     meta = {'gen': {'symbol': name + '_gen', 'block': BLOCK_THREADS, 'items': W}, 'vec': None, 'scan': None, 'red': None,
-            'tile': None}
+            'tile': None, 'rows': None}
 
     # ---- vectorised kernel
     plan = plan_vectorisation(kernel, info)
@@ -732,6 +803,50 @@ def emit_cuda(kernel, name, math='exact', pack=True):
     if tile_src is not None:
         src += tile_src
         meta['tile'] = tile_meta
+    # ---- rows staged in shared memory (per-worker loops over the worker's own row of an input)
+    staged, rows_smem = plan_row_staging(kernel, info)
+    if staged:
+        read_subst = {}
+        head, stage = [], []
+        for k, (tensor, rowlen, padded, nodes, offset) in enumerate(staged):
+            t = ctype(tensor.dtype)
+            tname = 'in' + str(tensor.attr['io_index'])
+            head.append('    ' + t + '* const ovl_row' + str(k) + ' = reinterpret_cast<' + t + '*>(ovl_rows_smem + ' +
+                        str(offset) + ');')
+            slot = 'ovl_row' + str(k) + '[ovl_e + (ovl_e / ' + str(rowlen) + 'u) * ' + str(padded - rowlen) + 'u]'
+            source = tname + '[ovl_first' + str(k) + ' + ovl_e]'
+            # 4- and 8-byte elements travel by asynchronous copies (no registers in between, any number in flight)
+            if tensor.dtype.itemsize in (4, 8):
+                move = 'ovl::cp_async_vec<' + str(tensor.dtype.itemsize) + '>(&' + slot + ', &' + source + ');'
+            else:
+                move = slot + ' = ' + source + ';'
+            stage += ['        const uint64_t ovl_first' + str(k) + ' = (uint64_t)ovl_w0 * ' + str(rowlen) + 'ull;',
+                      '        #pragma unroll 4',
+                      '        for (uint32_t ovl_e = threadIdx.x; ovl_e < ovl_live * ' + str(rowlen) + 'u; ovl_e += ' +
+                      str(ROWS_BLOCK) + 'u)',
+                      '            ' + move]
+            for n in nodes:
+                read_subst[id(n)] = 'ovl_row' + str(k) + '[(uint32_t)({index} - ovl_first' + str(k) + ') + threadIdx.x * ' + \
+                    str(padded - rowlen) + 'u]'
+        em = BodyEmitter(kernel, 3, read_subst, position_text=pos_text, math=math)
+        em.block(kernel.body)
+        src += ['extern "C" __global__ void __launch_bounds__(' + str(ROWS_BLOCK) + ') ' + name + '_rows(' + params + ') {',
+                '    extern __shared__ __align__(16) unsigned char ovl_rows_smem[];'] + head + \
+               ['    for (' + widx_t + ' ovl_w0 = (' + widx_t + ')blockIdx.x * ' + str(ROWS_BLOCK) + 'u; ovl_w0 < ' + str(W) +
+                'ull; ovl_w0 += (' + widx_t + ')gridDim.x * ' + str(ROWS_BLOCK) + 'u) {',
+                '        // the rows of this block\'s workers are one contiguous piece of each staged tensor',
+                '        const uint32_t ovl_live = (' + str(W) + 'ull - ovl_w0 < ' + str(ROWS_BLOCK) + 'u) ? (uint32_t)(' +
+                str(W) + 'ull - ovl_w0) : ' + str(ROWS_BLOCK) + 'u;'] + stage + \
+               ['        ovl::cp_async_commit();',
+                '        ovl::cp_async_wait_all();',
+                '        __syncthreads();',
+                '        if (threadIdx.x < ovl_live) {',
+                '            const ' + widx_t + ' worker_index = ovl_w0 + threadIdx.x;'] + em.lines + \
+               ['        }',
+                '        __syncthreads();        // the next round overwrites the rows',
+                '    }', '}', '']
+        meta['rows'] = {'symbol': name + '_rows', 'block': ROWS_BLOCK, 'items': W, 'smem': rows_smem,
+                        'staged': [[tensor.attr['io_index'], rowlen] for tensor, rowlen, _, _, _ in staged]}
     # ---- cooperative reduction loop
     red = patterns.match_reduce(kernel, info)
     if red is not None:

@@ -113,6 +113,12 @@ class KernelPlan(object):
             m = meta['tile']
             grid = max(1, min(m['tiles'], sms * (2048 // m['block']) * TILE_ROUNDS))
             return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out))]
+        if which == 'rows':
+            m = meta['rows']
+            per_sm = max(1, min(2048 // m['block'], (200 * 1024) // max(1, m['smem'])))
+            grid = max(1, min((m['items'] + m['block'] - 1) // m['block'], sms * per_sm * GRID_ROUNDS))
+            return [self._make(device, m['symbol'], grid, m['block'], all_in, all_out, [0] * (n_in + n_out), 0, 0,
+                               m['smem'])]
         if which == 'red':
             m = meta['red']
             if m.get('split'):
@@ -200,6 +206,8 @@ class KernelPlan(object):
             return 'red'
         if meta.get('tile') and os.environ.get('OVL_TILE_MODE') != 'off':
             return 'tile'
+        if meta.get('rows') and os.environ.get('OVL_ROWS_MODE') != 'off':
+            return 'rows'
         if meta.get('vec'):
             ok = True
             for kind, idx in meta['vec']['aligned']:

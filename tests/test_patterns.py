@@ -253,3 +253,21 @@ def test_seeded_scan_needs_assignment_before_the_first_store():
 
     assert patterns.match_scan(_kernel(make(False))) is not None
     assert patterns.match_scan(_kernel(make(True))) is None
+
+
+def test_rows_read_in_a_loop_are_staged_and_others_are_not():
+    """Row staging applies to inputs that a worker reads only inside its own row, with a read in a loop."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    u = cases.user_ops(ns)
+    prog, _ = runtime.compile_outputs([u.matvec(np.zeros((4096, 64), np.float32), np.zeros(64, np.float32))])
+    assert prog.plans[0].meta['rows']['staged'] == [[0, 64]]            # the matrix, not the vector
+    prog, _ = runtime.compile_outputs([u.matvec(np.zeros((4096, 8192), np.float32), np.zeros(8192, np.float32))])
+    assert prog.plans[0].meta['rows'] is None                           # rows of 32 KB: the reduction kernel's
+    prog, _ = runtime.compile_outputs([u.matvec(np.zeros((100, 64), np.float32), np.zeros(64, np.float32))])
+    assert prog.plans[0].meta['rows'] is None                           # too few workers
+    prog, _ = runtime.compile_outputs([u.colsum(np.zeros((64, 4096), np.float32))])
+    assert prog.plans[0].meta['rows'] is None                           # a worker's reads are a column, not a row
+    op = ns.lstm(np.zeros((512, 4096), np.float32), np.zeros((512, 1024), np.float32), forget_bias=0.0)
+    prog, _ = runtime.compile_outputs([op[0], op[1]])
+    assert prog.plans[0].meta['rows'] is None                           # no loop
