@@ -156,7 +156,7 @@ class BodyEmitter(object):
             self.put(self.name(node.args[0]) + ' = ' + self.name(node.args[1]) + ';')
         elif k == 'assign_tensor':
             if id(node) in self.write_subst:
-                self.put(self.write_subst[id(node)] % self.name(node.args[2]))
+                self.put(self.write_subst[id(node)].replace('{index}', self.name(node.args[1])) % self.name(node.args[2]))
             else:
                 self.put(self.name(node.args[0]) + '[' + self.name(node.args[1]) + '] = ' +
                          self.name(node.args[2]) + ';')
@@ -439,6 +439,64 @@ def plan_row_staging(kernel, info):
             padded += 1
             if itemsize >= 8:
                 break                   # (8-byte elements: a two-way conflict is the best a row stride can do)
+        bytes_ = (ROWS_BLOCK * padded * itemsize + 15) // 16 * 16
+        if smem + bytes_ > ROWS_MAX_SMEM:
+            continue
+        staged.append((tensor, rowlen, padded, [a.node for a in accs], smem))
+        smem += bytes_
+    if not staged:
+        return [], 0
+    # Outputs whose every write lies in the writing worker's own row, unconditionally, the writes together covering
+    # the whole row (``out[row, i] = ...`` in a loop over the row; ``out[row, 0] = ...`` followed by a loop from 1):
+    # the rows are collected in shared memory and written out as one contiguous piece.
+    writes = {}
+    for acc in info.accesses:
+        if acc.tensor.kind == 'output' and acc.is_write:
+            writes.setdefault(id(acc.tensor), (acc.tensor, []))[1].append(acc)
+    for tensor, accs in writes.values():
+        size = tensor.size
+        if size % W:
+            continue
+        rowlen = size // W
+        itemsize = tensor.dtype.itemsize
+        if rowlen < 2 or rowlen * itemsize > ROWS_MAX_ROW_BYTES:
+            continue
+        covered, ok = [], True
+        for acc in accs:
+            f = acc.form
+            if f is None or f.mod is not None or acc.cond_depth > 0:
+                ok = False
+                break
+            rest = {sym: c for sym, c in f.coefs.items() if sym[0] != 'p'}
+            if any(f.coef(('p', d)) != rowlen * strides[d] for d, n in enumerate(shape) if n > 1):
+                ok = False
+                break
+            if len(rest) > 1 or any(abs(c) != 1 for c in rest.values()):
+                ok = False
+                break
+            try:
+                lo, hi = Affine(rest, f.const).bounds(info.ranges)
+            except KeyError:
+                ok = False
+                break
+            if lo < 0 or hi >= rowlen:
+                ok = False
+                break
+            covered.append((lo, hi))
+        if not ok or not any(a.loop_depth > 0 for a in accs):
+            continue
+        reach = 0
+        for lo, hi in sorted(covered):
+            if lo > reach:
+                break
+            reach = max(reach, hi + 1)
+        if reach < rowlen:
+            continue                    # part of the row is never written: leave it alone
+        padded = rowlen
+        while (padded * itemsize) % 4 or ((padded * itemsize) // 4) % 2 == 0:
+            padded += 1
+            if itemsize >= 8:
+                break
         bytes_ = (ROWS_BLOCK * padded * itemsize + 15) // 16 * 16
         if smem + bytes_ > ROWS_MAX_SMEM:
             continue
@@ -806,13 +864,25 @@ def emit_cuda(kernel, name, math='exact', pack=True):
     # ---- rows staged in shared memory (per-worker loops over the worker's own row of an input)
     staged, rows_smem = plan_row_staging(kernel, info)
     if staged:
-        read_subst = {}
-        head, stage = [], []
+        read_subst, rows_write_subst = {}, {}
+        head, stage, unstage = [], [], []
         for k, (tensor, rowlen, padded, nodes, offset) in enumerate(staged):
             t = ctype(tensor.dtype)
-            tname = 'in' + str(tensor.attr['io_index'])
             head.append('    ' + t + '* const ovl_row' + str(k) + ' = reinterpret_cast<' + t + '*>(ovl_rows_smem + ' +
                         str(offset) + ');')
+            if tensor.kind == 'output':
+                tname = 'out' + str(tensor.attr['io_index'])
+                stage.append('        const uint64_t ovl_first' + str(k) + ' = (uint64_t)ovl_w0 * ' + str(rowlen) + 'ull;')
+                unstage += ['        #pragma unroll 4',
+                            '        for (uint32_t ovl_e = threadIdx.x; ovl_e < ovl_live * ' + str(rowlen) + 'u; ovl_e += ' +
+                            str(ROWS_BLOCK) + 'u)',
+                            '            ' + tname + '[ovl_first' + str(k) + ' + ovl_e] = ovl_row' + str(k) + '[ovl_e + (ovl_e / ' +
+                            str(rowlen) + 'u) * ' + str(padded - rowlen) + 'u];']
+                for n in nodes:
+                    rows_write_subst[id(n)] = 'ovl_row' + str(k) + '[(uint32_t)({index} - ovl_first' + str(k) + \
+                        ') + threadIdx.x * ' + str(padded - rowlen) + 'u] = %s;'
+                continue
+            tname = 'in' + str(tensor.attr['io_index'])
             slot = 'ovl_row' + str(k) + '[ovl_e + (ovl_e / ' + str(rowlen) + 'u) * ' + str(padded - rowlen) + 'u]'
             source = tname + '[ovl_first' + str(k) + ' + ovl_e]'
             # 4- and 8-byte elements travel by asynchronous copies (no registers in between, any number in flight)
@@ -828,8 +898,10 @@ def emit_cuda(kernel, name, math='exact', pack=True):
             for n in nodes:
                 read_subst[id(n)] = 'ovl_row' + str(k) + '[(uint32_t)({index} - ovl_first' + str(k) + ') + threadIdx.x * ' + \
                     str(padded - rowlen) + 'u]'
-        em = BodyEmitter(kernel, 3, read_subst, position_text=pos_text, math=math)
+        em = BodyEmitter(kernel, 3, read_subst, rows_write_subst, position_text=pos_text, math=math)
         em.block(kernel.body)
+        if unstage:
+            unstage = ['        __syncthreads();        // every row of the block is complete'] + unstage
         src += ['extern "C" __global__ void __launch_bounds__(' + str(ROWS_BLOCK) + ') ' + name + '_rows(' + params + ') {',
                 '    extern __shared__ __align__(16) unsigned char ovl_rows_smem[];'] + head + \
                ['    for (' + widx_t + ' ovl_w0 = (' + widx_t + ')blockIdx.x * ' + str(ROWS_BLOCK) + 'u; ovl_w0 < ' + str(W) +
@@ -842,11 +914,14 @@ def emit_cuda(kernel, name, math='exact', pack=True):
                 '        __syncthreads();',
                 '        if (threadIdx.x < ovl_live) {',
                 '            const ' + widx_t + ' worker_index = ovl_w0 + threadIdx.x;'] + em.lines + \
-               ['        }',
-                '        __syncthreads();        // the next round overwrites the rows',
+               ['        }'] + unstage + \
+               ['        __syncthreads();        // the next round overwrites the rows',
                 '    }', '}', '']
         meta['rows'] = {'symbol': name + '_rows', 'block': ROWS_BLOCK, 'items': W, 'smem': rows_smem,
-                        'staged': [[tensor.attr['io_index'], rowlen] for tensor, rowlen, _, _, _ in staged]}
+                        'staged': [[tensor.attr['io_index'], rowlen] for tensor, rowlen, _, _, _ in staged
+                                   if tensor.kind == 'input'],
+                        'staged_outputs': [[tensor.attr['io_index'], rowlen] for tensor, rowlen, _, _, _ in staged
+                                           if tensor.kind == 'output']}
     # ---- cooperative reduction loop
     red = patterns.match_reduce(kernel, info)
     if red is not None:

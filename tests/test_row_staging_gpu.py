@@ -92,3 +92,58 @@ def test_same_bits_without_staging(monkeypatch):
     monkeypatch.setenv('OVL_ROWS_MODE', 'off')
     plain = ns.ovl.evaluate([rowsum(x)], target_language='b200')
     assert np.array_equal(staged, plain)
+
+
+def test_rows_that_are_written_are_collected_and_stored_as_one_piece():
+    """``out[row, i] = a[row, i] / sum`` after a first loop that forms the sum, and an inclusive scan of short lines of
+    odd length (serial arithmetic, as the oracle's): input AND output rows go through shared memory."""
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    ovl = ns.ovl
+
+    @ovl.operator()
+    def normalise(a):
+        out = ovl.output_like(a)
+        row = ovl.position_in([a.shape[0]])[0]
+        acc = ovl.variable(0, a.dtype)
+        for i in ovl.arange(a.shape[1]):
+            acc <<= acc + a[row, i]
+        for i in ovl.arange(a.shape[1]):
+            out[row, i] = a[row, i] / acc
+        return out
+
+    rs = np.random.RandomState(8)
+    x = rs.uniform(0.5, 2, (9001, 50)).astype(np.float32)
+    for op in (normalise(x), ns.cumsum(x, axis=1), ns.cumprod(rs.uniform(0.9, 1.1, (4000, 7)).astype(np.float64), axis=1)):
+        prog, _ = runtime.compile_outputs([op])
+        assert prog.plans[0].meta['rows']['staged_outputs'], prog.plans[0].meta['rows']
+        _check(ns, [op])
+
+
+def test_partly_written_rows_are_not_collected():
+    from opveclib_b200 import runtime
+    ns = cases.impl()
+    ovl = ns.ovl
+
+    @ovl.operator()
+    def every_other(a):
+        out = ovl.output_like(a)
+        row = ovl.position_in([a.shape[0]])[0]
+        for i in ovl.arange(0, a.shape[1], 2):
+            out[row, i] = a[row, i] + a[row, i + 1]
+        return out
+
+    @ovl.operator()
+    def positive_only(a):
+        out = ovl.output_like(a)
+        row = ovl.position_in([a.shape[0]])[0]
+        for i in ovl.arange(a.shape[1]):
+            with ovl.if_(a[row, i] > 0):
+                out[row, i] = a[row, i]
+        return out
+
+    x = np.random.RandomState(9).normal(0, 1, (3000, 40)).astype(np.float32)
+    for op in (every_other(x), positive_only(x)):
+        prog, _ = runtime.compile_outputs([op])
+        rows = prog.plans[0].meta['rows']
+        assert rows is not None and rows['staged'] and not rows['staged_outputs']
