@@ -1,7 +1,7 @@
 """Benchmark of the hot path: fused OVL operator graphs on B200, next to the reference's CPU operator.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--math tolerance|exact]
-                    [--workload c4|c5|c2_cumsum|c2_cumprod|c1|c1_shift|c3|c3_grad|c3_stdops|light16|matvec|perf_accumulate|colscan|colscan_wide|colsum|colsum_narrow|dot_long|rows_short|transpose|transpose_axpy|op_<name>]
+                    [--workload c4|c5|c2_cumsum|c2_cumprod|c1|c1_shift|c3|c3_grad|c3_stdops|light16|matvec|perf_accumulate|colscan|colscan_wide|colsum|colsum_narrow|dot_long|rowsum_short|rownorm_short|scan_tiny|rows_short|transpose|transpose_axpy|op_<name>]
 
 Default workload (the one the headline metric is quoted on): the 16-operator fused element-wise chain over an
 fp32 tensor [8, 2^27] drawn from uniform[-2, 2], rows sharded contiguously over N GPUs with no communication
@@ -194,6 +194,15 @@ def build_graph(workload, rows_local=None, n_local=None):
         # ONE dot product of 2^28 terms (matvec with a single row): the loop is cut into slices that many blocks
         # fold; 1 GiB + 1 GiB, every element read once
         return [cases.user_ops(ns).matvec(z(1, 1 << 28), z(1 << 28))], 2 << 28, 4
+    if workload == 'rowsum_short':
+        # row sums of fp32 [2^22, 32]: the rows of a block's workers staged in shared memory, summed in order
+        return [cases.user_ops(ns).rowsum(z(1 << 22, 32))], 32 << 22, 4
+    if workload == 'rownorm_short':
+        # every row of fp32 [2^21, 50] divided by its sum: input and output rows through shared memory, 8 B per element
+        return [cases.user_ops(ns).row_normalise(z(1 << 21, 50))], 50 << 21, 8
+    if workload == 'scan_tiny':
+        # cumsum along axis 1 of fp32 [2^20, 128]: short lines share warps, the tensor streamed as one flat array
+        return [ns.cumsum(z(1 << 20, 128), axis=1)], 128 << 20, 8
     if workload == 'colsum_narrow':
         # column sums of fp32 [2^22, 64]: two groups of 32 columns, the rows cut into slices for many blocks
         return [cases.user_ops(ns).colsum(z(1 << 22, 64))], 64 << 22, 4
@@ -216,7 +225,8 @@ def _precompile_all(runtime, streaming):
         streaming.plan(outs, dag, prog, 3)          # the slab-shaped kernels of the end-to-end leg
     for w in ('c2_cumsum', 'c2_cumprod', 'c1', 'c1_shift', 'c3', 'c3_grad', 'c3_stdops', 'light16', 'matvec', 'op_tanh', 'op_exp',
               'op_log1p', 'op_expm1', 'op_mulc', 'op_add', 'op_where', 'perf_accumulate', 'colscan', 'colscan_wide', 'transpose',
-              'transpose_axpy', 'rows_short', 'colsum', 'dot_long', 'colsum_narrow'):
+              'transpose_axpy', 'rows_short', 'colsum', 'dot_long', 'colsum_narrow', 'rowsum_short', 'rownorm_short',
+              'scan_tiny'):
         runtime.compile_outputs(build_graph(w)[0])
 
 
@@ -227,8 +237,8 @@ def input_distribution(workload, index):
         return ('uniform', 0.99, 1.01)
     if workload in ('c1', 'c1_shift'):
         return ('uniform', -1.0, 1.0)
-    if workload == 'perf_accumulate':
-        return ('uniform', 0.0, 1.0)
+    if workload in ('perf_accumulate', 'rownorm_short'):
+        return ('uniform', 0.5, 1.5) if workload == 'rownorm_short' else ('uniform', 0.0, 1.0)
     if workload == 'c3_grad' and index >= 2:
         return ('normal', 0.0, 0.1)
     return ('normal', 0.0, 1.0)
@@ -343,6 +353,9 @@ def workload_config(workload, n):
         'colsum': 'column sums as a per-column reduction loop, fp32 [16384, 8192] normal(0,1)',
         'dot_long': 'one dot product of 2^28 terms (matvec fp32 [1, 2^28] x [2^28]), the loop split over the blocks',
         'colsum_narrow': 'column sums of fp32 [2^22, 64] normal(0,1), rows split over the blocks',
+        'rowsum_short': 'row sums of fp32 [2^22, 32] normal(0,1), rows staged in shared memory',
+        'rownorm_short': 'rows of fp32 [2^21, 50] uniform(0.5,1.5) divided by their sums, rows staged in shared memory both ways',
+        'scan_tiny': 'cumsum along axis 1 of fp32 [2^20, 128] normal(0,1), several lines per warp',
         'transpose': 'transpose of fp32 [16384, 16384] normal(0,1) written as an operator that reads its operand transposed',
         'transpose_axpy': 'a^T * 0.5 + b, fp32 [16384, 16384] normal(0,1)',
     }
@@ -353,7 +366,7 @@ def workload_config(workload, n):
     if workload == 'c4' and (C4_ROWS, C4_COLS) != (8, 1 << 27):
         names['c4'] = 'fused 16-op element-wise chain, fp32 [%d, %d] uniform[-2,2] (reduced case)' % (C4_ROWS, C4_COLS)
     return {'workload': names[workload], 'id': workload, 'parallelism': 'shard-leading-axis x%d' % n,
-            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec', 'colscan', 'colscan_wide', 'colsum', 'rows_short', 'transpose', 'transpose_axpy', 'dot_long', 'colsum_narrow')
+            'l2': 'inputs larger than L2 (126 MB)' if (workload in ('c4', 'light16', 'c5', 'c2_cumsum', 'c2_cumprod', 'matvec', 'colscan', 'colscan_wide', 'colsum', 'rows_short', 'transpose', 'transpose_axpy', 'dot_long', 'colsum_narrow', 'rowsum_short', 'rownorm_short', 'scan_tiny')
                                                       or workload.startswith('op_'))
             else 'inputs fit in L2; an L2-sized buffer is written between timed steps', 'seed': SEED}
 
@@ -766,6 +779,12 @@ def rebuild_with_inputs(workload, np_inputs, rows_local):
         return [cases.user_ops(ns).matvec(np_inputs[0], np_inputs[1])]
     if workload in ('colsum', 'colsum_narrow'):
         return [cases.user_ops(ns).colsum(np_inputs[0])]
+    if workload == 'rowsum_short':
+        return [cases.user_ops(ns).rowsum(np_inputs[0])]
+    if workload == 'rownorm_short':
+        return [cases.user_ops(ns).row_normalise(np_inputs[0])]
+    if workload == 'scan_tiny':
+        return [ns.cumsum(np_inputs[0], axis=1)]
     if workload == 'dot_long':
         mat, vec = sorted(np_inputs, key=lambda a: -a.ndim)
         return [cases.user_ops(ns).matvec(mat, vec)]

@@ -174,7 +174,31 @@ def user_ops(ns):
         out[col] = accum
         return out
 
-    ops = types.SimpleNamespace(transpose=transpose, transpose_axpy=transpose_axpy, colsum=colsum,
+    @ovl.operator()
+    def rowsum(a):
+        # one worker per row folds the row in order: short rows are staged in shared memory, long ones reduced by a warp
+        out = ovl.output([a.shape[0]], a.dtype)
+        row = ovl.position_in([a.shape[0]])[0]
+        accum = ovl.variable(0, a.dtype)
+        for i in ovl.arange(a.shape[1]):
+            accum <<= accum + a[row, i]
+        out[row] = accum
+        return out
+
+    @ovl.operator()
+    def row_normalise(a):
+        # every row divided by its sum: one loop that reads the row, a second one that reads and writes it
+        out = ovl.output_like(a)
+        row = ovl.position_in([a.shape[0]])[0]
+        accum = ovl.variable(0, a.dtype)
+        for i in ovl.arange(a.shape[1]):
+            accum <<= accum + a[row, i]
+        for i in ovl.arange(a.shape[1]):
+            out[row, i] = a[row, i] / accum
+        return out
+
+    ops = types.SimpleNamespace(transpose=transpose, transpose_axpy=transpose_axpy, colsum=colsum, rowsum=rowsum,
+                                row_normalise=row_normalise,
                                 shift_cyclic=shift_cyclic, absolute=absolute, halfplus=halfplus, ew_exp=ew_exp,
                                 dot=dot, matvec=matvec, rowprod_scaled=rowprod_scaled,
                                 ew_tanh=ew_tanh, ew_add=ew_add, ew_mul=ew_mul, ew_addc=ew_addc, ew_mulc=ew_mulc,
