@@ -82,12 +82,14 @@ class Access(object):
 class KernelInfo(object):
     """Result of :func:`analyze`: ``forms`` maps id(node) -> Affine for every integer scalar with a proven
     form; ``accesses`` lists reads/writes of inputs, outputs and local tensors in program order; ``ranges`` maps
-    symbols to inclusive value ranges; ``loop_vars`` maps id(loop variable node) -> symbol."""
+    symbols to inclusive value ranges (``steps``: the step of a loop symbol); ``loop_vars`` maps id(loop variable
+    node) -> symbol."""
 
     def __init__(self):
         self.forms = {}
         self.accesses = []
         self.ranges = {}
+        self.steps = {}
         self.loop_vars = {}
         self.assigned_vars = set()
         self.position_scalar_uses = 0
@@ -195,6 +197,7 @@ def analyze(kernel):
                         sym = ('l', len(info.loop_vars))
                         info.loop_vars[id(var)] = sym
                         info.ranges[sym] = (min(s, last), max(s, last))
+                        info.steps[sym] = st
                         info.forms[id(var)] = Affine({sym: 1})
                 visit(node.body, loop_depth + 1, cond_depth)
                 if sym is not None:

@@ -471,7 +471,8 @@ def plan_row_staging(kernel, info):
             if any(f.coef(('p', d)) != rowlen * strides[d] for d, n in enumerate(shape) if n > 1):
                 ok = False
                 break
-            if len(rest) > 1 or any(abs(c) != 1 for c in rest.values()):
+            # (a write covers the interval of its offsets only if the loop visits every value: step +-1)
+            if len(rest) > 1 or any(abs(c) != 1 or abs(info.steps.get(sym, 0)) != 1 for sym, c in rest.items()):
                 ok = False
                 break
             try:
