@@ -281,6 +281,45 @@ class ShardedReduce(object):
         return self.combine(self.partial)
 
 
+class ShardedShift(object):
+    """The cyclic shift of the documentation's first example (README.rst:40-74: ``out[i] = x[(i - 1) mod N]``,
+    ``[0, 1, 2, 3, 4] -> [4, 0, 1, 2, 3]``) for a vector split contiguously over the ranks of ``group``: a rank's first
+    output element is the LAST input element of the rank before it (of the last rank, for rank 0), everything else is
+    local.  One element per rank is all-gathered into local memory (the halo), the rank's shard is shifted by the
+    generated kernel, and the halo element replaces the one value the local shift wrapped around.  The reference has
+    no multi-GPU support; on one rank this is the plain operator."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+        self.dist = dist
+        self.group = group
+        self.distributed = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if self.distributed else 1
+        self.rank = dist.get_rank(group) if self.distributed else 0
+
+    def halo(self, last):
+        """``last``: this rank's last input element as a one-element tensor.  Returns the element that belongs in front
+        of this rank's shard: the last element of the rank before it."""
+        import torch
+        if self.world == 1:
+            return last
+        gathered = torch.empty(self.world, dtype=last.dtype, device=last.device)
+        self.dist.all_gather_into_tensor(gathered, last.contiguous().view(1), group=self.group)
+        return gathered[(self.rank - 1) % self.world].view(1)
+
+    def __call__(self, x):
+        """``x``: this rank's shard, a contiguous one-dimensional CUDA tensor.  Returns the rank's shard of the shifted
+        vector (a CUDA tensor)."""
+        from .examples.workloads import namespace, user_ops
+        from .runtime import evaluate
+        if x.dim() != 1 or not x.is_cuda or not x.is_contiguous():
+            raise ValueError('expected a contiguous one-dimensional CUDA tensor')
+        first = self.halo(x[-1:])                               # (enqueued before the kernel: they overlap)
+        out = evaluate([user_ops(namespace()).shift_cyclic(x)], target_language='b200')
+        out[0:1].copy_(first)
+        return out
+
+
 class HostScan(object):
     """Inclusive cumsum / cumprod of a rank-1 fp32 array that lives in HOST memory, on one GPU.
 

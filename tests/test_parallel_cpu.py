@@ -144,3 +144,36 @@ def test_combine_partials_is_rank_ordered():
     assert parallel.combine_partials(parts[:, 1:], 'mul').tolist() == [6.0]
     with pytest.raises(ValueError):
         parallel.combine_partials(parts, 'max')
+
+
+def _gloo_halo_rank(rank, world, port, queue):
+    import torch
+    import torch.distributed as dist
+    os.environ['MASTER_ADDR'] = '127.0.0.1'
+    os.environ['MASTER_PORT'] = str(port)
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        x = np.arange(11, dtype=np.float32)
+        mine = torch.from_numpy(np.ascontiguousarray(parallel.shard_leading_axis(x, rank, world)))
+        first = parallel.ShardedShift().halo(mine[-1:])
+        queue.put((rank, first.numpy()))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_halo_of_a_sharded_cyclic_shift_with_two_gloo_ranks():
+    """Every rank receives the last element of the rank before it (rank 0: of the last rank)."""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context('spawn')
+    queue = ctx.Queue()
+    world, port = 2, _free_port()
+    procs = [ctx.Process(target=_gloo_halo_rank, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict(queue.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    # shards of arange(11): [0..5] and [6..10]
+    assert got[0].tolist() == [10.0] and got[1].tolist() == [5.0]
