@@ -729,7 +729,7 @@ def _reduce_across_workers(kernel, info, red):
     trips' do not."""
     shape = kernel.workgroup_shape
     last = ('p', len(shape) - 1)
-    sym = info.loop_vars.get(id(red.loop.args[0]))
+    sym = info.loop_vars.get(id(red.fastest_var))
     if sym is None or shape[-1] < 8:        # (rows of fewer than 32 bytes: no layout reads them well)
         return False
     in_loop = set(id(n) for n in iter_nodes(red.loop.body))
@@ -925,6 +925,8 @@ def emit_cuda(kernel, name, math='exact', pack=True):
                                            if tensor.kind == 'output']}
     # ---- cooperative reduction loop
     red = patterns.match_reduce(kernel, info)
+    if red is not None and red.inner is not None and _reduce_across_workers(kernel, info, red):
+        red = None          # a nest whose reads are contiguous across workers: the generic kernel reads it coalesced
     if red is not None:
         src.insert(2, '#include "ovl_reduce.cuh"')
         across = _reduce_across_workers(kernel, info, red) and os.environ.get('OVL_RED_LAYOUT') != 'along'
@@ -945,6 +947,11 @@ def emit_cuda(kernel, name, math='exact', pack=True):
         acc_t = ctype(red.acc.dtype)
         opname = 'ovl::OpAdd' if red.op == 'add' else 'ovl::OpMul'
         ivar = em.name(red.loop.args[0])
+        ivar_t = ctype(red.loop.args[0].dtype)
+        if red.inner is not None:
+            # a nest of two loops runs as one loop over its trips; the loop variables are derived from the trip
+            ivar, ivar_t = 'ovl_trip', 'uint64_t'
+            em.put('uint64_t ovl_trip;')
         # few workers with long loops: the loop of a worker is cut into slices that different blocks fold
         if across:
             split = (W + 31) // 32 <= REDUCE_SPLIT_MAX_WORKERS // 2 and red.n >= REDUCE_SPLIT_MIN_TRIPS // 2
@@ -954,17 +961,29 @@ def emit_cuda(kernel, name, math='exact', pack=True):
         em.put(acc_t + ' ovl_partial = ' + opname + '::identity<' + acc_t + '>();')
         em.put('#pragma unroll ' + ('8' if across else '4'))
         if split:
-            ivar_t = ctype(red.loop.args[0].dtype)
             em.put('for(' + ivar + ' = (' + ivar_t + ')(ovl_lo + ovl_member); ' + ivar + ' < (' + ivar_t + ')ovl_hi; ' +
                    ivar + ' += ' + str(group) + '){')
         else:
             em.put('for(' + ivar + ' = ovl_member; ' + ivar + ' < ' + str(red.n) + '; ' + ivar + ' += ' + str(group) + '){')
         em.depth += 1
-        for node in red.loop.body.nodes:
-            if node is red.update:
-                em.put('ovl_partial = ' + opname + '::apply<' + acc_t + '>(ovl_partial, ' + em.name(red.term) + ');')
-            else:
-                em.node(node)
+
+        def fold_body(nodes):
+            for node in nodes:
+                if node is red.update:
+                    em.put('ovl_partial = ' + opname + '::apply<' + acc_t + '>(ovl_partial, ' + em.name(red.term) + ');')
+                else:
+                    em.node(node)
+        if red.inner is None:
+            fold_body(red.loop.body.nodes)
+        else:
+            outer_var, inner_var = red.loop.args[0], red.inner.args[0]
+            em.put(em.name(outer_var) + ' = (' + ctype(outer_var.dtype) + ')(ovl_trip / ' + str(red.n_inner) + 'ull);')
+            for node in red.loop.body.nodes:
+                if node is red.inner:
+                    em.put(em.name(inner_var) + ' = (' + ctype(inner_var.dtype) + ')(ovl_trip % ' + str(red.n_inner) + 'ull);')
+                    fold_body(red.inner.body.nodes)
+                else:
+                    em.node(node)
         em.depth -= 1
         em.put('}')
         fold_cols = ['ovl_red_cols[ovl_member][ovl_tx] = %s;', '__syncthreads();']

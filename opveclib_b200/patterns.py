@@ -191,15 +191,25 @@ REDUCE_MIN_TRIPS = 128
 
 class ReduceSpec(object):
     """A worker's counted loop ``acc = acc (op) term(position, i)`` for i in [0, n): ``loop`` is the loop node,
-    ``acc`` the accumulator variable, ``update`` the assignment inside the loop, ``term`` the folded-in expression."""
+    ``acc`` the accumulator variable, ``update`` the assignment inside the loop, ``term`` the folded-in expression.
+    For a nest of two loops (``for i: for j: acc += a[w, i, j]``) ``loop`` is the outer one, ``inner`` the inner one,
+    ``n`` the product of the trip counts and ``n_inner`` the inner trip count: trip t of the flattened loop is
+    i = t / n_inner, j = t % n_inner."""
 
-    def __init__(self, op, n, loop, acc, update, term):
+    def __init__(self, op, n, loop, acc, update, term, inner=None, n_inner=None):
         self.op = op
         self.n = n
         self.loop = loop
         self.acc = acc
         self.update = update
         self.term = term
+        self.inner = inner
+        self.n_inner = n_inner
+
+    @property
+    def fastest_var(self):
+        """The loop variable that changes from one trip to the next."""
+        return (self.loop if self.inner is None else self.inner).args[0]
 
 
 def _depends_on(node, targets, seen=None):
@@ -216,27 +226,43 @@ def match_reduce(kernel, info=None):
     """ReduceSpec if every worker of the kernel is: statements, ONE counted loop (start 0, step 1, constant trip
     count) whose only effect is folding a term into one accumulator with + or *, statements - else None.  The
     term may be any expression of the position, the loop variable and tensor reads; nothing inside the loop may
-    write a tensor or observe the accumulator."""
+    write a tensor or observe the accumulator.  A nest of two such loops whose outer body holds nothing but value
+    computations and the inner loop counts as one loop over the pairs (i, j) in row-major order."""
     top = kernel.body.nodes
     all_nodes = list(iter_nodes(kernel.body))
     if any(n.kind in ('if', 'local') for n in all_nodes):
         return None
     loops = [n for n in all_nodes if n.kind == 'for']
-    if len(loops) != 1 or not any(x is loops[0] for x in top):
+    if len(loops) not in (1, 2) or not any(x is loops[0] for x in top):
         return None
     loop = loops[0]
     info = info or analyze(kernel)
+
+    def trips_from_zero(lp):
+        sym = info.loop_vars.get(id(lp.args[0]))
+        step = info.form_of(lp.args[3])
+        if sym is None or step is None or not step.is_const() or step.const != 1:
+            return None
+        start, last = info.ranges[sym]
+        return last + 1 if start == 0 else None
+
     var = loop.args[0]
-    sym = info.loop_vars.get(id(var))
-    if sym is None:
+    n = trips_from_zero(loop)
+    if n is None:
         return None
-    step = info.form_of(loop.args[3])
-    if step is None or not step.is_const() or step.const != 1:
-        return None
-    start, last = info.ranges[sym]
-    if start != 0:
-        return None
-    n = last + 1
+    inner, n_inner = None, None
+    if len(loops) == 2:
+        inner = loops[1]
+        # the outer body: the inner loop and, around it, nothing that has an effect
+        if not any(x is inner for x in loop.body.nodes):
+            return None
+        if any(x.kind not in ('const', 'cast', 'variable', 'unary', 'binary', 'read', 'limit')
+               for x in loop.body.nodes if x is not inner):
+            return None
+        n_inner = trips_from_zero(inner)
+        if n_inner is None:
+            return None
+        n *= n_inner
     if n < REDUCE_MIN_TRIPS:
         return None
     assigns = [a for a in all_nodes if a.kind == 'assign_var']
@@ -247,6 +273,8 @@ def match_reduce(kernel, info=None):
     update = assigns[0]
     acc, value = update.args
     if acc.kind != 'variable' or not any(x is acc for x in top) or acc is var or acc.dtype.name == 'float16':
+        return None
+    if inner is not None and (acc is inner.args[0] or id(update) not in set(id(x) for x in inner.body.nodes)):
         return None
     if value.kind != 'binary' or value.attr['fn'] not in ('add', 'mul') or value.dtype != acc.dtype:
         return None
@@ -275,6 +303,6 @@ def match_reduce(kernel, info=None):
     if acc.args[0].kind != 'const':
         return None
     for node in top[at + 1:]:
-        if any(x is var for x in getattr(node, 'args', ()) if x is not None):
+        if any(x is var or (inner is not None and x is inner.args[0]) for x in getattr(node, 'args', ()) if x is not None):
             return None
-    return ReduceSpec(value.attr['fn'], n, loop, acc, update, term)
+    return ReduceSpec(value.attr['fn'], n, loop, acc, update, term, inner, n_inner)

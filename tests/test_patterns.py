@@ -271,3 +271,31 @@ def test_rows_read_in_a_loop_are_staged_and_others_are_not():
     op = ns.lstm(np.zeros((512, 4096), np.float32), np.zeros((512, 1024), np.float32), forget_bias=0.0)
     prog, _ = runtime.compile_outputs([op[0], op[1]])
     assert prog.plans[0].meta['rows'] is None                           # no loop
+
+
+def test_loop_nests_that_fold_into_one_accumulator():
+    """A nest of two counted loops is one reduction over its trips; anything else in the outer body, or an inner
+    loop whose length depends on the outer variable, leaves the kernel generic."""
+    ovl = cases.impl().ovl
+    x = np.zeros((4, 6, 20, 30), np.float32)
+
+    def make(kind):
+        @ovl.operator()
+        def op(a):
+            out = ovl.output([a.shape[0], a.shape[1]], a.dtype)
+            pos = ovl.position_in([a.shape[0], a.shape[1]])
+            acc = ovl.variable(0, a.dtype)
+            rows = ovl.variable(0, a.dtype)
+            for i in ovl.arange(a.shape[2]):
+                if kind == 'effect':
+                    rows <<= rows + 1
+                for j in (ovl.arange(i + 1) if kind == 'triangle' else ovl.arange(a.shape[3])):
+                    acc <<= acc + a[pos[0], pos[1], i, j]
+            out[pos] = acc + rows
+            return out
+        return op
+
+    spec = _spec(make('plain')(x))
+    assert spec is not None and spec.n == 600 and spec.n_inner == 30 and spec.inner is not None
+    assert _spec(make('effect')(x)) is None
+    assert _spec(make('triangle')(x)) is None

@@ -117,3 +117,41 @@ def test_split_reduction_profiled_repeatedly_and_from_device_tensors():
     md, vd = torch.from_numpy(m).cuda(), torch.from_numpy(v).cuda()
     got = ns.ovl.evaluate([cases.user_ops(ns).matvec(md, vd)], target_language='b200')
     assert np.array_equal(got.cpu().numpy(), once)
+
+
+def _pool(ovl):
+    @ovl.operator()
+    def pool(x):
+        # sum over the last two axes with a nest of two loops (global pooling of an image per batch and channel)
+        out = ovl.output([x.shape[0], x.shape[1]], x.dtype)
+        pos = ovl.position_in([x.shape[0], x.shape[1]])
+        acc = ovl.variable(0, x.dtype)
+        for i in ovl.arange(x.shape[2]):
+            for j in ovl.arange(x.shape[3]):
+                acc <<= acc + x[pos[0], pos[1], i, j]
+        out[pos] = acc
+        return out
+    return pool
+
+
+@pytest.mark.parametrize('shape,dtype', [((8, 64, 56, 56), np.float32), ((3, 5, 20, 30), np.int32),
+                                         ((2, 1, 512, 512), np.float32), ((1, 3, 300, 301), np.int64)])
+def test_nest_of_two_loops_is_reduced_as_one_loop(shape, dtype):
+    """``for i: for j: acc += x[n, c, i, j]``: one loop over the pairs (i, j); with few workers and many trips the
+    trips are also cut into slices for many blocks."""
+    ns = cases.impl()
+    rs = np.random.RandomState(shape[2])
+    x = (rs.randint(-1000, 1000, shape) if np.dtype(dtype).kind == 'i' else rs.normal(0, 1, shape)).astype(dtype)
+    op = [_pool(ns.ovl)(x)]
+    red = _plan(ns, op).meta['red']
+    assert red is not None and red['trips'] == shape[2] * shape[3]
+    assert bool(red.get('split')) == (shape[2] * shape[3] >= 65536)
+    got = _run(ns, op)
+    assert _plan(ns, op).last_variant == 'red'
+    if np.dtype(dtype).kind == 'i':
+        assert np.array_equal(got, x.sum(axis=(2, 3), dtype=dtype))
+    else:
+        want = x.astype(np.float64).sum(axis=(2, 3))
+        assert np.all(np.abs(got.astype(np.float64) - want) <= 2e-5 * np.abs(x.astype(np.float64)).sum(axis=(2, 3)))
+    from oracle import runner
+    np.testing.assert_allclose(got, runner.evaluate(op), rtol=1e-4, atol=1e-3)
