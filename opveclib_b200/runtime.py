@@ -203,6 +203,13 @@ class KernelPlan(object):
                     return 'scan'
                 return 'scanu'
         if meta.get('red'):
+            # rows short enough to be staged whose length is not a whole number of warp-wide steps: the staged kernel
+            # (a thread per row, rows read as one contiguous piece) beats a warp per row with a ragged last step
+            # (fp32 rows of 200: 5.0 against 4.2 TB/s; rows of 128, 160, 256: the warp per row wins, 5.8 - 6.0 against
+            # 4.2 - 5.3)
+            if (meta.get('rows') and meta['red'].get('group') == 32 and meta['red']['trips'] % 32
+                    and os.environ.get('OVL_ROWS_MODE') != 'off'):
+                return 'rows'
             return 'red'
         if meta.get('tile') and os.environ.get('OVL_TILE_MODE') != 'off':
             return 'tile'
