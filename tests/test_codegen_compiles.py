@@ -29,11 +29,22 @@ def _graphs(ns):
         'scan_columns': (lambda: ns.cumsum(np.zeros((512, 96), np.float64), axis=0),
                          lambda m: m['scan'] is not None and m['scan'].get('strided')),
         'generic': (lambda: u.shift_cyclic(np.zeros(1000, f32)), lambda m: m['gen'] is not None),
+        'red_sliced': (lambda: u.matvec(np.zeros((2, 1 << 17), f32), np.zeros(1 << 17, f32)),
+                       lambda m: m['red'] is not None and m['red'].get('split')),
+        'red_across_sliced': (lambda: u.colsum(np.zeros((1 << 16, 40), f32)),
+                              lambda m: m['red'] is not None and m['red']['layout'] == 'across' and m['red'].get('split')),
+        'rows': (lambda: u.row_normalise(np.zeros((1024, 24), f32)),
+                 lambda m: m['rows'] is not None and m['rows']['staged'] and m['rows']['staged_outputs']),
+        'scan_flat': (lambda: ns.cumsum(np.zeros((4096, 36), f32), axis=1),
+                      lambda m: m['scan'] is not None and m['scan']['warp'] and m['scan']['warp'].get('chunks')),
+        'scan_ring_grouped': (lambda: ns.cumsum(np.zeros((16, 20 * 8192), f32), axis=1),
+                              lambda m: m['scan'] is not None and m['scan']['ring']['layout'] == 'grouped'),
     }
 
 
 @pytest.mark.parametrize('family', ['vec', 'tile', 'red_along', 'red_across', 'scan_block', 'scan_warp', 'scan_ring',
-                                    'scan_columns', 'generic'])
+                                    'scan_columns', 'generic', 'red_sliced', 'red_across_sliced', 'rows', 'scan_flat',
+                                    'scan_ring_grouped'])
 def test_family_is_generated_and_compiles(family):
     ns = cases.impl()
     build, check = _graphs(ns)[family]
