@@ -39,6 +39,10 @@ def _template_stamp():
 _STAMP = None
 
 
+#: environment variables read while a kernel's source is generated
+EMIT_SWITCHES = ('OVL_RED_SPLIT', 'OVL_RED_LAYOUT')
+
+
 def kernel_name(kernel, math='exact'):
     """'f' + sha224 of (kernel text, version, templates, math lowering) - stable across processes."""
     global _STAMP
@@ -47,6 +51,10 @@ def kernel_name(kernel, math='exact'):
     key = kernel.text() + '|' + version + '|' + cuda_emit.TEMPLATE_VERSION + '|' + _STAMP
     if math != 'exact':
         key += '|math=' + math
+    # switches that change the generated source name a different kernel (unset: the usual name)
+    for switch in EMIT_SWITCHES:
+        if os.environ.get(switch):
+            key += '|' + switch + '=' + os.environ[switch]
     return 'f' + hashlib.sha224(key.encode('utf-8')).hexdigest()[:48]
 
 
